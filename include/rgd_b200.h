@@ -1,0 +1,217 @@
+/*
+ * rgd_b200.h — C ABI of librgd_b200.so: hand-written sm_100a CUDA kernels for the
+ * rgd_triton operator set (row L2 / RMS norms, per-head LayerNorm, rotary
+ * embedding, fused LayerNorm+rotary, FlashAttention with additive bias).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer on the current device.  The caller owns
+ *     every buffer; the library allocates no device memory.
+ *   - Strides are in ELEMENTS.  The innermost (channel / head_dim) stride is 1.
+ *   - Sizes are int64_t; dtype codes are RGD_F32 / RGD_F16 / RGD_BF16.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *   - Return value: 0 success; <0 argument error (see RGD_E_*); >=1000 is
+ *     1000 + cudaError_t; RGD_E_TIMEOUT a bounded device-side wait that ran out.
+ *     Argument errors correspond to the AssertionError / RuntimeError the
+ *     reference's host wrappers raise; the Python layer re-raises them as such.
+ *   - All entry points are re-entrant; the only process-wide state is the
+ *     one-time cudaFuncSetAttribute opt-in for large shared memory.
+ *
+ * Each declaration cites the reference interface (file:line inside the
+ * rgd_triton project) whose launch it replaces.
+ */
+#ifndef RGD_B200_H
+#define RGD_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- dtype codes ------------------------------------------------------- */
+#define RGD_F32  0
+#define RGD_F16  1
+#define RGD_BF16 2
+
+/* ---- status codes ------------------------------------------------------ */
+#define RGD_OK              0
+#define RGD_E_INVALID      -1   /* generic bad argument (shape mismatch, negative size) */
+#define RGD_E_DTYPE        -2   /* dtype not supported by this operator                 */
+#define RGD_E_SIZE         -3   /* size outside the operator's limits (e.g. head_dim)   */
+#define RGD_E_STRIDE       -4   /* stride / alignment the kernel cannot address         */
+#define RGD_E_NULL         -5   /* required pointer is NULL                             */
+#define RGD_E_WORKSPACE    -6   /* caller workspace too small                           */
+#define RGD_E_DEVICE       -7   /* current device is not compute capability 10.x        */
+#define RGD_E_BIAS_SHAPE   -8   /* bias is neither (1,Tk) "vector" nor (Tq,Tk) "matrix" */
+#define RGD_E_TIMEOUT    2001   /* bounded device-side wait expired                     */
+#define RGD_E_CUDA_BASE  1000   /* 1000 + cudaError_t                                   */
+
+/* ---- tensor views ------------------------------------------------------ */
+/* [B, N, C] row tensor, channel stride 1. */
+typedef struct rgd_rows {
+    void   *ptr;
+    int64_t stride_b;
+    int64_t stride_n;
+} rgd_rows;
+
+/* 4-D head tensor addressed as (batch, head, token, channel) whatever its
+ * memory order: a [B,N,H,d] tensor passes stride_h = stride(2), stride_n =
+ * stride(1); a [B,H,N,d] tensor passes them the other way round.  This is the
+ * (B,H,N) stride triple of head_layernorm_cached.py:216-231. */
+typedef struct rgd_heads {
+    void   *ptr;
+    int64_t stride_b;
+    int64_t stride_h;
+    int64_t stride_n;
+} rgd_heads;
+
+/* ---- library ----------------------------------------------------------- */
+/* 1 if `device` is compute capability 10.x, 0 if not, <0 on error. */
+int         rgd_device_supported(int device);
+/* Static string for a status code returned by any entry point. */
+const char *rgd_status_string(int status);
+/* ABI version of this header (bumped on any signature change). */
+int         rgd_abi_version(void);
+/* Number of kernels this library has launched in the calling process. */
+int64_t     rgd_launch_count(void);
+
+/* ---- row L2 normalise: y = x / max(||x||, eps) ------------------------- */
+/* Replaces _norm_fwd / _fused_norm_fwd (l2normalize_cached.py:237-318,
+ * fused_l2normalize_cached.py:251-345).  nstreams is 1 or 2; with 2 both
+ * tensors are processed by ONE launch (the reference's virtual-tensor fusion).
+ * x[s], y[s]: views of [B, N[s], C[s]]. */
+int rgd_l2norm_fwd(int nstreams, const rgd_rows *x, const rgd_rows *y,
+                   const int64_t *N, const int64_t *C, int64_t B,
+                   float eps, int dtype, void *stream);
+/* Replaces _norm_bwd / _fused_norm_bwd (l2normalize_cached.py:321-399,
+ * fused_l2normalize_cached.py:348-461).  The row scale is recomputed from x,
+ * so no statistics buffer is passed. */
+int rgd_l2norm_bwd(int nstreams, const rgd_rows *x, const rgd_rows *dy,
+                   const rgd_rows *dx, const int64_t *N, const int64_t *C,
+                   int64_t B, float eps, int dtype, void *stream);
+
+/* ---- row RMS norm with affine weight: y = x * rsqrt(mean(x^2)+eps) * w -- */
+/* Replaces _rms_fwd / _fused_rms_fwd (rmsnorm_cached.py:319-403,
+ * fused_rmsnorm_cached.py:385-487).  w[s] points at [B or 1, C[s]] weights;
+ * w_stride_b[s] is 0 for a weight shared by all batches. */
+int rgd_rmsnorm_fwd(int nstreams, const rgd_rows *x, const void *const *w,
+                    const int64_t *w_stride_b, const rgd_rows *y,
+                    const int64_t *N, const int64_t *C, int64_t B,
+                    float eps, int x_dtype, int w_dtype, void *stream);
+/* Bytes of scratch rgd_rmsnorm_bwd needs (per-CTA fp32 dweight partials). */
+int64_t rgd_rmsnorm_bwd_workspace_bytes(int nstreams, const int64_t *N,
+                                        const int64_t *C, int64_t B);
+/* Replaces _rms_bwd / _fused_rms_bwd plus the dweight reduce kernel
+ * (rmsnorm_cached.py:406-569, fused_rmsnorm_cached.py:490-722).  dw[s] is
+ * [B, C[s]] when dw_per_batch[s] != 0, else [C[s]] — the sum over batches
+ * is taken in fp32 and rounded once to w_dtype.  dweight is deterministic:
+ * per-CTA partials in `workspace`, then a fixed-order reduce. */
+int rgd_rmsnorm_bwd(int nstreams, const rgd_rows *x, const void *const *w,
+                    const int64_t *w_stride_b, const rgd_rows *dy,
+                    const rgd_rows *dx, void *const *dw,
+                    const int *dw_per_batch, const int64_t *N,
+                    const int64_t *C, int64_t B, float eps, int x_dtype,
+                    int w_dtype, void *workspace, int64_t workspace_bytes,
+                    void *stream);
+
+/* ---- per-head LayerNorm (no affine) on Q and K in one launch ----------- */
+/* Replaces _fused_ln_qk_fwd / _fused_ln_qk_bwd
+ * (head_layernorm_cached.py:204-308, :310-408).  head_dim <= 256. */
+int rgd_headln_fwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *qo,
+                   const rgd_heads *ko, int64_t B, int64_t H, int64_t Nq,
+                   int64_t Nk, int64_t head_dim, float eps, int dtype,
+                   void *stream);
+int rgd_headln_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *dqo,
+                   const rgd_heads *dko, const rgd_heads *dq,
+                   const rgd_heads *dk, int64_t B, int64_t H, int64_t Nq,
+                   int64_t Nk, int64_t head_dim, float eps, int dtype,
+                   void *stream);
+
+/* ---- rotary embedding on Q and K in one launch ------------------------- */
+/* Replaces combined_rope_fn (head_rope_cached.py:160-275).  pos is
+ * [2, P, R] (index 0 = sin, 1 = cos) with element strides pos_stride_s /
+ * pos_stride_n; the first R channels of the first cut_q / cut_k tokens are
+ * rotated as interleaved pairs, everything else is copied.  transposed != 0
+ * applies the inverse rotation (the backward pass).  Arithmetic is done in
+ * the promoted type of x and pos, as the reference does: pos_dtype must be
+ * either x_dtype or RGD_F32.  qo may alias q (in place).  head_dim <= 128. */
+int rgd_rope(const rgd_heads *q, const rgd_heads *k, const void *pos,
+             int64_t pos_stride_s, int64_t pos_stride_n, const rgd_heads *qo,
+             const rgd_heads *ko, int64_t B, int64_t H, int64_t Nq, int64_t Nk,
+             int64_t head_dim, int64_t P, int64_t R, int64_t cut_q,
+             int64_t cut_k, int transposed, int x_dtype, int pos_dtype,
+             void *stream);
+
+/* ---- fused per-head LayerNorm -> rotary -------------------------------- */
+/* Replaces _fused_rope_ln_qk_fwd / _fused_rope_ln_qk_bwd
+ * (fused_ln_rope_cached.py:382-516, :518-647).  fp32 arithmetic throughout,
+ * one rounding on store. */
+int rgd_lnrope_fwd(const rgd_heads *q, const rgd_heads *k, const void *pos,
+                   int64_t pos_stride_s, int64_t pos_stride_n,
+                   const rgd_heads *qo, const rgd_heads *ko, int64_t B,
+                   int64_t H, int64_t Nq, int64_t Nk, int64_t head_dim,
+                   int64_t P, int64_t R, int64_t cut_q, int64_t cut_k,
+                   float eps, int x_dtype, int pos_dtype, void *stream);
+int rgd_lnrope_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *dqo,
+                   const rgd_heads *dko, const void *pos, int64_t pos_stride_s,
+                   int64_t pos_stride_n, const rgd_heads *dq,
+                   const rgd_heads *dk, int64_t B, int64_t H, int64_t Nq,
+                   int64_t Nk, int64_t head_dim, int64_t P, int64_t R,
+                   int64_t cut_q, int64_t cut_k, float eps, int x_dtype,
+                   int pos_dtype, void *stream);
+
+/* ---- FlashAttention ---------------------------------------------------- */
+#define RGD_BIAS_NONE   0
+#define RGD_BIAS_VECTOR 1   /* last two dims (1, Tk)  */
+#define RGD_BIAS_MATRIX 2   /* last two dims (Tq, Tk) */
+
+/* Additive bias, logically (B, H, Tq, Tk) with stride 0 on broadcast dims,
+ * innermost stride 1 (flash_attn_triton_cached.py:771-788). */
+typedef struct rgd_bias {
+    const void *ptr;
+    int64_t stride_b;
+    int64_t stride_h;
+    int64_t stride_q;   /* ignored for RGD_BIAS_VECTOR */
+    int     kind;       /* RGD_BIAS_*                   */
+    int     dtype;      /* the q dtype or RGD_F32       */
+} rgd_bias;
+
+/* Rows of the log-sum-exp buffer: Tq rounded up to a multiple of 64, the
+ * same rule as flash_attn_triton_cached.py:790-792. */
+int64_t rgd_attn_lse_rows(int64_t Tq);
+
+/* O = softmax(Q K^T * scale + bias) V and LSE.  Replaces
+ * _flash_attn_forward (flash_attn_triton_cached.py:758-882).
+ * q: (B,H,Tq,d) view; k, v: (B,H,Tk,d) views; o: like q; lse: fp32
+ * [B, H, rgd_attn_lse_rows(Tq)].  dtype RGD_F16 / RGD_BF16, d <= 128.
+ * causal masks key j > query i (top-left aligned, as the reference). */
+int rgd_attn_fwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v,
+                 const rgd_bias *bias, const rgd_heads *o, float *lse,
+                 int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d,
+                 float softmax_scale, int causal, int dtype, void *stream);
+
+/* Scratch bytes for rgd_attn_bwd (delta rows and, on the tensor-memory path,
+ * an fp32 dQ accumulator). */
+int64_t rgd_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq,
+                                     int64_t Tk, int64_t d, int dtype);
+
+/* dQ, dK, dV given dO.  Replaces _flash_attn_backward, including the
+ * delta = rowsum(O * dO) pre-pass (flash_attn_triton_cached.py:885-1075).
+ * Bias gradient is not produced (the reference refuses it, :1107). */
+int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v,
+                 const rgd_bias *bias, const rgd_heads *o, const float *lse,
+                 const rgd_heads *d_o, const rgd_heads *dq,
+                 const rgd_heads *dk, const rgd_heads *dv, int64_t B,
+                 int64_t H, int64_t Tq, int64_t Tk, int64_t d,
+                 float softmax_scale, int causal, int dtype, void *workspace,
+                 int64_t workspace_bytes, void *stream);
+
+/* Which attention implementation a call with these sizes takes:
+ * 1 = tcgen05 / tensor-memory / TMA kernels, 0 = general mma.sync kernels. */
+int rgd_attn_uses_tmem(int64_t Tq, int64_t Tk, int64_t d, int dtype,
+                       int64_t q_stride_n, int64_t k_stride_n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RGD_B200_H */

@@ -1,0 +1,125 @@
+// extern "C" attention entry points: argument validation, path selection
+// (tensor-memory kernels for aligned head_dim 64 / 128, general mma.sync
+// kernels otherwise) and workspace layout.
+#include "attn_mma.cuh"
+
+namespace rgd {
+namespace attn {
+int general_fwd(const AttnParams &p, int dtype, cudaStream_t st);
+int general_bwd(const AttnParams &p, int dtype, cudaStream_t st);
+}  // namespace attn
+}  // namespace rgd
+
+using namespace rgd;
+using rgd::attn::AttnParams;
+
+namespace {
+
+bool heads_vec16(const rgd_heads *v) {
+    return v && is_aligned(v->ptr, 16) && v->stride_b % 8 == 0 && v->stride_h % 8 == 0 && v->stride_n % 8 == 0;
+}
+
+int64_t lse_rows(int64_t Tq) { return (Tq + 63) / 64 * 64; }
+
+int check_common(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias, int64_t B,
+                 int64_t H, int64_t Tq, int64_t Tk, int64_t d, int dtype) {
+    if (!q || !k || !v) return RGD_E_NULL;
+    if (dtype != RGD_F16 && dtype != RGD_BF16) return RGD_E_DTYPE;
+    if (B < 0 || H < 0 || Tq < 0 || Tk < 0 || d < 0) return RGD_E_INVALID;
+    if (d > 128) return RGD_E_SIZE;
+    if (B * H > 65535 * 32768LL || Tq > (1LL << 30) || Tk > (1LL << 30) || B > INT32_MAX || H > INT32_MAX)
+        return RGD_E_SIZE;
+    const bool empty = B == 0 || H == 0 || d == 0;
+    if (!empty) {
+        if (Tq > 0 && !q->ptr) return RGD_E_NULL;
+        if (Tk > 0 && (!k->ptr || !v->ptr)) return RGD_E_NULL;
+    }
+    if (bias && bias->kind != RGD_BIAS_NONE) {
+        if (bias->kind != RGD_BIAS_VECTOR && bias->kind != RGD_BIAS_MATRIX) return RGD_E_BIAS_SHAPE;
+        if (bias->dtype != dtype && bias->dtype != RGD_F32) return RGD_E_DTYPE;
+        if (!bias->ptr && !empty && Tq > 0 && Tk > 0) return RGD_E_NULL;
+    }
+    return RGD_OK;
+}
+
+void fill_common(AttnParams &p, const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
+                 int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d, float scale, int causal) {
+    p.q = q->ptr; p.q_sb = q->stride_b; p.q_sh = q->stride_h; p.q_sn = q->stride_n;
+    p.k = k->ptr; p.k_sb = k->stride_b; p.k_sh = k->stride_h; p.k_sn = k->stride_n;
+    p.v = v->ptr; p.v_sb = v->stride_b; p.v_sh = v->stride_h; p.v_sn = v->stride_n;
+    p.bias_kind = RGD_BIAS_NONE;
+    if (bias && bias->kind != RGD_BIAS_NONE) {
+        p.bias = bias->ptr;
+        p.b_sb = bias->stride_b;
+        p.b_sh = bias->stride_h;
+        p.b_sq = bias->kind == RGD_BIAS_MATRIX ? bias->stride_q : 0;
+        p.bias_kind = bias->kind;
+        p.bias_f32 = bias->dtype == RGD_F32;
+    }
+    p.B = (int)B; p.H = (int)H; p.Tq = (int)Tq; p.Tk = (int)Tk; p.d = (int)d;
+    p.Tq_rounded = (int)lse_rows(Tq);
+    p.causal = causal ? 1 : 0;
+    p.scale = scale;
+    const bool dvec = d % 8 == 0;
+    p.vec_q = dvec && heads_vec16(q);
+    p.vec_k = dvec && heads_vec16(k);
+    p.vec_v = dvec && heads_vec16(v);
+}
+
+}  // namespace
+
+extern "C" int64_t rgd_attn_lse_rows(int64_t Tq) { return Tq < 0 ? RGD_E_INVALID : lse_rows(Tq); }
+
+extern "C" int rgd_attn_uses_tmem(int64_t, int64_t, int64_t, int, int64_t, int64_t) { return 0; }
+
+extern "C" int rgd_attn_fwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
+                            const rgd_heads *o, float *lse, int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d,
+                            float softmax_scale, int causal, int dtype, void *stream) {
+    if (int e = check_common(q, k, v, bias, B, H, Tq, Tk, d, dtype)) return e;
+    if (!o) return RGD_E_NULL;
+    const bool work = B > 0 && H > 0 && Tq > 0;
+    if (work && (!lse || (d > 0 && !o->ptr))) return RGD_E_NULL;
+    AttnParams p{};
+    fill_common(p, q, k, v, bias, B, H, Tq, Tk, d, softmax_scale, causal);
+    p.out_o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_sn = o->stride_n;
+    p.vec_o = d % 8 == 0 && heads_vec16(o);
+    p.lse = lse;
+    return attn::general_fwd(p, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int64_t rgd_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d, int dtype) {
+    (void)Tk; (void)d; (void)dtype;
+    if (B < 0 || H < 0 || Tq < 0) return RGD_E_INVALID;
+    return B * H * lse_rows(Tq) * (int64_t)sizeof(float);   // delta
+}
+
+extern "C" int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
+                            const rgd_heads *o, const float *lse, const rgd_heads *d_o, const rgd_heads *dq,
+                            const rgd_heads *dk, const rgd_heads *dv, int64_t B, int64_t H, int64_t Tq, int64_t Tk,
+                            int64_t d, float softmax_scale, int causal, int dtype, void *workspace,
+                            int64_t workspace_bytes, void *stream) {
+    if (int e = check_common(q, k, v, bias, B, H, Tq, Tk, d, dtype)) return e;
+    if (!o || !d_o || !dq || !dk || !dv) return RGD_E_NULL;
+    const bool work = B > 0 && H > 0 && d > 0;
+    if (work && Tq > 0 && (!o->ptr || !d_o->ptr || !dq->ptr || !lse)) return RGD_E_NULL;
+    if (work && Tk > 0 && (!dk->ptr || !dv->ptr)) return RGD_E_NULL;
+    const int64_t need = rgd_attn_bwd_workspace_bytes(B, H, Tq, Tk, d, dtype);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return RGD_E_WORKSPACE;
+    if (need > 0 && !is_aligned(workspace, 16)) return RGD_E_STRIDE;
+    AttnParams p{};
+    fill_common(p, q, k, v, bias, B, H, Tq, Tk, d, softmax_scale, causal);
+    p.o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_sn = o->stride_n;
+    p.d_o = d_o->ptr; p.do_sb = d_o->stride_b; p.do_sh = d_o->stride_h; p.do_sn = d_o->stride_n;
+    p.dq = dq->ptr; p.dq_sb = dq->stride_b; p.dq_sh = dq->stride_h; p.dq_sn = dq->stride_n;
+    p.dk = dk->ptr; p.dk_sb = dk->stride_b; p.dk_sh = dk->stride_h; p.dk_sn = dk->stride_n;
+    p.dv = dv->ptr; p.dv_sb = dv->stride_b; p.dv_sh = dv->stride_h; p.dv_sn = dv->stride_n;
+    const bool dvec = d % 8 == 0;
+    p.vec_o = dvec && heads_vec16(o);
+    p.vec_do = dvec && heads_vec16(d_o);
+    p.vec_dq = dvec && heads_vec16(dq);
+    p.vec_dk = dvec && heads_vec16(dk);
+    p.vec_dv = dvec && heads_vec16(dv);
+    p.lse = const_cast<float *>(lse);
+    p.delta = reinterpret_cast<float *>(workspace);
+    return attn::general_bwd(p, dtype, (cudaStream_t)stream);
+}

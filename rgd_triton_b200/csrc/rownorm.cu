@@ -1,0 +1,555 @@
+// Row normalisations over [B, N, C] tensors: L2 normalise and RMS norm with an
+// affine weight, forward and backward, for one or two tensors per launch.
+//
+// Bandwidth-bound design: a group of `tpr` consecutive threads owns one row and
+// keeps it in registers (one 16-byte access per thread and per column slot, so
+// every tensor is read exactly once and written exactly once), row sums are
+// reduced with shuffles (plus one shared-memory hop when a row spans several
+// warps), and all arithmetic is fp32.  A CTA walks the rows of one batch of one
+// tensor; with two tensors the block index selects the tensor, which is the
+// reference's "virtual tensor" fusion (fused_rmsnorm_cached.py:429).
+//
+// dweight is accumulated per thread over all rows the CTA visits, reduced over
+// the CTA's row groups in shared memory and written as one fp32 partial row per
+// CTA; a second kernel adds the partial rows in a fixed order.  That replaces
+// the reference's spin-lock accumulation (rmsnorm_cached.py:245-264) by a
+// deterministic two-stage reduce.
+#include "common.cuh"
+
+namespace rgd {
+
+enum RowOp { L2_FWD = 0, L2_BWD = 1, RMS_FWD = 2, RMS_BWD = 3 };
+
+constexpr int ROW_THREADS = 256;
+
+struct RowStream {
+    const void *x;
+    const void *dy;
+    void *out;        // y (forward) or dx (backward)
+    const void *w;    // RMS only
+    float *dw_part;   // RMS backward: [B][P][C] fp32 partial rows
+    int64_t sxb, sxn, sdb, sdn, sob, son, swb;
+    int N, C, P;      // rows per batch, channels, CTAs per batch
+};
+
+struct RowParams {
+    RowStream s[2];
+    int split;        // number of CTAs that belong to stream 0
+    int tpr;          // threads per row (power of two, <= 256)
+    int w_dtype;
+    float eps;
+};
+
+// Sum over the `tpr` threads of a row group.  `red` is 2 x 8 floats of shared
+// memory used alternately (`phase` toggles) when a group spans several warps.
+__device__ __forceinline__ float group_sum(float v, int tpr, float (*red)[8], int &phase) {
+    v = warp_group_sum(v, tpr < 32 ? tpr : 32);
+    if (tpr > 32) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) red[phase][warp] = v;
+        __syncthreads();
+        const int wpg = tpr >> 5;
+        const int first = (warp / wpg) * wpg;
+        float t = 0.f;
+        for (int i = 0; i < wpg; ++i) t += red[phase][first + i];
+        v = t;
+        phase ^= 1;
+    }
+    return v;
+}
+
+// T: element type.  VE: elements per access (16 bytes / sizeof(T), or 1 for
+// rows that are not 16-byte addressable).  VPT: column slots per thread.
+template <typename T, int VE, int VPT, int OP>
+__global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant__ RowParams p) {
+    constexpr bool BWD = (OP == L2_BWD || OP == RMS_BWD);
+    constexpr bool RMS = (OP == RMS_FWD || OP == RMS_BWD);
+    using V = Vec<T, VE>;
+
+    __shared__ float red[2][8];
+    __shared__ float dwred[OP == RMS_BWD ? ROW_THREADS * VE : 1];
+    int phase = 0;
+
+    const int sid = (int)blockIdx.x >= p.split ? 1 : 0;
+    const RowStream &s = p.s[sid];
+    const int local = (int)blockIdx.x - (sid ? p.split : 0);
+    const int b = local / s.P;
+    const int chunk = local - b * s.P;
+    const int tpr = p.tpr;
+    const int rpc = ROW_THREADS / tpr;
+    const int rg = (int)threadIdx.x / tpr;
+    const int t = (int)threadIdx.x - rg * tpr;
+    const int C = s.C;
+    const float invC = 1.0f / (float)C;
+
+    float wv[RMS ? VPT * VE : 1];
+    float dwacc[OP == RMS_BWD ? VPT * VE : 1];
+    if (RMS) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+#pragma unroll
+            for (int e = 0; e < VE; ++e) {
+                const int col = (t + j * tpr) * VE + e;
+                wv[j * VE + e] = col < C ? load_as_f32(s.w, (int64_t)b * s.swb + col, p.w_dtype) : 0.f;
+            }
+    }
+    if (OP == RMS_BWD) {
+#pragma unroll
+        for (int i = 0; i < VPT * VE; ++i) dwacc[i] = 0.f;
+    }
+
+    const T *xb = reinterpret_cast<const T *>(s.x) + (int64_t)b * s.sxb;
+    const T *db = BWD ? reinterpret_cast<const T *>(s.dy) + (int64_t)b * s.sdb : nullptr;
+    T *ob = reinterpret_cast<T *>(s.out) + (int64_t)b * s.sob;
+
+    const int step = s.P * rpc;
+    const int iters = (s.N + step - 1) / step;
+    for (int it = 0; it < iters; ++it) {
+        const int n = it * step + chunk * rpc + rg;
+        const bool valid = n < s.N;
+        const T *xr = xb + (int64_t)n * s.sxn;
+        const T *dr = BWD ? db + (int64_t)n * s.sdn : nullptr;
+
+        V xq[VPT];
+        V dq[BWD ? VPT : 1];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int col = (t + j * tpr) * VE;
+            if (valid && col < C) {
+                xq[j] = load_vec<T, VE>(xr + col);
+                if (BWD) dq[j] = load_vec<T, VE>(dr + col);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    xq[j].v[e] = from_f32<T>(0.f);
+                    if (BWD) dq[j].v[e] = from_f32<T>(0.f);
+                }
+            }
+        }
+
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+#pragma unroll
+            for (int e = 0; e < VE; ++e) {
+                const float v = to_f32<T>(xq[j].v[e]);
+                ss += v * v;
+            }
+        ss = group_sum(ss, tpr, red, phase);
+
+        // Row scale: rmsnorm_cached.py:75-76, l2normalize_cached.py:72-77.
+        float r;
+        if (RMS) {
+            r = rsqrtf(ss * invC + p.eps);
+        } else {
+            const float len = sqrtf(ss);
+            r = (len < p.eps) ? (1.0f / p.eps) : (1.0f / len);
+        }
+
+        if (!BWD) {
+            T *orow = ob + (int64_t)n * s.son;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int col = (t + j * tpr) * VE;
+                V yo;
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    float v = to_f32<T>(xq[j].v[e]) * r;
+                    if (RMS) v = v * wv[j * VE + e];
+                    yo.v[e] = from_f32<T>(v);
+                }
+                if (valid && col < C) store_vec<T, VE>(orow + col, yo);
+            }
+        } else {
+            // g = sum(xhat * dy * w) [/ C for RMS]: rmsnorm_cached.py:213-231,
+            // l2normalize_cached.py:214-226.
+            float g = 0.f;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j)
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    const float xh = to_f32<T>(xq[j].v[e]) * r;
+                    const float d = to_f32<T>(dq[j].v[e]);
+                    g += RMS ? xh * d * wv[j * VE + e] : xh * d;
+                }
+            g = group_sum(g, tpr, red, phase);
+            if (RMS) g *= invC;
+
+            T *orow = ob + (int64_t)n * s.son;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int col = (t + j * tpr) * VE;
+                V yo;
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    const float xh = to_f32<T>(xq[j].v[e]) * r;
+                    const float d = to_f32<T>(dq[j].v[e]);
+                    float v;
+                    if (RMS) {
+                        v = (d * wv[j * VE + e] - xh * g) * r;
+                        if (OP == RMS_BWD) dwacc[j * VE + e] += xh * d;   // zero for padded rows
+                    } else {
+                        v = (d - xh * g) * r;
+                    }
+                    yo.v[e] = from_f32<T>(v);
+                }
+                if (valid && col < C) store_vec<T, VE>(orow + col, yo);
+            }
+        }
+    }
+
+    if (OP == RMS_BWD) {
+        // Fold the CTA's row groups together, one column slot at a time, and
+        // write this CTA's partial row.
+        float *prow = s.dw_part + ((int64_t)b * s.P + chunk) * C;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            __syncthreads();
+#pragma unroll
+            for (int e = 0; e < VE; ++e) dwred[threadIdx.x * VE + e] = dwacc[j * VE + e];
+            __syncthreads();
+            if (rg == 0) {
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    float a = 0.f;
+                    for (int g2 = 0; g2 < rpc; ++g2) a += dwred[(g2 * tpr + t) * VE + e];
+                    const int col = (t + j * tpr) * VE + e;
+                    if (col < C) prow[col] = a;
+                }
+            }
+        }
+    }
+}
+
+// Second stage of dweight: dw[b or -, c] = sum over partial rows, fixed order.
+// blockDim = (32 columns, 32 row lanes); grid = (ceil(C/32), B or 1, streams).
+struct DwReduceStream {
+    const float *part;   // [rows_total][C]
+    void *dw;            // [B or 1][C] in w dtype
+    int C;
+    int rows_per_out;    // partial rows folded into one output row
+    int n_out;           // output rows (B for per-batch weights, else 1)
+};
+struct DwReduceParams {
+    DwReduceStream s[2];
+    int w_dtype;
+};
+
+__global__ void __launch_bounds__(1024) dw_reduce_kernel(const __grid_constant__ DwReduceParams p) {
+    __shared__ float tile[32][33];
+    const DwReduceStream &s = p.s[blockIdx.z];
+    const int o = blockIdx.y;
+    if (o >= s.n_out) return;
+    const int col = blockIdx.x * 32 + threadIdx.x;
+    if (blockIdx.x * 32 >= s.C) return;
+    float a = 0.f;
+    if (col < s.C) {
+        const float *base = s.part + (int64_t)o * s.rows_per_out * s.C + col;
+        for (int r = threadIdx.y; r < s.rows_per_out; r += 32) a += base[(int64_t)r * s.C];
+    }
+    tile[threadIdx.y][threadIdx.x] = a;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < s.C) {
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) t += tile[r][threadIdx.x];
+        store_from_f32(s.dw, (int64_t)o * s.C + col, p.w_dtype, t);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+namespace {
+
+struct RowPlan {
+    int ve;    // 1 or 16/sizeof(T)
+    int vpt;   // template slot count
+    int tpr;
+};
+
+// Pick the access width, threads per row and slots per thread for rows of
+// `cmax` channels.  Returns false when the row does not fit in registers.
+bool plan_rows(int cmax, int esize, bool vector_ok, RowPlan &pl) {
+    const int ve = vector_ok ? 16 / esize : 1;
+    const int nvec = (cmax + ve - 1) / ve;
+    int tpr = next_pow2(nvec);
+    if (tpr > 32) tpr = 32;
+    int vpt = (nvec + tpr - 1) / tpr;
+    while (vpt > 4 && tpr < ROW_THREADS) {
+        tpr <<= 1;
+        vpt = (nvec + tpr - 1) / tpr;
+    }
+    const int vmax = vector_ok ? 8 : 32;
+    if (vpt > vmax) return false;
+    if (vector_ok) {
+        if (vpt > 4) vpt = 8;
+    } else {
+        vpt = vpt <= 4 ? 4 : 32;
+    }
+    pl.ve = ve;
+    pl.vpt = vpt;
+    pl.tpr = tpr;
+    return true;
+}
+
+template <typename T, int VE, int OP>
+int launch_rows_vpt(const RowParams &p, int vpt, int grid, cudaStream_t st) {
+    switch (vpt) {
+#define RGD_CASE(N)                                                   \
+    case N:                                                           \
+        row_kernel<T, VE, N, OP><<<grid, ROW_THREADS, 0, st>>>(p);    \
+        break;
+        RGD_CASE(1)
+        RGD_CASE(2)
+        RGD_CASE(3)
+        RGD_CASE(4)
+        RGD_CASE(8)
+#undef RGD_CASE
+        default:
+            return RGD_E_SIZE;
+    }
+    count_launch();
+    return check_launch();
+}
+
+template <typename T, int OP>
+int launch_rows_scalar(const RowParams &p, int vpt, int grid, cudaStream_t st) {
+    if (vpt == 4)
+        row_kernel<T, 1, 4, OP><<<grid, ROW_THREADS, 0, st>>>(p);
+    else if (vpt == 32)
+        row_kernel<T, 1, 32, OP><<<grid, ROW_THREADS, 0, st>>>(p);
+    else
+        return RGD_E_SIZE;
+    count_launch();
+    return check_launch();
+}
+
+template <typename T, int OP>
+int launch_rows(const RowParams &p, const RowPlan &pl, int grid, cudaStream_t st) {
+    if (pl.ve == 1) return launch_rows_scalar<T, OP>(p, pl.vpt, grid, st);
+    return launch_rows_vpt<T, VecElems<T>::value, OP>(p, pl.vpt, grid, st);
+}
+
+template <int OP>
+int launch_rows_dtype(int dtype, const RowParams &p, const RowPlan &pl, int grid, cudaStream_t st) {
+    switch (dtype) {
+        case RGD_F32: return launch_rows<float, OP>(p, pl, grid, st);
+        case RGD_F16: return launch_rows<__half, OP>(p, pl, grid, st);
+        case RGD_BF16: return launch_rows<__nv_bfloat16, OP>(p, pl, grid, st);
+    }
+    return RGD_E_DTYPE;
+}
+
+bool view_vec_ok(const rgd_rows &v, int esize) {
+    const int ve = 16 / esize;
+    return is_aligned(v.ptr, 16) && v.stride_b % ve == 0 && v.stride_n % ve == 0;
+}
+
+// CTAs per batch for each stream.  `budget` is the total CTA count aimed at.
+void split_ctas(int nstreams, const int64_t *N, int64_t B, int rpc, int budget, int *P) {
+    int64_t groups[2] = {0, 0}, total = 0;
+    for (int s = 0; s < nstreams; ++s) {
+        groups[s] = ceil_div64(N[s], rpc);
+        total += groups[s] * B;
+    }
+    for (int s = 0; s < nstreams; ++s) {
+        int64_t ps = groups[s];
+        if (total > budget) {
+            ps = (groups[s] * budget + total - 1) / total;   // proportional share per batch
+            if (ps < 1) ps = 1;
+            if (ps > groups[s]) ps = groups[s];
+        }
+        if (ps < 1) ps = 1;
+        P[s] = (int)ps;
+    }
+}
+
+struct RowCall {
+    int nstreams;
+    const rgd_rows *x, *dy, *out;
+    const void *const *w;
+    const int64_t *wsb;
+    const int64_t *N, *C;
+    int64_t B;
+    float eps;
+    int x_dtype, w_dtype;
+};
+
+int validate_rows(const RowCall &c, bool bwd, bool rms) {
+    if (c.nstreams < 1 || c.nstreams > 2) return RGD_E_INVALID;
+    if (!c.x || !c.out || !c.N || !c.C) return RGD_E_NULL;
+    if (bwd && !c.dy) return RGD_E_NULL;
+    if (rms && (!c.w || !c.wsb)) return RGD_E_NULL;
+    if (!dtype_ok(c.x_dtype)) return RGD_E_DTYPE;
+    if (rms && !dtype_ok(c.w_dtype)) return RGD_E_DTYPE;
+    if (c.B < 0 || c.B > INT32_MAX) return RGD_E_INVALID;
+    for (int s = 0; s < c.nstreams; ++s) {
+        if (c.N[s] < 0 || c.C[s] < 0 || c.N[s] > INT32_MAX || c.C[s] > INT32_MAX) return RGD_E_INVALID;
+        const bool empty = c.B == 0 || c.N[s] == 0 || c.C[s] == 0;
+        if (!empty) {
+            if (!c.x[s].ptr || !c.out[s].ptr) return RGD_E_NULL;
+            if (bwd && !c.dy[s].ptr) return RGD_E_NULL;
+        }
+        if (rms && c.C[s] > 0 && !c.w[s]) return RGD_E_NULL;
+    }
+    return RGD_OK;
+}
+
+// Build the launch for one of the four row operators.  *plan_out / *P_out
+// return the chosen geometry (needed by the dweight reduce).
+template <int OP>
+int run_rows(const RowCall &c, float *dw_part0, float *dw_part1, int budget, cudaStream_t st, int *P_out) {
+    constexpr bool BWD = (OP == L2_BWD || OP == RMS_BWD);
+    const int esize = dtype_size(c.x_dtype);
+    int cmax = 0;
+    bool vec_ok = true;
+    for (int s = 0; s < c.nstreams; ++s) {
+        if (c.C[s] > cmax) cmax = (int)c.C[s];
+        vec_ok = vec_ok && (c.C[s] % (16 / esize) == 0) && view_vec_ok(c.x[s], esize) && view_vec_ok(c.out[s], esize);
+        if (BWD) vec_ok = vec_ok && view_vec_ok(c.dy[s], esize);
+    }
+    RowPlan pl;
+    if (!plan_rows(cmax > 0 ? cmax : 1, esize, vec_ok, pl)) return RGD_E_SIZE;
+
+    RowParams p{};
+    p.tpr = pl.tpr;
+    p.w_dtype = c.w_dtype;
+    p.eps = c.eps;
+    int P[2] = {0, 0};
+    split_ctas(c.nstreams, c.N, c.B, ROW_THREADS / pl.tpr, budget, P);
+    int64_t grid = 0;
+    for (int s = 0; s < c.nstreams; ++s) {
+        RowStream &rs = p.s[s];
+        rs.x = c.x[s].ptr;
+        rs.sxb = c.x[s].stride_b;
+        rs.sxn = c.x[s].stride_n;
+        rs.out = c.out[s].ptr;
+        rs.sob = c.out[s].stride_b;
+        rs.son = c.out[s].stride_n;
+        if (BWD) {
+            rs.dy = c.dy[s].ptr;
+            rs.sdb = c.dy[s].stride_b;
+            rs.sdn = c.dy[s].stride_n;
+        }
+        if (c.w) {
+            rs.w = c.w[s];
+            rs.swb = c.wsb[s];
+        }
+        rs.dw_part = s == 0 ? dw_part0 : dw_part1;
+        rs.N = (int)c.N[s];
+        rs.C = (int)c.C[s];
+        // A stream with no rows or no channels gets no CTAs.
+        const bool empty = c.N[s] == 0 || c.C[s] == 0;
+        rs.P = empty ? 0 : P[s];
+        if (rs.P == 0) rs.P = 1, P[s] = 0; else P[s] = rs.P;
+        const int64_t ctas = (int64_t)P[s] * c.B;
+        if (s == 0) p.split = (int)ctas;
+        grid += ctas;
+    }
+    if (P_out) { P_out[0] = P[0]; P_out[1] = P[1]; }
+    if (grid == 0) return RGD_OK;
+    if (grid > INT32_MAX) return RGD_E_SIZE;
+    return launch_rows_dtype<OP>(c.x_dtype, p, pl, (int)grid, st);
+}
+
+constexpr int FWD_CTAS_PER_SM = 16;
+constexpr int BWD_CTAS_PER_SM = 4;
+
+}  // namespace
+
+}  // namespace rgd
+
+using namespace rgd;
+
+extern "C" int rgd_l2norm_fwd(int nstreams, const rgd_rows *x, const rgd_rows *y, const int64_t *N,
+                              const int64_t *C, int64_t B, float eps, int dtype, void *stream) {
+    RowCall c{nstreams, x, nullptr, y, nullptr, nullptr, N, C, B, eps, dtype, RGD_F32};
+    if (int e = validate_rows(c, false, false)) return e;
+    return run_rows<L2_FWD>(c, nullptr, nullptr, FWD_CTAS_PER_SM * num_sms(), (cudaStream_t)stream, nullptr);
+}
+
+extern "C" int rgd_l2norm_bwd(int nstreams, const rgd_rows *x, const rgd_rows *dy, const rgd_rows *dx,
+                              const int64_t *N, const int64_t *C, int64_t B, float eps, int dtype,
+                              void *stream) {
+    RowCall c{nstreams, x, dy, dx, nullptr, nullptr, N, C, B, eps, dtype, RGD_F32};
+    if (int e = validate_rows(c, true, false)) return e;
+    return run_rows<L2_BWD>(c, nullptr, nullptr, FWD_CTAS_PER_SM * num_sms(), (cudaStream_t)stream, nullptr);
+}
+
+extern "C" int rgd_rmsnorm_fwd(int nstreams, const rgd_rows *x, const void *const *w,
+                               const int64_t *w_stride_b, const rgd_rows *y, const int64_t *N,
+                               const int64_t *C, int64_t B, float eps, int x_dtype, int w_dtype,
+                               void *stream) {
+    RowCall c{nstreams, x, nullptr, y, w, w_stride_b, N, C, B, eps, x_dtype, w_dtype};
+    if (int e = validate_rows(c, false, true)) return e;
+    return run_rows<RMS_FWD>(c, nullptr, nullptr, FWD_CTAS_PER_SM * num_sms(), (cudaStream_t)stream, nullptr);
+}
+
+// Upper bound of partial rows per stream: never more CTAs than the budget.
+static int64_t rms_bwd_part_rows() { return (int64_t)BWD_CTAS_PER_SM * num_sms(); }
+
+extern "C" int64_t rgd_rmsnorm_bwd_workspace_bytes(int nstreams, const int64_t *N, const int64_t *C,
+                                                   int64_t B) {
+    if (nstreams < 1 || nstreams > 2 || !N || !C || B < 0) return RGD_E_INVALID;
+    int64_t bytes = 0;
+    for (int s = 0; s < nstreams; ++s) {
+        // P[s] * B <= budget + B (each stream keeps at least one CTA per batch).
+        const int64_t rows = rms_bwd_part_rows() + B;
+        bytes += rows * C[s] * (int64_t)sizeof(float);
+        bytes = (bytes + 255) / 256 * 256;
+    }
+    return bytes;
+}
+
+extern "C" int rgd_rmsnorm_bwd(int nstreams, const rgd_rows *x, const void *const *w,
+                               const int64_t *w_stride_b, const rgd_rows *dy, const rgd_rows *dx,
+                               void *const *dw, const int *dw_per_batch, const int64_t *N,
+                               const int64_t *C, int64_t B, float eps, int x_dtype, int w_dtype,
+                               void *workspace, int64_t workspace_bytes, void *stream) {
+    RowCall c{nstreams, x, dy, dx, w, w_stride_b, N, C, B, eps, x_dtype, w_dtype};
+    if (int e = validate_rows(c, true, true)) return e;
+    if (!dw || !dw_per_batch) return RGD_E_NULL;
+    const int64_t need = rgd_rmsnorm_bwd_workspace_bytes(nstreams, N, C, B);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return RGD_E_WORKSPACE;
+    if (need > 0 && !is_aligned(workspace, 16)) return RGD_E_STRIDE;
+
+    float *part[2] = {nullptr, nullptr};
+    {
+        int64_t off = 0;
+        for (int s = 0; s < nstreams; ++s) {
+            part[s] = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + off);
+            off += (rms_bwd_part_rows() + B) * C[s] * (int64_t)sizeof(float);
+            off = (off + 255) / 256 * 256;
+        }
+    }
+    int P[2] = {0, 0};
+    cudaStream_t st = (cudaStream_t)stream;
+    if (int e = run_rows<RMS_BWD>(c, part[0], part[1], (int)rms_bwd_part_rows(), st, P)) return e;
+
+    // Second stage.  A stream without rows still has to produce dw = 0.
+    DwReduceParams rp{};
+    rp.w_dtype = w_dtype;
+    int cmax = 0, omax = 0;
+    for (int s = 0; s < nstreams; ++s) {
+        if (C[s] > 0 && !dw[s]) return RGD_E_NULL;
+        DwReduceStream &d = rp.s[s];
+        d.part = part[s];
+        d.dw = dw[s];
+        d.C = (int)C[s];
+        if (dw_per_batch[s]) {
+            d.n_out = (int)B;
+            d.rows_per_out = P[s];
+        } else {
+            d.n_out = B > 0 ? 1 : 0;
+            d.rows_per_out = P[s] * (int)B;
+        }
+        if (d.C > cmax) cmax = d.C;
+        if (d.n_out > omax) omax = d.n_out;
+    }
+    if (cmax == 0 || omax == 0) return RGD_OK;
+    dim3 grid((cmax + 31) / 32, omax, nstreams), block(32, 32);
+    dw_reduce_kernel<<<grid, block, 0, st>>>(rp);
+    count_launch();
+    return check_launch();
+}
