@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Benchmark of the operator hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload ("step"): FlashAttention forward + backward, bf16, q/k/v
+[4, 4096, 16, 128], no bias, non-causal — the third benchmark configuration,
+the one the TFLOPS metric is quoted on.  The norm / RoPE half of the metric
+(HBM GB/s) is measured in the same run on the second configuration
+(FusedLNRoPE forward + backward, q/k [8, 4096, 16, 128] bf16) and reported
+under ``norm_rope``.  With N > 1 (launched by torchrun, one rank per GPU)
+every rank runs the full workload on its own GPU (weak scaling, no collective
+on the data path); time is the max over ranks.
+
+One JSON line is printed by rank 0.  ``--impl reference`` times the equivalent
+torch-eager path on the host CPU cores instead (the reference has no CPU
+implementation of its own; its kernels are GPU-only Triton).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CFG3 = dict(B=4, T=4096, H=16, D=128)          # attention
+CFG2 = dict(B=8, T=4096, H=16, D=128, R=64)    # FusedLNRoPE
+METRIC = "attn fwd+bwd TFLOPS (bf16,T=4096,d=128) + norm/RoPE HBM GB/s at 1/2/4/8 B200"
+
+
+def attn_flops(B, T, H, D):
+    fwd = 4.0 * B * H * T * T * D
+    return fwd, 2.5 * fwd
+
+
+def lnrope_bytes(B, T, H, D):
+    per = B * T * H * D * 2            # one bf16 tensor
+    return 4 * per, 6 * per            # fwd: q,k in + out; bwd: q,k,dqo,dko in + dq,dk out
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], d.get("bf16_tflops_sustained", d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.proc.wait(timeout=5)
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = [s for s in sm if s > 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def synth_attn(cfg, device, seed=0):
+    """Seeded N(0,1) bf16 inputs generated on the CPU in fp32, then cast."""
+    g = torch.Generator().manual_seed(seed)
+    shape = (cfg["B"], cfg["T"], cfg["H"], cfg["D"])
+    host = [torch.randn(*shape, generator=g).to(torch.bfloat16).pin_memory() if device != "cpu"
+            else torch.randn(*shape, generator=g).to(torch.bfloat16) for _ in range(4)]
+    return host   # q, k, v, do
+
+
+def rotary_table(P, R, dtype):
+    inv = 1.0 / (10000.0 ** (torch.arange(0, R, 2, dtype=torch.float32) / R))
+    ang = (torch.arange(P, dtype=torch.float32)[:, None] * inv[None, :]).repeat_interleave(2, dim=-1)
+    return torch.stack([ang.sin(), ang.cos()]).to(dtype)
+
+
+# ---------------------------------------------------------------------------
+# CPU side: torch-eager equivalents (baseline / reference arm)
+# ---------------------------------------------------------------------------
+def cpu_attn_step(q, k, v, do):
+    """fwd+bwd of eager attention on the CPU, chunked per batch element."""
+    scale = 1.0 / math.sqrt(q.shape[-1])
+    for b in range(q.shape[0]):
+        qb, kb, vb = (t[b:b + 1].detach().requires_grad_(True) for t in (q, k, v))
+        s = torch.einsum("bthd,bshd->bhts", qb * scale, kb)
+        o = torch.einsum("bhts,bshd->bthd", torch.softmax(s, dim=-1), vb)
+        torch.autograd.grad(o, (qb, kb, vb), do[b:b + 1])
+
+
+def cpu_baseline(cfg, seconds_budget=25.0):
+    """Eager attention fwd+bwd on the host cores for a bounded sample (whole
+    batch elements of the headline workload), reported in the metric's unit."""
+    q, k, v, do = synth_attn(dict(cfg, B=1), "cpu")
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    cpu_attn_step(q, k, v, do)                     # untimed
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        cpu_attn_step(q, k, v, do)
+        reps += 1
+        if time.perf_counter() - t0 > seconds_budget / 2 or reps >= 3:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    f, b = attn_flops(1, cfg["T"], cfg["H"], cfg["D"])
+    return {"value": (f + b) / dt / 1e12, "unit": "TFLOPS", "cores": cores, "kind": "port",
+            "sample": f"1 of {cfg['B']} batch elements (q/k/v [1,{cfg['T']},{cfg['H']},{cfg['D']}] bf16), "
+                      f"torch eager fwd+bwd, {reps} timed repetition(s), {dt:.2f} s each"}
+
+
+def run_reference(args):
+    """Reference arm: the torch-eager path on the host CPU, same workload/metric."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    cfg = CFG3
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    q, k, v, do = synth_attn(dict(cfg, B=1), "cpu")
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_attn_step(q, k, v, do)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_attn_step(q, k, v, do)
+    dt = (time.perf_counter() - t0) / args.steps
+    f, b = attn_flops(1, cfg["T"], cfg["H"], cfg["D"])
+    val = (f + b) / dt / 1e12
+    sample = (f"each step = 1 of {cfg['B']} batch elements of the workload (bounded sample), torch eager fwd+bwd "
+              f"on {cores} host threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "config3 FlashAttention fwd+bwd bf16 q/k/v [4,4096,16,128] no bias non-causal",
+                   "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------------
+# GPU side
+# ---------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    import torch.distributed as dist
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+
+    from rgd_triton_b200 import _lib, ops
+    lib = _lib.load()
+    if lib.rgd_device_supported(local) != 1:
+        raise RuntimeError("bench.py needs a compute-capability-10 GPU (B200)")
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    hbm_peak, tf_burst, tf_sust, peak_src = peaks()
+
+    # ---------------- attention, config 3 ----------------
+    cfg = CFG3
+    hq, hk, hv, hdo = synth_attn(cfg, "cuda")
+    q, k, v, do = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
+    attn = ops.FlashAttention()
+
+    def attn_step(q, k, v, do, ev=None):
+        qi, ki, vi = q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+        if ev:
+            ev[0].record()
+        o = attn(qi, ki, vi)
+        if ev:
+            ev[1].record()
+        grads = torch.autograd.grad(o, (qi, ki, vi), do)
+        if ev:
+            ev[2].record()
+        return o, grads
+
+    for _ in range(args.warmup):
+        attn_step(q, k, v, do)
+    barrier()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    launches0 = lib.rgd_launch_count()
+    with ClockSampler(local) as clk:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for i in range(args.steps):
+            attn_step(q, k, v, do, evs[i])
+        end.record()
+        barrier()
+    launches = lib.rgd_launch_count() - launches0
+    ms_total = max_over_ranks(start.elapsed_time(end))
+    ms_step = ms_total / args.steps
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    f_fwd, f_bwd = attn_flops(**cfg)
+    tflops = world * (f_fwd + f_bwd) / (ms_step * 1e-3) / 1e12
+    clocks = clk.summary()
+    dom = ("attention backward (delta + dK/dV + dQ kernels)", f_bwd, bwd_ms) if bwd_ms >= fwd_ms else \
+          ("attention forward kernel", f_fwd, fwd_ms)
+    achieved = dom[1] / (dom[2] * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": dom[0], "achieved": achieved, "peak": tf_burst, "unit": "TFLOP/s",
+                "frac": achieved / tf_burst, "peak_source": peak_src, "traffic": None,
+                "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+                "fwd_tflops": f_fwd / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": f_bwd / (bwd_ms * 1e-3) / 1e12}
+
+    # ---------------- end to end: host buffers through the module API ----------------
+    ho = torch.empty_like(hq).pin_memory()
+    hgrads = [torch.empty_like(hq).pin_memory() for _ in range(3)]
+
+    def e2e_step():
+        dq_, dk_, dv_, ddo = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
+        o, grads = attn_step(dq_, dk_, dv_, ddo)
+        ho.copy_(o.detach(), non_blocking=True)
+        for h, g_ in zip(hgrads, grads):
+            h.copy_(g_, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2.record()
+    barrier()
+    e2e_ms = max_over_ranks(s2.elapsed_time(e2)) / e2e_steps
+    nbytes = hq.numel() * hq.element_size()
+    e2e = {"value": world * (f_fwd + f_bwd) / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "steps": e2e_steps}
+    del q, k, v, do
+    torch.cuda.empty_cache()
+
+    # ---------------- FusedLNRoPE, config 2 (HBM-bound half of the metric) ----------------
+    c2 = CFG2
+    g = torch.Generator().manual_seed(1)
+    shp = (c2["B"], c2["T"], c2["H"], c2["D"])
+    q2, k2, gq2, gk2 = (torch.randn(*shp, generator=g).to(torch.bfloat16).to(dev) for _ in range(4))
+    pos = rotary_table(c2["T"] + 1, c2["R"], torch.bfloat16).to(dev)
+    lnrope = ops.FusedLNRoPE()
+
+    def lnrope_step(ev=None):
+        qi, ki = q2.requires_grad_(True), k2.requires_grad_(True)
+        if ev:
+            ev[0].record()
+        qo, ko = lnrope(qi, ki, pos, seq_cutoff=(c2["T"], c2["T"]), heads_second=False, eps=1e-5)
+        if ev:
+            ev[1].record()
+        torch.autograd.grad((qo, ko), (qi, ki), (gq2, gk2))
+        if ev:
+            ev[2].record()
+
+    for _ in range(args.warmup):
+        lnrope_step()
+    barrier()
+    evs2 = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    s3, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s3.record()
+    for i in range(args.steps):
+        lnrope_step(evs2[i])
+    e3.record()
+    barrier()
+    ln_ms = max_over_ranks(s3.elapsed_time(e3)) / args.steps
+    b_fwd, b_bwd = lnrope_bytes(c2["B"], c2["T"], c2["H"], c2["D"])
+    ln_fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs2)
+    ln_bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs2)
+    norm_rope = {
+        "workload": "config2 FusedLNRoPE fwd+bwd bf16 q/k [8,4096,16,128] heads_second=False R=64",
+        "value": world * (b_fwd + b_bwd) / (ln_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ln_ms,
+        "roofline": {"bound": "hbm", "peak": hbm_peak, "unit": "GB/s", "peak_source": peak_src,
+                     "fwd_gbs": b_fwd / (ln_fwd_ms * 1e-3) / 1e9, "bwd_gbs": b_bwd / (ln_bwd_ms * 1e-3) / 1e9,
+                     "fwd_frac": b_fwd / (ln_fwd_ms * 1e-3) / 1e9 / hbm_peak,
+                     "bwd_frac": b_bwd / (ln_bwd_ms * 1e-3) / 1e9 / hbm_peak,
+                     "fwd_ms": ln_fwd_ms, "bwd_ms": ln_bwd_ms, "traffic": None},
+        "l2": "working set 1.3 GB per step, larger than the 126 MB L2",
+    }
+    del q2, k2, gq2, gk2
+
+    base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        base = cpu_baseline(cfg)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": tflops, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "config3 FlashAttention fwd+bwd bf16 q/k/v [4,4096,16,128] no bias non-causal, "
+                                   "per GPU", "l2": "inputs+outputs 256 MiB per step, larger than the 126 MB L2",
+                       "parallelism": f"replicas x{world} (batch x heads shard, no collective)"},
+            "roofline": roofline, "norm_rope": norm_rope, "e2e": e2e, "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if base is not None:
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -30,14 +30,14 @@ int check_common(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, con
     if (B * H > 65535 * 32768LL || Tq > (1LL << 30) || Tk > (1LL << 30) || B > INT32_MAX || H > INT32_MAX)
         return RGD_E_SIZE;
     const bool empty = B == 0 || H == 0 || d == 0;
-    if (!empty) {
-        if (Tq > 0 && !q->ptr) return RGD_E_NULL;
-        if (Tk > 0 && (!k->ptr || !v->ptr)) return RGD_E_NULL;
-    }
     if (bias && bias->kind != RGD_BIAS_NONE) {
         if (bias->kind != RGD_BIAS_VECTOR && bias->kind != RGD_BIAS_MATRIX) return RGD_E_BIAS_SHAPE;
         if (bias->dtype != dtype && bias->dtype != RGD_F32) return RGD_E_DTYPE;
         if (!bias->ptr && !empty && Tq > 0 && Tk > 0) return RGD_E_NULL;
+    }
+    if (!empty) {
+        if (Tq > 0 && !q->ptr) return RGD_E_NULL;
+        if (Tk > 0 && (!k->ptr || !v->ptr)) return RGD_E_NULL;
     }
     return RGD_OK;
 }

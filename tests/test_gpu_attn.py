@@ -1,0 +1,215 @@
+"""GPU parity of FlashAttention forward / backward.
+
+Bar (from the reference's own tests, tests/test_flash_attn.py:175-178,
+:307-309): the max-abs error against the exact fp32 evaluation must be at most
+2x the error a low-precision eager implementation makes on the same inputs.
+Shapes follow the reference's grid (d in {32, 64}, odd and unequal lengths)
+and add d in {40, 96, 128}, every bias kind incl. broadcast and fp32 bias,
+causal, non-contiguous inputs and the benchmark configurations' sizes."""
+import math
+
+import pytest
+import torch
+
+from oracle import oracle as O
+from rgd_triton_b200 import functional as F_, ops
+from tests._util import DTYPES, T, assert_attn, attn_error, gen, randn
+
+pytestmark = pytest.mark.gpu
+
+LENS = [(113, 203), (128, 217), (108, 256), (256, 512), (1, 1), (3, 1023), (1023, 1024), (64, 64)]
+
+
+def run_attn(q, k, v, do, bias=None, causal=False, scale=None):
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    bd = bias.cuda() if bias is not None else None
+    o, lse = F_.flash_attn_func(qd, kd, vd, bd, causal, scale, return_lse=True)
+    dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), do.cuda())
+    torch.cuda.synchronize()
+    return o.detach().cpu(), lse.cpu(), dq.cpu(), dk.cpu(), dv.cpu()
+
+
+def check(q, k, v, do, bias=None, causal=False, what=""):
+    o, lse, dq, dk, dv = run_attn(q, k, v, do, bias, causal)
+    eo, elsed = O.attn_fwd(q.float(), k.float(), v.float(), None if bias is None else bias.float(), causal)
+    edq, edk, edv = O.attn_bwd(q.float(), k.float(), v.float(), do.float(), None if bias is None else bias.float(),
+                               causal)
+    lo, ldq, ldk, ldv = O.attn_lowp(q, k, v, do, bias, causal)
+    tq = q.shape[1]
+    torch.testing.assert_close(lse[:, :, :tq], elsed, rtol=1e-3, atol=2e-3, msg=lambda m: f"{what} lse: {m}")
+    assert_attn(o, eo, lo, f"{what} o")
+    # gradients: the reference's tests allow up to 5x here for the hardest shapes
+    assert_attn(dq, edq, ldq, f"{what} dq", factor=2.0, floor=2e-3)
+    assert_attn(dk, edk, ldk, f"{what} dk", factor=2.0, floor=2e-3)
+    assert_attn(dv, edv, ldv, f"{what} dv", factor=2.0, floor=2e-3)
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("d", [32, 64, 128, 40, 96])
+@pytest.mark.parametrize("causal", [False, True])
+def test_no_bias(dt, d, causal):
+    dtype = DTYPES[dt]
+    g = gen(d)
+    for tq, tk in LENS:
+        q, k, v = randn(g, 2, tq, 3, d, dtype=dtype), randn(g, 2, tk, 3, d, dtype=dtype), randn(g, 2, tk, 3, d, dtype=dtype)
+        do = randn(g, 2, tq, 3, d, dtype=dtype)
+        check(q, k, v, do, None, causal, f"d={d} ({tq},{tk}) causal={causal}")
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("kind", ["vector", "matrix", "matrix_bcast_b", "matrix_bcast_h", "vector_bcast", "matrix_f32"])
+def test_bias(dt, d, kind):
+    dtype = DTYPES[dt]
+    g = gen(d + len(kind))
+    B, H = 2, 3
+    for tq, tk in [(113, 203), (128, 217), (256, 512), (3, 1023)]:
+        q, k, v = randn(g, B, tq, H, d, dtype=dtype), randn(g, B, tk, H, d, dtype=dtype), randn(g, B, tk, H, d, dtype=dtype)
+        do = randn(g, B, tq, H, d, dtype=dtype)
+        shape = {"vector": (B, H, 1, tk), "matrix": (B, H, tq, tk), "matrix_bcast_b": (1, H, tq, tk),
+                 "matrix_bcast_h": (B, 1, tq, tk), "vector_bcast": (1, 1, 1, tk), "matrix_f32": (B, H, tq, tk)}[kind]
+        bias = randn(g, *shape, dtype=torch.float32 if kind == "matrix_f32" else dtype)
+        check(q, k, v, do, bias, False, f"{kind} d={d} ({tq},{tk})")
+
+
+def test_block_mask_bias_like_config4():
+    """-1e4 on random 64x64 blocks (diagonal kept), the bias of the fourth
+    benchmark configuration at a size the oracle handles quickly."""
+    g = gen(44)
+    B, H, Tn, d = 1, 2, 512, 64
+    q, k, v, do = (randn(g, B, Tn, H, d, dtype=torch.float16) for _ in range(4))
+    bias = randn(g, B, H, Tn, Tn)
+    blk = (torch.rand(B, H, Tn // 64, Tn // 64, generator=g) < 0.1)
+    blk &= ~torch.eye(Tn // 64, dtype=torch.bool)
+    bias = (bias - 1e4 * blk.repeat_interleave(64, 2).repeat_interleave(64, 3)).to(torch.float16)
+    check(q, k, v, do, bias, False, "block mask")
+    check(q, k, v, do, bias[:1].clone(), False, "block mask broadcast")
+
+
+def test_bias_shape_error_is_runtime_error():
+    q = torch.zeros(1, 8, 2, 64, device="cuda", dtype=torch.float16)
+    with pytest.raises(RuntimeError):
+        F_.flash_attn_func(q, q, q, torch.zeros(1, 2, 4, 8, device="cuda", dtype=torch.float16))
+    with pytest.raises(AssertionError):
+        F_.flash_attn_func(q, q, q, torch.zeros(1, 2, 8, 8, device="cuda", dtype=torch.float64))
+    b = torch.zeros(1, 2, 8, 8, device="cuda", dtype=torch.float16, requires_grad=True)
+    o = F_.flash_attn_func(q.clone().requires_grad_(True), q, q, b)
+    with pytest.raises(AssertionError):
+        o.sum().backward()
+
+
+def test_golden_vectors(golden):
+    """Against outputs of the reference's own kernel (fp16)."""
+    g = golden("attn_f16")
+    q, k, v, do = T(g["q"]), T(g["k"]), T(g["v"]), T(g["do"])
+    for kind in ("none", "matrix", "vector", "causal"):
+        bias = {"none": None, "causal": None, "matrix": T(g["bias_matrix"]), "vector": T(g["bias_vector"])}[kind]
+        o, lse, dq, dk, dv = run_attn(q, k, v, do, bias, kind == "causal")
+        tq = q.shape[1]
+        torch.testing.assert_close(lse[:, :, :tq], T(g[f"lse_{kind}"])[:, :, :tq], rtol=1e-4, atol=1e-4)
+        for got, name in ((o, "o"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+            want = T(g[f"{name}_{kind}"])
+            err = attn_error(got, want)
+            assert err <= 4e-3 * max(want.float().abs().max().item(), 1.0), f"{name}_{kind}: {err}"
+
+
+def test_noncontiguous_inputs_and_grad():
+    """(B,h,T,d) tensors passed as transposed views, and a non-contiguous dO
+    (tests/test_flash_attn.py:463-513)."""
+    g = gen(8)
+    B, H, Tn, d = 2, 3, 200, 64
+    qh, kh, vh = (randn(g, B, H, Tn, d, dtype=torch.bfloat16) for _ in range(3))
+    q, k, v = qh.transpose(1, 2), kh.transpose(1, 2), vh.transpose(1, 2)
+    do = randn(g, B, Tn, d, H, dtype=torch.bfloat16).transpose(2, 3)       # channel stride != 1
+    qd, kd, vd = (t.cuda().transpose(1, 2).requires_grad_(True) for t in (qh, kh, vh))
+    o = F_.flash_attn_func(qd, kd, vd)
+    dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), do.cuda())
+    eo, _ = O.attn_fwd(q.float(), k.float(), v.float())
+    edq, edk, edv = O.attn_bwd(q.float(), k.float(), v.float(), do.float())
+    lo, ldq, ldk, ldv = O.attn_lowp(q, k, v, do)
+    assert_attn(o, eo, lo, "o")
+    assert_attn(dq, edq, ldq, "dq", floor=2e-3)
+    assert_attn(dk, edk, ldk, "dk", floor=2e-3)
+    assert_attn(dv, edv, ldv, "dv", floor=2e-3)
+
+
+def test_backward_overflow_small_seqlens():
+    """Scaled inputs at tiny lengths (tests/test_flash_attn.py:399-451)."""
+    g = gen(9)
+    for tq, tk in [(15, 15), (31, 17), (64, 129)]:
+        q, k, v = (randn(g, 2, n, 4, 64, dtype=torch.float16, scale=5.0) for n in (tq, tk, tk))
+        do = randn(g, 2, tq, 4, 64, dtype=torch.float16)
+        o, lse, dq, dk, dv = run_attn(q, k, v, do)
+        for t in (o, dq, dk, dv):
+            assert torch.isfinite(t.float()).all()
+        edq, edk, edv = O.attn_bwd(q.float(), k.float(), v.float(), do.float())
+        _, ldq, ldk, ldv = O.attn_lowp(q, k, v, do)
+        assert_attn(dq, edq, ldq, "dq", factor=5.0, floor=2e-2)
+        assert_attn(dk, edk, ldk, "dk", factor=5.0, floor=2e-2)
+        assert_attn(dv, edv, ldv, "dv", factor=5.0, floor=2e-2)
+
+
+def test_repeat_runs_are_bit_identical():
+    """tests/test_flash_attn.py:341-388: outputs and dK/dV bit-equal across
+    repeated launches; here dQ as well (no atomics anywhere)."""
+    g = gen(10)
+    q, k, v = (randn(g, 6, n, 5, 64, dtype=torch.bfloat16).cuda() for n in (239, 127, 127))
+    do = randn(g, 6, 239, 5, 64, dtype=torch.bfloat16).cuda()
+    m = ops.FlashAttention()
+    first = None
+    for _ in range(10):
+        qi, ki, vi = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o = m(qi, ki, vi)
+        cur = [o, *torch.autograd.grad(o, (qi, ki, vi), do)]
+        if first is None:
+            first = [t.clone() for t in cur]
+        else:
+            assert all(torch.equal(a, b) for a, b in zip(first, cur))
+    assert m.cache.fwd is not None and m.cache.bwd is not None
+
+
+def _one_head_check(q, k, v, do, bias, b, h, what):
+    """Exact fp32 oracle on one (batch, head) of a large problem."""
+    sl = lambda t: t[b:b + 1, :, h:h + 1]
+    bsl = None if bias is None else bias[(b if bias.shape[0] > 1 else 0):(b if bias.shape[0] > 1 else 0) + 1,
+                                         (h if bias.shape[1] > 1 else 0):(h if bias.shape[1] > 1 else 0) + 1]
+    return sl(q), sl(k), sl(v), sl(do), bsl
+
+
+@pytest.mark.parametrize("cfg", ["config3", "config4"])
+def test_benchmark_configurations_full_size(cfg):
+    """Third / fourth benchmark configurations at full size; the exact oracle
+    is evaluated for two (batch, head) pairs, and linearity in dO is checked
+    on the whole tensor."""
+    g = gen(0)
+    if cfg == "config3":
+        B, Tn, H, d, dtype = 4, 4096, 16, 128, torch.bfloat16
+        bias = None
+    else:
+        B, Tn, H, d, dtype = 2, 4096, 24, 64, torch.float16
+        bias = randn(g, 1, H, Tn, Tn)
+        blk = (torch.rand(1, H, 64, 64, generator=g) < 0.1) & ~torch.eye(64, dtype=torch.bool)
+        bias = (bias - 1e4 * blk.repeat_interleave(64, 2).repeat_interleave(64, 3)).to(dtype)
+    q, k, v, do = (randn(g, B, Tn, H, d, dtype=dtype) for _ in range(4))
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    bd = None if bias is None else bias.cuda()
+    o = F_.flash_attn_func(qd, kd, vd, bd)
+    dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), do.cuda(), retain_graph=True)
+    for b, h in ((0, 0), (B - 1, H - 1)):
+        sq, sk, sv, sdo, sb = _one_head_check(q, k, v, do, bias, b, h, cfg)
+        eo, _ = O.attn_fwd(sq.float(), sk.float(), sv.float(), None if sb is None else sb.float())
+        edq, edk, edv = O.attn_bwd(sq.float(), sk.float(), sv.float(), sdo.float(), None if sb is None else sb.float())
+        lo, ldq, ldk, ldv = O.attn_lowp(sq, sk, sv, sdo, sb)
+        sl = lambda t: t.detach().cpu()[b:b + 1, :, h:h + 1]
+        assert_attn(sl(o), eo, lo, f"{cfg} o[{b},{h}]")
+        assert_attn(sl(dq), edq, ldq, f"{cfg} dq[{b},{h}]", floor=2e-3)
+        assert_attn(sl(dk), edk, ldk, f"{cfg} dk[{b},{h}]", floor=2e-3)
+        assert_attn(sl(dv), edv, ldv, f"{cfg} dv[{b},{h}]", floor=2e-3)
+    # linearity of the backward in dO: scaling dO by a power of two scales every
+    # gradient by it — exactly in bf16; in fp16 up to subnormal rounding of dS
+    dq2, dk2, dv2 = torch.autograd.grad(o, (qd, kd, vd), 2 * do.cuda())
+    for a, b2 in ((dq, dq2), (dk, dk2), (dv, dv2)):
+        if dtype == torch.bfloat16:
+            assert torch.equal((2 * a.float()).to(a.dtype), b2)
+        else:
+            torch.testing.assert_close(2 * a.float(), b2.float(), rtol=2e-3, atol=2e-4)
