@@ -189,6 +189,88 @@ def run_reference(args):
 # ---------------------------------------------------------------------------
 # GPU side
 # ---------------------------------------------------------------------------
+def op_table(dev, steps, hbm_peak):
+    """HBM GB/s of every norm / RoPE operator, forward and backward timed
+    separately with CUDA events, at the benchmark configurations' shapes.
+    L2 is flushed before every timed launch: a 512 MiB fill evicts the
+    operator's tensors, then a 256 MiB read-only pass pushes the fill's dirty
+    lines out so their write-back does not compete with the timed kernel.  The
+    flush also keeps the GPU busy while the host enqueues the operator, so the
+    events bracket kernel time and not launch latency."""
+    from rgd_triton_b200 import ops
+    bf = torch.bfloat16
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    clean = torch.zeros(64 << 20, dtype=torch.float32, device=dev)     # 256 MiB, only ever read
+    g = torch.Generator().manual_seed(2)
+
+    def rn(*shape, dtype=bf):
+        return torch.randn(*shape, generator=g).to(dtype).to(dev)
+
+    def nbytes(*ts):
+        return sum(t.numel() * t.element_size() for t in ts)
+
+    def timed(run):
+        ts = []
+        for _ in range(steps + 2):
+            flush.fill_(1)          # evicts the operator's tensors from L2 ...
+            clean.sum()             # ... and a read pass drains the fill's dirty lines before the timed launch
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            run()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts[2:])
+
+    def case(name, fwd, inputs, grads_of, upstream, extra_bwd_bytes=0):
+        ins = [t.requires_grad_(True) for t in inputs]
+        outs = fwd(*ins)
+        outs = outs if isinstance(outs, tuple) else (outs,)
+        fwd_b = nbytes(*inputs) + nbytes(*outs)
+        bwd_b = nbytes(*inputs) + nbytes(*upstream) + nbytes(*inputs) + extra_bwd_bytes
+        with torch.no_grad():
+            t_f = timed(lambda: fwd(*ins))
+        wrt = ins + grads_of
+        t_b = timed(lambda: torch.autograd.grad(outs, wrt, upstream, retain_graph=True))
+        return {"op": name, "fwd_bytes": fwd_b, "bwd_bytes": bwd_b, "fwd_ms": t_f, "bwd_ms": t_b,
+                "fwd_gbs": fwd_b / t_f / 1e6, "bwd_gbs": bwd_b / t_b / 1e6,
+                "fwd_frac": fwd_b / t_f / 1e6 / hbm_peak, "bwd_frac": bwd_b / t_b / 1e6 / hbm_peak}
+
+    rows = []
+    # config 1: FusedRMSNorm fp32 [4,256,1024]
+    m = ops.FusedRMSNorm(1024).to(dev)
+    rows.append(case("FusedRMSNorm f32 [4,256,1024] (config1)", m, [rn(4, 256, 1024, dtype=torch.float32)],
+                     [m.weight], [rn(4, 256, 1024, dtype=torch.float32)]))
+    # config 2: FusedLNRoPE bf16 [8,4096,16,128]
+    pos = rotary_table(4097, 64, bf).to(dev)
+    f = ops.FusedLNRoPE()
+    rows.append(case("FusedLNRoPE bf16 q,k [8,4096,16,128] (config2)",
+                     lambda a, b: f(a, b, pos, (4096, 4096), False, 1e-5),
+                     [rn(8, 4096, 16, 128), rn(8, 4096, 16, 128)], [], [rn(8, 4096, 16, 128), rn(8, 4096, 16, 128)]))
+    # config 5, per GPU (batch 2)
+    m2 = ops.FusedRMSNorm2((3072, 3072), dtype=bf).to(dev)
+    rows.append(case("FusedRMSNorm2 bf16 [2,512,3072]+[2,4096,3072] (config5)", m2,
+                     [rn(2, 512, 3072), rn(2, 4096, 3072)], [m2.weight1, m2.weight2],
+                     [rn(2, 512, 3072), rn(2, 4096, 3072)]))
+    pos5 = rotary_table(4609, 64, bf).to(dev)
+    hl, rp, l2, l22 = ops.FusedHeadLayerNorm(), ops.RoPE(), ops.L2Normalize(), ops.FusedL2Normalize2()
+    qk = lambda: [rn(2, 4608, 24, 128), rn(2, 4608, 24, 128)]
+    rows.append(case("FusedHeadLayerNorm bf16 q,k [2,4608,24,128] (config5)",
+                     lambda a, b: hl(a, b, False, 1e-6), qk(), [], qk()))
+    r = case("RoPE bf16 q,k [2,4608,24,128] R=64 cutoff 4096 (config5)",
+             lambda a, b: rp(a, b, pos5, 4096, False), qk(), [], qk())
+    r["bwd_bytes"] = r["fwd_bytes"]          # the backward reads only the upstream gradients
+    r["bwd_gbs"] = r["bwd_bytes"] / r["bwd_ms"] / 1e6
+    r["bwd_frac"] = r["bwd_gbs"] / hbm_peak
+    rows.append(r)
+    rows.append(case("L2Normalize bf16 [2,4096,3072]", lambda a: l2(a), [rn(2, 4096, 3072)], [],
+                     [rn(2, 4096, 3072)]))
+    rows.append(case("FusedL2Normalize2 bf16 [2,512,3072]+[2,4096,3072]", lambda a, b: l22(a, b),
+                     [rn(2, 512, 3072), rn(2, 4096, 3072)], [], [rn(2, 512, 3072), rn(2, 4096, 3072)]))
+    del flush, clean
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -196,6 +278,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ops-only", action="store_true", help="only the per-operator norm / RoPE table")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -232,6 +315,11 @@ def main():
         return t.item()
 
     hbm_peak, tf_burst, tf_sust, peak_src = peaks()
+    if args.ops_only:
+        rows = op_table(dev, args.steps, hbm_peak)
+        if rank == 0:
+            print(json.dumps({"ops": rows, "hbm_peak_gbs": hbm_peak, "peak_source": peak_src}), flush=True)
+        return 0
 
     # ---------------- attention, config 3 ----------------
     cfg = CFG3
@@ -352,6 +440,7 @@ def main():
         "l2": "working set 1.3 GB per step, larger than the 126 MB L2",
     }
     del q2, k2, gq2, gk2
+    norm_rope["ops"] = op_table(dev, min(args.steps, 10), hbm_peak)
 
     base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

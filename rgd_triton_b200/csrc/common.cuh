@@ -68,6 +68,28 @@ __device__ __forceinline__ void st_stream16(void *p, const uint4 &v) {
                  : "memory");
 }
 
+// Vector accesses with the evict-first hint when the vector is 16 bytes wide.
+template <typename T, int N>
+__device__ __forceinline__ Vec<T, N> load_vec_stream(const T *p) {
+    if constexpr (sizeof(T) * N == 16) {
+        union { uint4 u; Vec<T, N> v; } c;
+        c.u = ld_stream16(p);
+        return c.v;
+    } else {
+        return load_vec<T, N>(p);
+    }
+}
+template <typename T, int N>
+__device__ __forceinline__ void store_vec_stream(T *p, const Vec<T, N> &v) {
+    if constexpr (sizeof(T) * N == 16) {
+        union { uint4 u; Vec<T, N> v; } c;
+        c.v = v;
+        st_stream16(p, c.u);
+    } else {
+        store_vec<T, N>(p, v);
+    }
+}
+
 // Elements of T per 16-byte access.
 template <typename T> struct VecElems { static constexpr int value = 16 / sizeof(T); };
 

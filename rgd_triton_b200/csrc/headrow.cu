@@ -68,7 +68,7 @@ __device__ __forceinline__ void load_table(const TP *row, int col, int R, bool v
 // T: tensor element type.  TP: table element type (T or float).  VE: elements
 // per access (16 / sizeof(T), or 1).  VPT: column slots per thread.
 template <typename T, typename TP, int VE, int VPT, int OP>
-__global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constant__ HeadParams p) {
+__global__ void __launch_bounds__(HEAD_THREADS, (OP == LN_BWD || OP == LNROPE_BWD) ? 3 : 4) head_kernel(const __grid_constant__ HeadParams p) {
     constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
     constexpr bool HAS_ROPE = (OP == ROPE || OP == LNROPE_FWD || OP == LNROPE_BWD);
     constexpr bool HAS_LN = (OP != ROPE);
@@ -91,8 +91,10 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constan
     const bool pos_vec_ok = (reinterpret_cast<uintptr_t>(p.pos) % 16 == 0) &&
                             (p.pos_ss % (16 / (int)sizeof(TP)) == 0) && (p.pos_sn % (16 / (int)sizeof(TP)) == 0);
 
-    float xv[ROWS_PER_THREAD][NE];
-    float dv[ROWS_PER_THREAD][HAS_DY ? NE : 1];
+    // Loaded rows stay packed (16 bytes per slot) until their turn to be
+    // processed: that keeps the register count low enough for 4 CTAs per SM.
+    V xq[ROWS_PER_THREAD][VPT];
+    V gq[HAS_DY ? ROWS_PER_THREAD : 1][VPT];
     int64_t ooff[ROWS_PER_THREAD];
     int tok[ROWS_PER_THREAD];
     bool valid[ROWS_PER_THREAD];
@@ -127,19 +129,13 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constan
         for (int j = 0; j < VPT; ++j) {
             const int col = (t + j * tpr) * VE;
             if (valid[r] && col < d) {
-                V a = load_vec<T, VE>(xr + col);
-#pragma unroll
-                for (int e = 0; e < VE; ++e) xv[r][j * VE + e] = to_f32<T>(a.v[e]);
-                if constexpr (HAS_DY) {
-                    V g = load_vec<T, VE>(dr + col);
-#pragma unroll
-                    for (int e = 0; e < VE; ++e) dv[r][j * VE + e] = to_f32<T>(g.v[e]);
-                }
+                xq[r][j] = load_vec_stream<T, VE>(xr + col);
+                if constexpr (HAS_DY) gq[r][j] = load_vec_stream<T, VE>(dr + col);
             } else {
 #pragma unroll
                 for (int e = 0; e < VE; ++e) {
-                    xv[r][j * VE + e] = 0.f;
-                    if constexpr (HAS_DY) dv[r][j * VE + e] = 0.f;
+                    xq[r][j].v[e] = from_f32<T>(0.f);
+                    if constexpr (HAS_DY) gq[r][j].v[e] = from_f32<T>(0.f);
                 }
             }
         }
@@ -148,12 +144,21 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constan
     // ---- per row -------------------------------------------------------------
 #pragma unroll
     for (int r = 0; r < ROWS_PER_THREAD; ++r) {
+        float xv[NE];
+        float dv[HAS_DY ? NE : 1];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+#pragma unroll
+            for (int e = 0; e < VE; ++e) {
+                xv[j * VE + e] = to_f32<T>(xq[r][j].v[e]);
+                if constexpr (HAS_DY) dv[j * VE + e] = to_f32<T>(gq[r][j].v[e]);
+            }
         float mean = 0.f, rstd = 1.f;
         if (HAS_LN) {
             // head_layernorm_cached.py:85-99 / fused_ln_rope_cached.py:66-74
             float s = 0.f;
 #pragma unroll
-            for (int i = 0; i < NE; ++i) s += xv[r][i];
+            for (int i = 0; i < NE; ++i) s += xv[i];
             mean = warp_group_sum(s, tpr) * invd;
             float s2 = 0.f;
 #pragma unroll
@@ -161,13 +166,13 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constan
 #pragma unroll
                 for (int e = 0; e < VE; ++e) {
                     const int col = (t + j * tpr) * VE + e;
-                    const float c = col < d ? xv[r][j * VE + e] - mean : 0.f;
-                    xv[r][j * VE + e] = c;           // centred
+                    const float c = col < d ? xv[j * VE + e] - mean : 0.f;
+                    xv[j * VE + e] = c;           // centred
                     s2 += c * c;
                 }
             rstd = rsqrtf(warp_group_sum(s2, tpr) * invd + p.eps);
 #pragma unroll
-            for (int i = 0; i < NE; ++i) xv[r][i] *= rstd;   // xhat
+            for (int i = 0; i < NE; ++i) xv[i] *= rstd;   // xhat
         }
 
         const bool rot_row = HAS_ROPE && tok[r] < ht.cut;
@@ -181,16 +186,16 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constan
 #pragma unroll
             for (int j = 0; j < NE; ++j) {
                 float mine;
-                if constexpr (OP == LNROPE_BWD) mine = dv[r][j]; else mine = xv[r][j];
+                if constexpr (OP == LNROPE_BWD) mine = dv[j]; else mine = xv[j];
                 oth[j] = __shfl_xor_sync(0xffffffffu, mine, 1);
             }
         }
 
         if constexpr (OP == LN_FWD) {
 #pragma unroll
-            for (int i = 0; i < NE; ++i) res[i] = xv[r][i];
+            for (int i = 0; i < NE; ++i) res[i] = xv[i];
         } else if constexpr (OP == LN_BWD || OP == LNROPE_BWD) {
-            float *g = dv[r];
+            float *g = dv;
             if constexpr (OP == LNROPE_BWD) {
                 if (rot_row) {
                     // Inverse rotation of the upstream gradient (fused_ln_rope_cached.py:349-360).
@@ -222,17 +227,17 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constan
             float sa = 0.f, sb = 0.f;
 #pragma unroll
             for (int i = 0; i < NE; ++i) {
-                sa += xv[r][i] * g[i];
+                sa += xv[i] * g[i];
                 sb += g[i];
             }
             const float a = warp_group_sum(sa, tpr) * invd;
             const float bm = warp_group_sum(sb, tpr) * invd;
 #pragma unroll
-            for (int i = 0; i < NE; ++i) res[i] = (g[i] - xv[r][i] * a - bm) * rstd;
+            for (int i = 0; i < NE; ++i) res[i] = (g[i] - xv[i] * a - bm) * rstd;
         } else {
             // ROPE or LNROPE_FWD: rotate xv (raw x, or xhat).
 #pragma unroll
-            for (int i = 0; i < NE; ++i) res[i] = xv[r][i];
+            for (int i = 0; i < NE; ++i) res[i] = xv[i];
             if (rot_row) {
                 const TP *srow = reinterpret_cast<const TP *>(p.pos) + (int64_t)tok[r] * p.pos_sn;
                 const TP *crow = srow + p.pos_ss;
@@ -247,7 +252,7 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constan
                         if constexpr (VE > 1) {
 #pragma unroll
                             for (int e = 0; e < VE; e += 2) {
-                                const float xe = xv[r][j * VE + e], xo = xv[r][j * VE + e + 1];
+                                const float xe = xv[j * VE + e], xo = xv[j * VE + e + 1];
                                 // rotated partner: (-x_odd, x_even), sign flipped for the inverse
                                 const float re = inv ? xo : -xo;
                                 const float ro = inv ? -xe : xe;
@@ -263,7 +268,7 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constan
                                 if (col + e + 1 < p.R) res[j * VE + e + 1] = oo;
                             }
                         } else {
-                            const float me = xv[r][j];
+                            const float me = xv[j];
                             float rot = (col & 1) ? oth[j] : -oth[j];
                             if (inv) rot = -rot;
                             if constexpr (ROUND_EACH)
@@ -285,7 +290,7 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constan
                     V o;
 #pragma unroll
                     for (int e = 0; e < VE; ++e) o.v[e] = from_f32<T>(res[j * VE + e]);
-                    store_vec<T, VE>(orow + col, o);
+                    store_vec_stream<T, VE>(orow + col, o);
                 }
             }
         }

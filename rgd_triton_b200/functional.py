@@ -52,7 +52,14 @@ def _require(cond: bool, msg: str = "") -> None:
 
 
 def _last_contig(t: torch.Tensor) -> torch.Tensor:
-    return t if t.stride(-1) == 1 else t.contiguous()
+    """The kernels need a unit channel stride; anything else is copied, as in
+    the reference.  Empty and single-channel tensors may report any stride."""
+    if t.stride(-1) == 1:
+        return t
+    t = t.contiguous()
+    if t.stride(-1) != 1:              # numel == 0 or a size-1 last dimension
+        t = t.new_empty(t.shape).copy_(t)
+    return t
 
 
 def _i64(*vals) -> C.Array:
@@ -80,7 +87,8 @@ def _check_rows(xs, what: str) -> None:
     for x in xs:
         _require(x.ndim == 3, f"{what}: expected [B, N, C] tensors, got {tuple(x.shape)}")
         _require(x.dtype in _FLOATS, "Only support fp16, bf16, and fp32")
-        _require(x.stride(-1) == 1, f"{what}: last dimension must be contiguous")
+        _require(x.stride(-1) == 1 or x.numel() == 0 or x.shape[-1] == 1,
+                 f"{what}: last dimension must be contiguous")
         _lib.require_device(x)
     _require(all(x.dtype == xs[0].dtype for x in xs), "All tensors must have the same type")
     _require(all(x.shape[0] == xs[0].shape[0] for x in xs), f"{what}: batch sizes differ")
@@ -333,7 +341,8 @@ def _check_heads(ts, what: str, dmax: int) -> None:
     for t in ts:
         _require(t.ndim == 4, f"{what}: expected 4-D tensors, got {tuple(t.shape)}")
         _require(t.dtype in _FLOATS, "Only support fp16, bf16, and fp32")
-        _require(t.stride(-1) == 1, f"{what}: last dimension must be contiguous")
+        _require(t.stride(-1) == 1 or t.numel() == 0 or t.shape[-1] == 1,
+                 f"{what}: last dimension must be contiguous")
         _lib.require_device(t)
     _require(all(t.dtype == ts[0].dtype for t in ts), "All tensors must have the same type")
     _require(ts[0].shape[-1] <= dmax, f"Only supports head dimensions up to {dmax}")

@@ -121,12 +121,14 @@ def test_strided_and_noncontiguous_inputs():
     falls back to .contiguous() like the reference (rmsnorm_cached.py:578)."""
     g = gen(5)
     base = randn(g, 2, 40, 2 * 96)
-    x = base[:, ::2, :96]                     # strided rows, offset-free, channel stride 1
-    xt = randn(g, 2, 96, 20).transpose(1, 2)  # channel stride != 1
+    base_t = randn(g, 2, 96, 20)
     w = 1 + 0.02 * torch.randn(96, generator=g)
-    for inp in (x, xt):
+    views = (lambda t: t[:, ::2, :96],        # strided rows, channel stride 1
+             lambda t: t.transpose(1, 2))     # channel stride != 1
+    for view, host in zip(views, (base, base_t)):
+        inp = view(host)
         dy = randn(g, *inp.shape)
-        dev = inp.cuda()
+        dev = view(host.cuda())
         assert dev.stride() == inp.stride()
         xin = dev.detach().requires_grad_(True)
         y = F_.triton_rms_func_fn(xin, w.cuda(), 1e-6)
