@@ -74,6 +74,11 @@ const char *rgd_status_string(int status);
 int         rgd_abi_version(void);
 /* Number of kernels this library has launched in the calling process. */
 int64_t     rgd_launch_count(void);
+/* Sticky status of the tensor-memory kernels' bounded device-side waits:
+ * RGD_OK, or RGD_E_TIMEOUT if a wait ran out since the last call (the flag is
+ * cleared by the call).  Synchronises the device; meant for tests, smoke
+ * checks and debugging, not for the per-step path. */
+int         rgd_device_status(void);
 
 /* ---- row L2 normalise: y = x / max(||x||, eps) ------------------------- */
 /* Replaces _norm_fwd / _fused_norm_fwd (l2normalize_cached.py:237-318,

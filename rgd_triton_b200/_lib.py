@@ -52,6 +52,7 @@ SIGNATURES = {
     "rgd_status_string": (C.c_char_p, [_i32]),
     "rgd_abi_version": (_i32, []),
     "rgd_launch_count": (_i64, []),
+    "rgd_device_status": (_i32, []),
     "rgd_l2norm_fwd": (_i32, [_i32, _pRows, _pRows, _pi64, _pi64, _i64, _f32, _i32, _vp]),
     "rgd_l2norm_bwd": (_i32, [_i32, _pRows, _pRows, _pRows, _pi64, _pi64, _i64, _f32, _i32, _vp]),
     "rgd_rmsnorm_fwd": (_i32, [_i32, _pRows, _pvp, _pi64, _pRows, _pi64, _pi64, _i64, _f32, _i32, _i32, _vp]),

@@ -7,6 +7,9 @@ namespace rgd {
 namespace attn {
 int general_fwd(const AttnParams &p, int dtype, cudaStream_t st);
 int general_bwd(const AttnParams &p, int dtype, cudaStream_t st);
+bool tmem_fwd_eligible(const AttnParams &p);
+int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st);
+int tmem_status_fetch();
 }  // namespace attn
 }  // namespace rgd
 
@@ -70,7 +73,17 @@ void fill_common(AttnParams &p, const rgd_heads *q, const rgd_heads *k, const rg
 
 extern "C" int64_t rgd_attn_lse_rows(int64_t Tq) { return Tq < 0 ? RGD_E_INVALID : lse_rows(Tq); }
 
-extern "C" int rgd_attn_uses_tmem(int64_t, int64_t, int64_t, int, int64_t, int64_t) { return 0; }
+extern "C" int rgd_attn_uses_tmem(int64_t Tq, int64_t Tk, int64_t d, int dtype, int64_t q_stride_n,
+                                  int64_t k_stride_n) {
+    return (d == 64 || d == 128) && Tq >= 1 && Tk >= 1 && (dtype == RGD_F16 || dtype == RGD_BF16) &&
+           q_stride_n % 8 == 0 && k_stride_n % 8 == 0;
+}
+
+extern "C" int rgd_device_status(void) {
+    const int v = attn::tmem_status_fetch();
+    if (v < 0) return RGD_E_CUDA_BASE;
+    return v == 0 ? RGD_OK : RGD_E_TIMEOUT;
+}
 
 extern "C" int rgd_attn_fwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
                             const rgd_heads *o, float *lse, int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d,
@@ -84,6 +97,7 @@ extern "C" int rgd_attn_fwd(const rgd_heads *q, const rgd_heads *k, const rgd_he
     p.out_o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_sn = o->stride_n;
     p.vec_o = d % 8 == 0 && heads_vec16(o);
     p.lse = lse;
+    if (work && attn::tmem_fwd_eligible(p)) return attn::tmem_fwd(p, dtype, (cudaStream_t)stream);
     return attn::general_fwd(p, dtype, (cudaStream_t)stream);
 }
 

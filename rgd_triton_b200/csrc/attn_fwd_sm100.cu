@@ -1,0 +1,411 @@
+// FlashAttention forward on Blackwell tensor memory (tcgen05 + TMEM + TMA).
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the keys in
+// blocks of 128.  Warp roles:
+//   warps 0-3  softmax: thread r owns query row r (TMEM lane r) — row maximum
+//              and row sum need no shuffles; writes P back to tensor memory
+//              as packed 16-bit pairs over the S columns it has consumed
+//   warp 4     TMA producer: Q once, then K and V tiles (128-byte swizzle)
+//   warp 5     MMA issuer: S = Q K^T (operands in shared memory), then
+//              O += P V with P read straight from tensor memory
+// Tensor memory: S/P in columns [0,128), the O accumulator in [128,128+D).
+// 256 columns and at most 96 KB of shared memory per CTA let two CTAs share an
+// SM, so one CTA's softmax overlaps the other's MMAs.
+//
+// Online softmax runs in the base-2 domain with a lazily updated reference
+// maximum: the accumulator is only rescaled when the running maximum grows by
+// more than 2^8, which keeps P <= 256 (exact in fp32, safe in 16 bits) and
+// makes rescaling rare.  The result equals softmax(QK^T*scale + bias) V for any
+// choice of reference, so this matches flash_attn_triton_cached.py:143-220 up
+// to rounding.  Every mbarrier wait is bounded; a wait that runs out flags the
+// status word, all roles drain, tensor memory is released and the host reports
+// RGD_E_TIMEOUT.
+#include <math.h>
+
+#include "attn_mma.cuh"
+#include "sm100_prims.cuh"
+
+namespace rgd {
+namespace attn {
+
+using namespace rgd::sm100;
+
+__device__ int g_tmem_status;
+
+constexpr int FWD_THREADS = 192;
+constexpr int TM = 128;   // query rows per CTA
+constexpr int TN = 128;   // keys per block
+constexpr float RESCALE_THRESHOLD = 8.0f;
+
+struct FwdTmaParams {
+    CUtensorMap mq, mk, mv;
+    void *o;
+    int64_t o_sb, o_sh, o_sn;
+    const void *bias;
+    int64_t b_sb, b_sh, b_sq;
+    int bias_kind, bias_f32, bias_vec;
+    float *lse;
+    int H, Tq, Tk, Tq_rounded, causal;
+    float scale_log2;   // softmax_scale * log2(e)
+};
+
+template <int D, int STAGES>
+struct alignas(1024) FwdTmaSmem {
+    unsigned char q[TM * D * 2];
+    unsigned char k[STAGES][TN * D * 2];
+    unsigned char v[STAGES][TN * D * 2];
+    uint64_t q_full, s_full, p_full, o_full;
+    uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    uint32_t tmem_base;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float a, float b) {
+    if (BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    } else {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+}
+
+// 32 bias values (already multiplied by log2 e) for `row`, columns [col0, col0+32).
+template <bool BF16>
+__device__ __forceinline__ void load_bias32(const FwdTmaParams &p, const char *bias_bh, int row, int col0, float (&b)[32]) {
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    const int64_t off = (p.bias_kind == RGD_BIAS_MATRIX ? (int64_t)row * p.b_sq : 0) + col0;
+    const bool full = col0 + 32 <= p.Tk;
+    if (p.bias_f32) {
+        const float *src = reinterpret_cast<const float *>(bias_bh) + off;
+        if (full && p.bias_vec) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float4 v = reinterpret_cast<const float4 *>(src)[i];
+                b[4 * i] = v.x * LOG2E; b[4 * i + 1] = v.y * LOG2E; b[4 * i + 2] = v.z * LOG2E; b[4 * i + 3] = v.w * LOG2E;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) b[i] = (col0 + i < p.Tk) ? src[i] * LOG2E : 0.f;
+        }
+    } else {
+        const T *src = reinterpret_cast<const T *>(bias_bh) + off;
+        if (full && p.bias_vec) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const Vec<T, 8> v = load_vec<T, 8>(src + 8 * i);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) b[8 * i + e] = to_f32<T>(v.v[e]) * LOG2E;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) b[i] = (col0 + i < p.Tk) ? to_f32<T>(src[i]) * LOG2E : 0.f;
+        }
+    }
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(FWD_THREADS, 2) attn_fwd_tmem(const __grid_constant__ FwdTmaParams p) {
+    constexpr int STAGES = (D == 64) ? 2 : 1;
+    constexpr int HALVES = D / 64;                 // 64-channel (128-byte) swizzle panels per tile
+    constexpr uint32_t PANEL = 128 * 64 * 2;       // bytes of one 128-row panel
+    constexpr uint32_t TILE_BYTES = TM * D * 2;
+    constexpr uint32_t TMEM_COLS = 256;
+    constexpr uint32_t O_COL = 128;
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+
+    extern __shared__ unsigned char smem_raw[];
+    FwdTmaSmem<D, STAGES> &sm =
+        *reinterpret_cast<FwdTmaSmem<D, STAGES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mblk = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;   // heavy causal tiles first
+    const int bh = blockIdx.y;
+    const int b = bh / p.H, h = bh - b * p.H;
+    const int m0 = mblk * TM;
+    const int n_end = p.causal ? min(p.Tk, m0 + TM) : p.Tk;
+    const int nblk = (n_end + TN - 1) / TN;
+    int *status = &g_tmem_status;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.p_full, 128);
+        mbar_init(&sm.o_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&sm.tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tbase = sm.tmem_base;
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&p.mq);
+            tma_prefetch_desc(&p.mk);
+            tma_prefetch_desc(&p.mv);
+            mbar_expect_tx(&sm.q_full, TILE_BYTES);
+            for (int hh = 0; hh < HALVES; ++hh) tma_load_4d(sm.q + hh * PANEL, &p.mq, &sm.q_full, hh * 64, m0, h, b);
+            bool ok = true;
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int s = j % STAGES;
+                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
+                ok = mbar_wait(&sm.k_empty[s], ph ^ 1u, status, 11);
+                if (!ok) break;
+                mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
+                for (int hh = 0; hh < HALVES; ++hh)
+                    tma_load_4d(sm.k[s] + hh * PANEL, &p.mk, &sm.k_full[s], hh * 64, j * TN, h, b);
+                ok = mbar_wait(&sm.v_empty[s], ph ^ 1u, status, 12);
+                if (!ok) break;
+                mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
+                for (int hh = 0; hh < HALVES; ++hh)
+                    tma_load_4d(sm.v[s] + hh * PANEL, &p.mv, &sm.v_full[s], hh * 64, j * TN, h, b);
+            }
+            if (!ok) {
+                // Give copies already in flight time to land before the CTA goes away.
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = make_idesc(BF16, TM, TN, false, false);
+            constexpr uint32_t idesc_pv = make_idesc(BF16, TM, D, false, true);
+            bool ok = mbar_wait(&sm.q_full, 0, status, 21);
+            const uint32_t q_addr = smem_u32(sm.q);
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int s = j % STAGES;
+                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
+                ok = mbar_wait(&sm.k_full[s], ph, status, 22);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t k_addr = smem_u32(sm.k[s]);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * PANEL + (kk % 4) * 32;
+                    umma_ss(tbase, make_sdesc(q_addr + off, 16, 1024), make_sdesc(k_addr + off, 16, 1024), idesc_qk,
+                            kk > 0);
+                }
+                umma_commit(&sm.k_empty[s]);
+                umma_commit(&sm.s_full);
+                ok = mbar_wait(&sm.p_full, (uint32_t)j & 1u, status, 23);
+                if (!ok) break;
+                ok = mbar_wait(&sm.v_full[s], ph, status, 24);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t v_addr = smem_u32(sm.v[s]);
+#pragma unroll
+                for (int kk = 0; kk < TN / 16; ++kk)
+                    umma_ts(tbase + O_COL, tbase + kk * 8, make_sdesc(v_addr + kk * 2048, PANEL, 1024), idesc_pv,
+                            j > 0 || kk > 0);
+                umma_commit(&sm.v_empty[s]);
+            }
+            umma_commit(&sm.o_full);
+        }
+    } else {
+        // ------------------------------ softmax + epilogue ------------------------------
+        const int row_l = warp * 32 + lane;          // row inside the tile == TMEM lane
+        const int row = m0 + row_l;
+        const uint32_t lane_base = tbase + ((uint32_t)(warp * 32) << 16);
+        const char *bias_bh = nullptr;
+        if (p.bias_kind != RGD_BIAS_NONE)
+            bias_bh = reinterpret_cast<const char *>(p.bias) +
+                      ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
+        const int brow = row < p.Tq ? row : (p.Tq - 1);     // rows past the end read a valid bias row
+
+        float m_ref = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nblk; ++j) {
+            ok = mbar_wait(&sm.s_full, (uint32_t)j & 1u, status, 31);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int n0 = j * TN;
+            const bool need_mask = (n0 + TN > p.Tk) || (p.causal && n0 + TN > m0);
+
+            // pass 1: block maximum of x = s * scale * log2e + bias * log2e
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(lane_base + c * 32, r);
+                float bb[32];
+                if (bias_bh != nullptr) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 32, bb);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x = __uint_as_float(r[i]) * p.scale_log2;
+                    if (bias_bh != nullptr) x += bb[i];
+                    if (need_mask) {
+                        const int col = n0 + c * 32 + i;
+                        if (col >= p.Tk || (p.causal && col > row)) x = -INFINITY;
+                    }
+                    mx = fmaxf(mx, x);
+                }
+            }
+            // lazy reference update (warp-uniform decision: TMEM accesses are warp-collective)
+            const bool want = (mx > m_ref + RESCALE_THRESHOLD) || (m_ref == -INFINITY && mx > -INFINITY);
+            if (__any_sync(0xffffffffu, want)) {
+                // lanes that keep their reference scale by exactly 1
+                const float alpha = !want ? 1.f : (m_ref == -INFINITY ? 0.f : ex2(m_ref - mx));
+                l_sum *= alpha;
+                if (want) m_ref = mx;
+                if (j > 0) {
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(lane_base + O_COL + c * 32, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st32(lane_base + O_COL + c * 32, r);
+                    }
+                }
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+
+            // pass 2: P = 2^(x - m), row sum, packed 16-bit P over the consumed S columns
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(lane_base + c * 32, r);
+                float bb[32];
+                if (bias_bh != nullptr) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 32, bb);
+                tmem_wait_ld();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0 = __uint_as_float(r[i]) * p.scale_log2, x1 = __uint_as_float(r[i + 1]) * p.scale_log2;
+                    if (bias_bh != nullptr) {
+                        x0 += bb[i];
+                        x1 += bb[i + 1];
+                    }
+                    if (need_mask) {
+                        const int col = n0 + c * 32 + i;
+                        if (col >= p.Tk || (p.causal && col > row)) x0 = -INFINITY;
+                        if (col + 1 >= p.Tk || (p.causal && col + 1 > row)) x1 = -INFINITY;
+                    }
+                    const float p0 = ex2(x0 - m_use), p1 = ex2(x1 - m_use);
+                    l_sum += p0 + p1;
+                    pk[i >> 1] = pack16<BF16>(p0, p1);
+                }
+                tmem_st16(lane_base + c * 16, pk);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.p_full);
+        }
+
+        // epilogue: O / l, LSE
+        if (ok) ok = mbar_wait(&sm.o_full, 0, status, 32);
+        tc_fence_after_sync();
+        const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+        if (ok) {
+            T *orow = reinterpret_cast<T *>(p.o) + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)row * p.o_sn;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                if (nblk > 0) {
+                    tmem_ld32(lane_base + O_COL + c * 32, r);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = 0u;
+                }
+                if (row < p.Tq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack16<BF16>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        v.y = pack16<BF16>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        v.z = pack16<BF16>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        v.w = pack16<BF16>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        *reinterpret_cast<uint4 *>(orow + c * 32 + i) = v;
+                    }
+                }
+            }
+            if (row < p.Tq_rounded) {
+                const float lse = l_sum > 0.f ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
+                p.lse[(int64_t)bh * p.Tq_rounded + row] = row < p.Tq ? lse : INFINITY;
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tbase, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Host
+// ---------------------------------------------------------------------------
+bool tmem_fwd_eligible(const AttnParams &p) {
+    return (p.d == 64 || p.d == 128) && p.Tq >= 1 && p.Tk >= 1 && p.vec_q && p.vec_k && p.vec_v && p.vec_o;
+}
+
+template <int D, bool BF16>
+static int launch_fwd_tmem(const FwdTmaParams &fp, int nq_tiles, int BH, cudaStream_t st) {
+    constexpr int STAGES = (D == 64) ? 2 : 1;
+    const size_t smem = sizeof(FwdTmaSmem<D, STAGES>) + 1024;
+    if (int e = cuda_status(cudaFuncSetAttribute(attn_fwd_tmem<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem)))
+        return e;
+    dim3 grid(nq_tiles, BH);
+    attn_fwd_tmem<D, BF16><<<grid, FWD_THREADS, smem, st>>>(fp);
+    count_launch();
+    return check_launch();
+}
+
+int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
+    FwdTmaParams fp{};
+    const bool bf16 = dtype == RGD_BF16;
+    if (int e = encode_heads_map(&fp.mq, p.q, p.B, p.H, p.Tq, p.d, p.q_sb, p.q_sh, p.q_sn, 64, TM, bf16)) return e;
+    if (int e = encode_heads_map(&fp.mk, p.k, p.B, p.H, p.Tk, p.d, p.k_sb, p.k_sh, p.k_sn, 64, TN, bf16)) return e;
+    if (int e = encode_heads_map(&fp.mv, p.v, p.B, p.H, p.Tk, p.d, p.v_sb, p.v_sh, p.v_sn, 64, TN, bf16)) return e;
+    fp.o = p.out_o; fp.o_sb = p.o_sb; fp.o_sh = p.o_sh; fp.o_sn = p.o_sn;
+    fp.bias = p.bias; fp.b_sb = p.b_sb; fp.b_sh = p.b_sh; fp.b_sq = p.b_sq;
+    fp.bias_kind = p.bias_kind; fp.bias_f32 = p.bias_f32;
+    const int bel = p.bias_f32 ? 4 : 8;   // bias elements per 16 bytes
+    fp.bias_vec = p.bias_kind != RGD_BIAS_NONE && is_aligned(p.bias, 16) && p.b_sb % bel == 0 && p.b_sh % bel == 0 &&
+                  (p.bias_kind != RGD_BIAS_MATRIX || p.b_sq % bel == 0);
+    fp.lse = p.lse;
+    fp.H = p.H; fp.Tq = p.Tq; fp.Tk = p.Tk; fp.Tq_rounded = p.Tq_rounded; fp.causal = p.causal;
+    fp.scale_log2 = p.scale * LOG2E;
+    const int nq = (p.Tq + TM - 1) / TM, BH = p.B * p.H;
+    if (p.d == 128) return bf16 ? launch_fwd_tmem<128, true>(fp, nq, BH, st) : launch_fwd_tmem<128, false>(fp, nq, BH, st);
+    return bf16 ? launch_fwd_tmem<64, true>(fp, nq, BH, st) : launch_fwd_tmem<64, false>(fp, nq, BH, st);
+}
+
+// Read and clear the sticky device status word of the tensor-memory kernels
+// (synchronises the device).
+int tmem_status_fetch() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tmem_status, sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -1;
+    }
+    if (v != 0) {
+        const int zero = 0;
+        (void)cudaMemcpyToSymbol(g_tmem_status, &zero, sizeof(int));
+    }
+    return v;
+}
+
+}  // namespace attn
+}  // namespace rgd

@@ -17,6 +17,15 @@ from tests._util import DTYPES, T, assert_attn, attn_error, gen, randn
 
 pytestmark = pytest.mark.gpu
 
+@pytest.fixture(autouse=True)
+def _no_device_wait_timed_out():
+    """Every bounded device-side wait of the tensor-memory kernels must have
+    completed normally."""
+    yield
+    from rgd_triton_b200 import _lib
+    assert _lib.load().rgd_device_status() == 0, "a bounded device-side wait expired (RGD_E_TIMEOUT)"
+
+
 LENS = [(113, 203), (128, 217), (108, 256), (256, 512), (1, 1), (3, 1023), (1023, 1024), (64, 64)]
 
 
