@@ -10,6 +10,9 @@ int general_bwd(const AttnParams &p, int dtype, cudaStream_t st);
 bool tmem_fwd_eligible(const AttnParams &p);
 int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st);
 int tmem_status_fetch();
+bool tmem_bwd_eligible(const AttnParams &p);
+int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st);
+int delta_only(const AttnParams &p, int dtype, cudaStream_t st);
 }  // namespace attn
 }  // namespace rgd
 
@@ -135,5 +138,9 @@ extern "C" int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_he
     p.vec_dv = dvec && heads_vec16(dv);
     p.lse = const_cast<float *>(lse);
     p.delta = reinterpret_cast<float *>(workspace);
+    if (work && attn::tmem_bwd_eligible(p)) {
+        if (int e = attn::delta_only(p, dtype, (cudaStream_t)stream)) return e;
+        return attn::tmem_bwd(p, dtype, (cudaStream_t)stream);
+    }
     return attn::general_bwd(p, dtype, (cudaStream_t)stream);
 }

@@ -30,7 +30,7 @@ namespace attn {
 
 using namespace rgd::sm100;
 
-__device__ int g_tmem_status;
+__device__ int g_tmem_status = 0;
 
 constexpr int FWD_THREADS = 192;
 constexpr int TM = 128;   // query rows per CTA
@@ -47,6 +47,7 @@ struct FwdTmaParams {
     float *lse;
     int H, Tq, Tk, Tq_rounded, causal;
     float scale_log2;   // softmax_scale * log2(e)
+    int *status;        // device status word (bounded waits report here)
 };
 
 template <int D, int STAGES>
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) attn_fwd_tmem(const __grid_con
     const int m0 = mblk * TM;
     const int n_end = p.causal ? min(p.Tk, m0 + TM) : p.Tk;
     const int nblk = (n_end + TN - 1) / TN;
-    int *status = &g_tmem_status;
+    int *status = p.status;
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
@@ -355,6 +356,23 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) attn_fwd_tmem(const __grid_con
 // ---------------------------------------------------------------------------
 // Host
 // ---------------------------------------------------------------------------
+// Device address of the status word on the current device (the symbol has one
+// instance per device, so the address is looked up per device and cached).
+int *tmem_status_ptr() {
+    static int *cache[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cache[dev] == nullptr) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_tmem_status) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        cache[dev] = reinterpret_cast<int *>(ptr);
+    }
+    return cache[dev];
+}
+
 bool tmem_fwd_eligible(const AttnParams &p) {
     return (p.d == 64 || p.d == 128) && p.Tq >= 1 && p.Tk >= 1 && p.vec_q && p.vec_k && p.vec_v && p.vec_o;
 }
@@ -387,6 +405,8 @@ int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
     fp.lse = p.lse;
     fp.H = p.H; fp.Tq = p.Tq; fp.Tk = p.Tk; fp.Tq_rounded = p.Tq_rounded; fp.causal = p.causal;
     fp.scale_log2 = p.scale * LOG2E;
+    fp.status = tmem_status_ptr();
+    if (!fp.status) return RGD_E_DEVICE;
     const int nq = (p.Tq + TM - 1) / TM, BH = p.B * p.H;
     if (p.d == 128) return bf16 ? launch_fwd_tmem<128, true>(fp, nq, BH, st) : launch_fwd_tmem<128, false>(fp, nq, BH, st);
     return bf16 ? launch_fwd_tmem<64, true>(fp, nq, BH, st) : launch_fwd_tmem<64, false>(fp, nq, BH, st);
