@@ -1,16 +1,20 @@
 // FlashAttention forward on Blackwell tensor memory (tcgen05 + TMEM + TMA).
 //
-// One CTA owns 128 query rows of one (batch, head) and walks the keys in
-// blocks of 128.  Warp roles:
-//   warps 0-3  softmax: thread r owns query row r (TMEM lane r) — row maximum
-//              and row sum need no shuffles; writes P back to tensor memory
-//              as packed 16-bit pairs over the S columns it has consumed
-//   warp 4     TMA producer: Q once, then K and V tiles (128-byte swizzle)
-//   warp 5     MMA issuer: S = Q K^T (operands in shared memory), then
-//              O += P V with P read straight from tensor memory
-// Tensor memory: S/P in columns [0,128), the O accumulator in [128,128+D).
-// 256 columns and at most 96 KB of shared memory per CTA let two CTAs share an
-// SM, so one CTA's softmax overlaps the other's MMAs.
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles and
+// walks the keys in blocks of 128; both tiles share every K / V block, which
+// is double-buffered in shared memory.  Warp roles:
+//   warps 0-3  softmax of tile 0: thread r owns query row r (TMEM lane r), so
+//              row maximum and row sum need no shuffles; P goes back to tensor
+//              memory as packed 16-bit pairs over the S columns already read
+//   warps 4-7  softmax of tile 1
+//   warp 8     TMA producer: both Q tiles once, then K and V blocks (128-byte
+//              swizzle, 2 stages)
+//   warp 9     MMA issuer: S_t = Q_t K^T (operands in shared memory) and
+//              O_t += P_t V with P read straight from tensor memory.  The issue
+//              order interleaves the tiles — S of the next key block for tile 0
+//              is issued between the two P V products — so one tile's softmax
+//              overlaps the other tile's tensor-core work.
+// Tensor memory (512 columns): S0 / P0 at 0, S1 / P1 at 128, O0 at 256, O1 at 384.
 //
 // Online softmax runs in the base-2 domain with a lazily updated reference
 // maximum: the accumulator is only rescaled when the running maximum grows by
@@ -32,8 +36,8 @@ using namespace rgd::sm100;
 
 __device__ int g_tmem_status = 0;
 
-constexpr int FWD_THREADS = 192;
-constexpr int TM = 128;   // query rows per CTA
+constexpr int FWD_THREADS = 320;
+constexpr int TM = 128;   // query rows per tile (two tiles per CTA)
 constexpr int TN = 128;   // keys per block
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
@@ -50,13 +54,14 @@ struct FwdTmaParams {
     int *status;        // device status word (bounded waits report here)
 };
 
-template <int D, int STAGES>
+template <int D>
 struct alignas(1024) FwdTmaSmem {
-    unsigned char q[TM * D * 2];
-    unsigned char k[STAGES][TN * D * 2];
-    unsigned char v[STAGES][TN * D * 2];
-    uint64_t q_full, s_full, p_full, o_full;
-    uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    unsigned char q[2][TM * D * 2];
+    unsigned char k[2][TN * D * 2];
+    unsigned char v[2][TN * D * 2];
+    uint64_t q_full, o_full;
+    uint64_t s_full[2], p_full[2];
+    uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
     uint32_t tmem_base;
 };
 
@@ -112,34 +117,39 @@ __device__ __forceinline__ void load_bias32(const FwdTmaParams &p, const char *b
 }
 
 template <int D, bool BF16>
-__global__ void __launch_bounds__(FWD_THREADS, 2) attn_fwd_tmem(const __grid_constant__ FwdTmaParams p) {
-    constexpr int STAGES = (D == 64) ? 2 : 1;
+__global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_constant__ FwdTmaParams p) {
     constexpr int HALVES = D / 64;                 // 64-channel (128-byte) swizzle panels per tile
     constexpr uint32_t PANEL = 128 * 64 * 2;       // bytes of one 128-row panel
     constexpr uint32_t TILE_BYTES = TM * D * 2;
-    constexpr uint32_t TMEM_COLS = 256;
-    constexpr uint32_t O_COL = 128;
+    constexpr uint32_t TMEM_COLS = 512;
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
 
     extern __shared__ unsigned char smem_raw[];
-    FwdTmaSmem<D, STAGES> &sm =
-        *reinterpret_cast<FwdTmaSmem<D, STAGES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    FwdTmaSmem<D> &sm = *reinterpret_cast<FwdTmaSmem<D> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mblk = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;   // heavy causal tiles first
     const int bh = blockIdx.y;
     const int b = bh / p.H, h = bh - b * p.H;
-    const int m0 = mblk * TM;
-    const int n_end = p.causal ? min(p.Tk, m0 + TM) : p.Tk;
-    const int nblk = (n_end + TN - 1) / TN;
+    const int m0 = mblk * 2 * TM;
+    // Key blocks each tile visits (a tile past the end of Q visits none; under
+    // the causal mask tile 0 stops one block earlier than tile 1).
+    int nb[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int mt = m0 + t * TM;
+        const int n_end = p.causal ? min(p.Tk, mt + TM) : p.Tk;
+        nb[t] = mt < p.Tq ? (n_end + TN - 1) / TN : 0;
+    }
+    const int nblk = max(nb[0], nb[1]);
     int *status = p.status;
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
-        mbar_init(&sm.s_full, 1);
-        mbar_init(&sm.p_full, 128);
         mbar_init(&sm.o_full, 1);
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.s_full[s], 1);
+            mbar_init(&sm.p_full[s], 128);
             mbar_init(&sm.k_full[s], 1);
             mbar_init(&sm.k_empty[s], 1);
             mbar_init(&sm.v_full[s], 1);
@@ -156,18 +166,20 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) attn_fwd_tmem(const __grid_con
     tc_fence_after_sync();
     const uint32_t tbase = sm.tmem_base;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&p.mq);
             tma_prefetch_desc(&p.mk);
             tma_prefetch_desc(&p.mv);
-            mbar_expect_tx(&sm.q_full, TILE_BYTES);
-            for (int hh = 0; hh < HALVES; ++hh) tma_load_4d(sm.q + hh * PANEL, &p.mq, &sm.q_full, hh * 64, m0, h, b);
+            mbar_expect_tx(&sm.q_full, 2 * TILE_BYTES);
+            for (int t = 0; t < 2; ++t)
+                for (int hh = 0; hh < HALVES; ++hh)
+                    tma_load_4d(sm.q[t] + hh * PANEL, &p.mq, &sm.q_full, hh * 64, m0 + t * TM, h, b);
             bool ok = true;
-            for (int j = 0; j < nblk && ok; ++j) {
-                const int s = j % STAGES;
-                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
+            for (int j = 0; j < nblk; ++j) {
+                const int s = j & 1;
+                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
                 ok = mbar_wait(&sm.k_empty[s], ph ^ 1u, status, 11);
                 if (!ok) break;
                 mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
@@ -184,47 +196,76 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) attn_fwd_tmem(const __grid_con
                 for (int i = 0; i < 64; ++i) __nanosleep(1000);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_qk = make_idesc(BF16, TM, TN, false, false);
             constexpr uint32_t idesc_pv = make_idesc(BF16, TM, D, false, true);
-            bool ok = mbar_wait(&sm.q_full, 0, status, 21);
-            const uint32_t q_addr = smem_u32(sm.q);
-            for (int j = 0; j < nblk && ok; ++j) {
-                const int s = j % STAGES;
-                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
-                ok = mbar_wait(&sm.k_full[s], ph, status, 22);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t k_addr = smem_u32(sm.k[s]);
+            auto issue_s = [&](int t, int s) {
+                const uint32_t q_addr = smem_u32(sm.q[t]), k_addr = smem_u32(sm.k[s]);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk / 4) * PANEL + (kk % 4) * 32;
-                    umma_ss(tbase, make_sdesc(q_addr + off, 16, 1024), make_sdesc(k_addr + off, 16, 1024), idesc_qk,
-                            kk > 0);
+                    umma_ss(tbase + t * 128, make_sdesc(q_addr + off, 16, 1024), make_sdesc(k_addr + off, 16, 1024),
+                            idesc_qk, kk > 0);
                 }
-                umma_commit(&sm.k_empty[s]);
-                umma_commit(&sm.s_full);
-                ok = mbar_wait(&sm.p_full, (uint32_t)j & 1u, status, 23);
-                if (!ok) break;
-                ok = mbar_wait(&sm.v_full[s], ph, status, 24);
-                if (!ok) break;
-                tc_fence_after_sync();
+                umma_commit(&sm.s_full[t]);
+            };
+            auto issue_pv = [&](int t, int s, bool first) {
                 const uint32_t v_addr = smem_u32(sm.v[s]);
 #pragma unroll
                 for (int kk = 0; kk < TN / 16; ++kk)
-                    umma_ts(tbase + O_COL, tbase + kk * 8, make_sdesc(v_addr + kk * 2048, PANEL, 1024), idesc_pv,
-                            j > 0 || kk > 0);
+                    umma_ts(tbase + 256 + t * 128, tbase + t * 128 + kk * 8, make_sdesc(v_addr + kk * 2048, PANEL, 1024),
+                            idesc_pv, !first || kk > 0);
+            };
+            bool ok = nblk > 0 ? mbar_wait(&sm.q_full, 0, status, 21) : true;
+            if (ok && nblk > 0) ok = mbar_wait(&sm.k_full[0], 0, status, 22);
+            if (ok && nblk > 0) {
+                tc_fence_after_sync();
+                if (nb[0] > 0) issue_s(0, 0);
+                if (nb[1] > 0) issue_s(1, 0);
+                umma_commit(&sm.k_empty[0]);
+            }
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int s = j & 1;
+                const uint32_t ph = (uint32_t)(j >> 1) & 1u, par = (uint32_t)j & 1u;
+                const bool more = j + 1 < nblk;
+                ok = mbar_wait(&sm.v_full[s], ph, status, 23);
+                if (!ok) break;
+                if (j < nb[0]) {
+                    ok = mbar_wait(&sm.p_full[0], par, status, 24);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(0, s, j == 0);
+                }
+                if (more) {
+                    ok = mbar_wait(&sm.k_full[s ^ 1], (uint32_t)((j + 1) >> 1) & 1u, status, 25);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    if (j + 1 < nb[0]) issue_s(0, s ^ 1);
+                }
+                if (j < nb[1]) {
+                    ok = mbar_wait(&sm.p_full[1], par, status, 26);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(1, s, j == 0);
+                }
                 umma_commit(&sm.v_empty[s]);
+                if (more) {
+                    if (j + 1 < nb[1]) issue_s(1, s ^ 1);
+                    umma_commit(&sm.k_empty[s ^ 1]);
+                }
             }
             umma_commit(&sm.o_full);
         }
     } else {
         // ------------------------------ softmax + epilogue ------------------------------
-        const int row_l = warp * 32 + lane;          // row inside the tile == TMEM lane
-        const int row = m0 + row_l;
-        const uint32_t lane_base = tbase + ((uint32_t)(warp * 32) << 16);
+        const int t = warp >> 2;                         // which query tile
+        const int row_l = (warp & 3) * 32 + lane;        // row inside the tile == TMEM lane
+        const int row = m0 + t * TM + row_l;
+        const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t s_col = t * 128, o_col = 256 + t * 128;
+        const int my_nb = nb[t];
         const char *bias_bh = nullptr;
         if (p.bias_kind != RGD_BIAS_NONE)
             bias_bh = reinterpret_cast<const char *>(p.bias) +
@@ -233,31 +274,46 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) attn_fwd_tmem(const __grid_con
 
         float m_ref = -INFINITY, l_sum = 0.f;
         bool ok = true;
-        for (int j = 0; j < nblk; ++j) {
-            ok = mbar_wait(&sm.s_full, (uint32_t)j & 1u, status, 31);
+        for (int j = 0; j < my_nb; ++j) {
+            ok = mbar_wait(&sm.s_full[t], (uint32_t)j & 1u, status, 31);
             if (!ok) break;
             tc_fence_after_sync();
             const int n0 = j * TN;
-            const bool need_mask = (n0 + TN > p.Tk) || (p.causal && n0 + TN > m0);
+            const bool need_mask = (n0 + TN > p.Tk) || (p.causal && n0 + TN > m0 + t * TM);
 
-            // pass 1: block maximum of x = s * scale * log2e + bias * log2e
+            // pass 1: block maximum of x = s * scale * log2e + bias * log2e, 64 columns per round
             float mx = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + c * 32, r);
-                float bb[32];
-                if (bias_bh != nullptr) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 32, bb);
-                tmem_wait_ld();
+            for (int c = 0; c < 2; ++c) {
+                uint32_t r0[32], r1[32];
+                tmem_ld32(lane_base + s_col + c * 64, r0);
+                tmem_ld32(lane_base + s_col + c * 64 + 32, r1);
+                if (bias_bh == nullptr && !need_mask) {
+                    tmem_wait_ld();
+                    float a = -INFINITY, bq = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __uint_as_float(r[i]) * p.scale_log2;
-                    if (bias_bh != nullptr) x += bb[i];
-                    if (need_mask) {
-                        const int col = n0 + c * 32 + i;
-                        if (col >= p.Tk || (p.causal && col > row)) x = -INFINITY;
+                    for (int i = 0; i < 32; ++i) {
+                        a = fmaxf(a, __uint_as_float(r0[i]));
+                        bq = fmaxf(bq, __uint_as_float(r1[i]));
                     }
-                    mx = fmaxf(mx, x);
+                    mx = fmaxf(mx, fmaxf(a, bq) * p.scale_log2);      // scale > 0: max commutes with it
+                } else {
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        float bb[32];
+                        if (bias_bh != nullptr) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
+                        if (hf == 0) tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float x = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
+                            if (bias_bh != nullptr) x += bb[i];
+                            if (need_mask) {
+                                const int col = n0 + c * 64 + hf * 32 + i;
+                                if (col >= p.Tk || (p.causal && col > row)) x = -INFINITY;
+                            }
+                            mx = fmaxf(mx, x);
+                        }
+                    }
                 }
             }
             // lazy reference update (warp-uniform decision: TMEM accesses are warp-collective)
@@ -271,11 +327,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) attn_fwd_tmem(const __grid_con
 #pragma unroll 1
                     for (int c = 0; c < D / 32; ++c) {
                         uint32_t r[32];
-                        tmem_ld32(lane_base + O_COL + c * 32, r);
+                        tmem_ld32(lane_base + o_col + c * 32, r);
                         tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st32(lane_base + O_COL + c * 32, r);
+                        tmem_st32(lane_base + o_col + c * 32, r);
                     }
                 }
             }
@@ -283,68 +339,90 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) attn_fwd_tmem(const __grid_con
 
             // pass 2: P = 2^(x - m), row sum, packed 16-bit P over the consumed S columns
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + c * 32, r);
-                float bb[32];
-                if (bias_bh != nullptr) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 32, bb);
-                tmem_wait_ld();
-                uint32_t pk[16];
+            for (int c = 0; c < 2; ++c) {
+                uint32_t r0[32], r1[32];
+                tmem_ld32(lane_base + s_col + c * 64, r0);
+                tmem_ld32(lane_base + s_col + c * 64 + 32, r1);
+                uint32_t pk[32];
+                float ls0 = 0.f, ls1 = 0.f;
+                if (bias_bh == nullptr && !need_mask) {
+                    tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float x0 = __uint_as_float(r[i]) * p.scale_log2, x1 = __uint_as_float(r[i + 1]) * p.scale_log2;
-                    if (bias_bh != nullptr) {
-                        x0 += bb[i];
-                        x1 += bb[i + 1];
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = ex2(fmaf(__uint_as_float(r0[i]), p.scale_log2, -m_use));
+                        const float p1 = ex2(fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, -m_use));
+                        const float p2 = ex2(fmaf(__uint_as_float(r1[i]), p.scale_log2, -m_use));
+                        const float p3 = ex2(fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, -m_use));
+                        ls0 += p0 + p1;
+                        ls1 += p2 + p3;
+                        pk[i >> 1] = pack16<BF16>(p0, p1);
+                        pk[16 + (i >> 1)] = pack16<BF16>(p2, p3);
                     }
-                    if (need_mask) {
-                        const int col = n0 + c * 32 + i;
-                        if (col >= p.Tk || (p.causal && col > row)) x0 = -INFINITY;
-                        if (col + 1 >= p.Tk || (p.causal && col + 1 > row)) x1 = -INFINITY;
+                } else {
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        float bb[32];
+                        if (bias_bh != nullptr) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
+                        if (hf == 0) tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float x0 = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
+                            float x1 = __uint_as_float(hf ? r1[i + 1] : r0[i + 1]) * p.scale_log2;
+                            if (bias_bh != nullptr) {
+                                x0 += bb[i];
+                                x1 += bb[i + 1];
+                            }
+                            if (need_mask) {
+                                const int col = n0 + c * 64 + hf * 32 + i;
+                                if (col >= p.Tk || (p.causal && col > row)) x0 = -INFINITY;
+                                if (col + 1 >= p.Tk || (p.causal && col + 1 > row)) x1 = -INFINITY;
+                            }
+                            const float p0 = ex2(x0 - m_use), p1 = ex2(x1 - m_use);
+                            ls0 += p0 + p1;
+                            pk[hf * 16 + (i >> 1)] = pack16<BF16>(p0, p1);
+                        }
                     }
-                    const float p0 = ex2(x0 - m_use), p1 = ex2(x1 - m_use);
-                    l_sum += p0 + p1;
-                    pk[i >> 1] = pack16<BF16>(p0, p1);
                 }
-                tmem_st16(lane_base + c * 16, pk);
+                l_sum += ls0 + ls1;
+                tmem_st32(lane_base + s_col + c * 32, pk);
             }
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&sm.p_full);
+            mbar_arrive(&sm.p_full[t]);
         }
 
         // epilogue: O / l, LSE
-        if (ok) ok = mbar_wait(&sm.o_full, 0, status, 32);
-        tc_fence_after_sync();
-        const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-        if (ok) {
-            T *orow = reinterpret_cast<T *>(p.o) + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)row * p.o_sn;
+        if (my_nb > 0) {
+            if (ok) ok = mbar_wait(&sm.o_full, 0, status, 32);
+            tc_fence_after_sync();
+            const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+            if (ok) {
+                T *orow = reinterpret_cast<T *>(p.o) + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)row * p.o_sn;
 #pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                if (nblk > 0) {
-                    tmem_ld32(lane_base + O_COL + c * 32, r);
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_base + o_col + c * 32, r);
                     tmem_wait_ld();
-                } else {
+                    if (row < p.Tq) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = 0u;
-                }
-                if (row < p.Tq) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 v;
-                        v.x = pack16<BF16>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-                        v.y = pack16<BF16>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-                        v.z = pack16<BF16>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-                        v.w = pack16<BF16>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-                        *reinterpret_cast<uint4 *>(orow + c * 32 + i) = v;
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 v;
+                            v.x = pack16<BF16>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                            v.y = pack16<BF16>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                            v.z = pack16<BF16>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                            v.w = pack16<BF16>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                            *reinterpret_cast<uint4 *>(orow + c * 32 + i) = v;
+                        }
                     }
                 }
+                if (row < p.Tq_rounded) {
+                    const float lse = l_sum > 0.f ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
+                    p.lse[(int64_t)bh * p.Tq_rounded + row] = row < p.Tq ? lse : INFINITY;
+                }
             }
-            if (row < p.Tq_rounded) {
-                const float lse = l_sum > 0.f ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
-                p.lse[(int64_t)bh * p.Tq_rounded + row] = row < p.Tq ? lse : INFINITY;
-            }
+        } else if (row < p.Tq_rounded) {
+            // tile entirely past the end of Q: only the padded LSE rows exist
+            p.lse[(int64_t)bh * p.Tq_rounded + row] = INFINITY;
         }
     }
 
@@ -379,8 +457,7 @@ bool tmem_fwd_eligible(const AttnParams &p) {
 
 template <int D, bool BF16>
 static int launch_fwd_tmem(const FwdTmaParams &fp, int nq_tiles, int BH, cudaStream_t st) {
-    constexpr int STAGES = (D == 64) ? 2 : 1;
-    const size_t smem = sizeof(FwdTmaSmem<D, STAGES>) + 1024;
+    const size_t smem = sizeof(FwdTmaSmem<D>) + 1024;
     if (int e = cuda_status(cudaFuncSetAttribute(attn_fwd_tmem<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)smem)))
         return e;
@@ -407,7 +484,7 @@ int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
     fp.scale_log2 = p.scale * LOG2E;
     fp.status = tmem_status_ptr();
     if (!fp.status) return RGD_E_DEVICE;
-    const int nq = (p.Tq + TM - 1) / TM, BH = p.B * p.H;
+    const int nq = (p.Tq + 2 * TM - 1) / (2 * TM), BH = p.B * p.H;
     if (p.d == 128) return bf16 ? launch_fwd_tmem<128, true>(fp, nq, BH, st) : launch_fwd_tmem<128, false>(fp, nq, BH, st);
     return bf16 ? launch_fwd_tmem<64, true>(fp, nq, BH, st) : launch_fwd_tmem<64, false>(fp, nq, BH, st);
 }
