@@ -12,7 +12,7 @@ int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st);
 int tmem_status_fetch();
 bool tmem_bwd_eligible(const AttnParams &p);
 int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st);
-int delta_only(const AttnParams &p, int dtype, cudaStream_t st);
+int64_t tmem_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq);
 }  // namespace attn
 }  // namespace rgd
 
@@ -107,7 +107,10 @@ extern "C" int rgd_attn_fwd(const rgd_heads *q, const rgd_heads *k, const rgd_he
 extern "C" int64_t rgd_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d, int dtype) {
     (void)Tk; (void)d; (void)dtype;
     if (B < 0 || H < 0 || Tq < 0) return RGD_E_INVALID;
-    return B * H * lse_rows(Tq) * (int64_t)sizeof(float);   // delta
+    // general path: delta [B,H,Tq_rounded]; tensor-memory path: lse*log2e and delta*scale, [B,H,Tq128] each
+    const int64_t general = B * H * lse_rows(Tq) * (int64_t)sizeof(float);
+    const int64_t tmem = attn::tmem_bwd_workspace_bytes(B, H, Tq);
+    return general > tmem ? general : tmem;
 }
 
 extern "C" int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
@@ -138,9 +141,6 @@ extern "C" int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_he
     p.vec_dv = dvec && heads_vec16(dv);
     p.lse = const_cast<float *>(lse);
     p.delta = reinterpret_cast<float *>(workspace);
-    if (work && attn::tmem_bwd_eligible(p)) {
-        if (int e = attn::delta_only(p, dtype, (cudaStream_t)stream)) return e;
-        return attn::tmem_bwd(p, dtype, (cudaStream_t)stream);
-    }
+    if (work && attn::tmem_bwd_eligible(p)) return attn::tmem_bwd(p, dtype, (cudaStream_t)stream);
     return attn::general_bwd(p, dtype, (cudaStream_t)stream);
 }

@@ -43,8 +43,8 @@ struct BwdTmaParams {
     const void *bias;
     int64_t b_sb, b_sh, b_sq;
     int bias_kind, bias_f32, bias_vec;
-    const float *lse, *delta;           // [B, H, Tq_rounded]
-    int H, Tq, Tk, Tq_rounded, causal;
+    const float *lse2, *delta_s;        // [B, H, Tq128]: lse * log2(e) (+inf past Tq), delta * scale (0 past Tq)
+    int H, Tq, Tk, Tq128, causal;
     float scale, scale_log2;
     int *status;
 };
@@ -215,86 +215,136 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
         const int half = warp >> 2;                        // which 64 of the 128 columns
         const int row = r0 + row_l;                        // key (DKDV) or query (DQ) index
         const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
-        const float *lse_bh = p.lse + (int64_t)bh * p.Tq_rounded;
-        const float *delta_bh = p.delta + (int64_t)bh * p.Tq_rounded;
+        const float *lse2_bh = p.lse2 + (int64_t)bh * p.Tq128;
+        const float *ds_bh = p.delta_s + (int64_t)bh * p.Tq128;
         const char *bias_bh = nullptr;
         if (p.bias_kind != RGD_BIAS_NONE)
             bias_bh = reinterpret_cast<const char *>(p.bias) +
                       ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
 
-        float lse_row = INFINITY, delta_row = 0.f;         // DQ: per-thread row statistics
-        if (!DKDV && row < p.Tq) {
-            lse_row = lse_bh[row] * LOG2E;
-            delta_row = delta_bh[row];
+        // DQ: per-thread row statistics (rows past Tq hold +inf / 0, so they yield P = 0)
+        float lse_row = INFINITY, dsc_row = 0.f;
+        if (!DKDV) {
+            lse_row = lse2_bh[row];
+            dsc_row = ds_bh[row];
         }
+        const bool cta_key_tail = DKDV && (r0 + BT > p.Tk);
 
         bool ok = true;
         for (int it = 0; it < nit; ++it) {
             const uint32_t par = (uint32_t)it & 1u;
-            const int c0 = (i_begin + it) * BT + half * 64;   // first column index (query for DKDV, key for DQ)
+            const int blk0 = (i_begin + it) * BT;          // first column index of this block
+            const int c0 = blk0 + half * 64;               // first column this thread handles
+            // Blocks that need per-element masking: the diagonal block under the causal
+            // mask, and any block touching the end of the keys.  Rows / columns past
+            // the end of the QUERIES need nothing: their lse2 is +inf.
+            const bool diag = p.causal && (DKDV ? (blk0 == r0) : (blk0 + BT > r0));
+            const bool slow = diag || cta_key_tail || (!DKDV && blk0 + BT > p.Tk) || bias_bh != nullptr;
             float pv[64];
 
             ok = mbar_wait(&sm.g1_full, par, status, 61);
             if (!ok) break;
             tc_fence_after_sync();
+            {
+                uint32_t ra[32], rb[32];
+                tmem_ld32(lane_base + G1_COL + half * 64, ra);
+                tmem_ld32(lane_base + G1_COL + half * 64 + 32, rb);
+                if (!slow) {
+                    if (DKDV) {
+                        float4 l4[16];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + G1_COL + half * 64 + c * 32, r);
-                tmem_wait_ld();
+                        for (int i = 0; i < 16; ++i) l4[i] = __ldg(reinterpret_cast<const float4 *>(lse2_bh + c0) + i);
+                        tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int col = c0 + c * 32 + i;
-                    const int qi = DKDV ? col : row, kj = DKDV ? row : col;
-                    float x = __uint_as_float(r[i]) * p.scale_log2;
-                    const bool masked = kj >= p.Tk || qi >= p.Tq || (p.causal && kj > qi);
-                    float l2;
-                    if (DKDV) l2 = (qi < p.Tq) ? __ldg(lse_bh + qi) * LOG2E : INFINITY;
-                    else l2 = lse_row;
-                    if (bias_bh != nullptr && !masked) {
-                        const int64_t off = (p.bias_kind == RGD_BIAS_MATRIX ? (int64_t)qi * p.b_sq : 0) + kj;
-                        x += (p.bias_f32 ? reinterpret_cast<const float *>(bias_bh)[off]
-                                         : to_f32<T>(reinterpret_cast<const T *>(bias_bh)[off])) * LOG2E;
+                        for (int i = 0; i < 8; ++i) {
+                            pv[4 * i + 0] = ex2b(fmaf(__uint_as_float(ra[4 * i + 0]), p.scale_log2, -l4[i].x));
+                            pv[4 * i + 1] = ex2b(fmaf(__uint_as_float(ra[4 * i + 1]), p.scale_log2, -l4[i].y));
+                            pv[4 * i + 2] = ex2b(fmaf(__uint_as_float(ra[4 * i + 2]), p.scale_log2, -l4[i].z));
+                            pv[4 * i + 3] = ex2b(fmaf(__uint_as_float(ra[4 * i + 3]), p.scale_log2, -l4[i].w));
+                            pv[32 + 4 * i + 0] = ex2b(fmaf(__uint_as_float(rb[4 * i + 0]), p.scale_log2, -l4[8 + i].x));
+                            pv[32 + 4 * i + 1] = ex2b(fmaf(__uint_as_float(rb[4 * i + 1]), p.scale_log2, -l4[8 + i].y));
+                            pv[32 + 4 * i + 2] = ex2b(fmaf(__uint_as_float(rb[4 * i + 2]), p.scale_log2, -l4[8 + i].z));
+                            pv[32 + 4 * i + 3] = ex2b(fmaf(__uint_as_float(rb[4 * i + 3]), p.scale_log2, -l4[8 + i].w));
+                        }
+                    } else {
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            pv[i] = ex2b(fmaf(__uint_as_float(ra[i]), p.scale_log2, -lse_row));
+                            pv[32 + i] = ex2b(fmaf(__uint_as_float(rb[i]), p.scale_log2, -lse_row));
+                        }
                     }
-                    pv[c * 32 + i] = masked ? 0.f : ex2b(x - l2);
+                } else {
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int col = c0 + i;
+                        const int qi = DKDV ? col : row, kj = DKDV ? row : col;
+                        float x = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]) * p.scale_log2;
+                        const bool masked = kj >= p.Tk || qi >= p.Tq || (p.causal && kj > qi);
+                        const float l2 = DKDV ? __ldg(lse2_bh + qi) : lse_row;
+                        if (bias_bh != nullptr && !masked) {
+                            const int64_t off = (p.bias_kind == RGD_BIAS_MATRIX ? (int64_t)qi * p.b_sq : 0) + kj;
+                            x += (p.bias_f32 ? reinterpret_cast<const float *>(bias_bh)[off]
+                                             : to_f32<T>(reinterpret_cast<const T *>(bias_bh)[off])) * LOG2E;
+                        }
+                        pv[i] = masked ? 0.f : ex2b(x - l2);
+                    }
                 }
                 if (DKDV) {
-                    uint32_t pk[16];
+                    uint32_t pk[32];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) pk[i] = pack16b<BF16>(pv[c * 32 + 2 * i], pv[c * 32 + 2 * i + 1]);
-                    tmem_st16(lane_base + G1_COL + half * 64 + c * 16, pk);
+                    for (int i = 0; i < 32; ++i) pk[i] = pack16b<BF16>(pv[2 * i], pv[2 * i + 1]);
+                    tmem_st32(lane_base + G1_COL + half * 64, pk);
+                    tmem_wait_st();
                 }
             }
-            if (DKDV) tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&sm.p_ready);
 
             ok = mbar_wait(&sm.g2_full, par, status, 62);
             if (!ok) break;
             tc_fence_after_sync();
+            {
+                uint32_t ga[32], gb[32];
+                tmem_ld32(lane_base + G2_COL + half * 64, ga);
+                tmem_ld32(lane_base + G2_COL + half * 64 + 32, gb);
+                uint32_t pk[32];
+                if (DKDV) {
+                    float4 d4[16];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t g2[32];
-                tmem_ld32(lane_base + G2_COL + half * 64 + c * 32, g2);
-                tmem_wait_ld();
-                uint32_t pk[16];
+                    for (int i = 0; i < 16; ++i) d4[i] = __ldg(reinterpret_cast<const float4 *>(ds_bh + c0) + i);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float d0, d1;
-                    if (DKDV) {
-                        const int q0 = c0 + c * 32 + i;
-                        d0 = (q0 < p.Tq) ? __ldg(delta_bh + q0) : 0.f;
-                        d1 = (q0 + 1 < p.Tq) ? __ldg(delta_bh + q0 + 1) : 0.f;
-                    } else {
-                        d0 = d1 = delta_row;
+                    for (int i = 0; i < 8; ++i) {
+                        const float a0 = pv[4 * i + 0] * fmaf(__uint_as_float(ga[4 * i + 0]), p.scale, -d4[i].x);
+                        const float a1 = pv[4 * i + 1] * fmaf(__uint_as_float(ga[4 * i + 1]), p.scale, -d4[i].y);
+                        const float a2 = pv[4 * i + 2] * fmaf(__uint_as_float(ga[4 * i + 2]), p.scale, -d4[i].z);
+                        const float a3 = pv[4 * i + 3] * fmaf(__uint_as_float(ga[4 * i + 3]), p.scale, -d4[i].w);
+                        pk[2 * i] = pack16b<BF16>(a0, a1);
+                        pk[2 * i + 1] = pack16b<BF16>(a2, a3);
+                        const float b0 = pv[32 + 4 * i + 0] * fmaf(__uint_as_float(gb[4 * i + 0]), p.scale, -d4[8 + i].x);
+                        const float b1 = pv[32 + 4 * i + 1] * fmaf(__uint_as_float(gb[4 * i + 1]), p.scale, -d4[8 + i].y);
+                        const float b2 = pv[32 + 4 * i + 2] * fmaf(__uint_as_float(gb[4 * i + 2]), p.scale, -d4[8 + i].z);
+                        const float b3 = pv[32 + 4 * i + 3] * fmaf(__uint_as_float(gb[4 * i + 3]), p.scale, -d4[8 + i].w);
+                        pk[16 + 2 * i] = pack16b<BF16>(b0, b1);
+                        pk[16 + 2 * i + 1] = pack16b<BF16>(b2, b3);
                     }
-                    const float s0 = pv[c * 32 + i] * (__uint_as_float(g2[i]) - d0) * p.scale;
-                    const float s1 = pv[c * 32 + i + 1] * (__uint_as_float(g2[i + 1]) - d1) * p.scale;
-                    pk[i >> 1] = pack16b<BF16>(s0, s1);
+                } else {
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float a0 = pv[2 * i] * fmaf(__uint_as_float(ga[2 * i]), p.scale, -dsc_row);
+                        const float a1 = pv[2 * i + 1] * fmaf(__uint_as_float(ga[2 * i + 1]), p.scale, -dsc_row);
+                        pk[i] = pack16b<BF16>(a0, a1);
+                        const float b0 = pv[32 + 2 * i] * fmaf(__uint_as_float(gb[2 * i]), p.scale, -dsc_row);
+                        const float b1 = pv[32 + 2 * i + 1] * fmaf(__uint_as_float(gb[2 * i + 1]), p.scale, -dsc_row);
+                        pk[16 + i] = pack16b<BF16>(b0, b1);
+                    }
                 }
-                tmem_st16(lane_base + G2_COL + half * 64 + c * 16, pk);
+                tmem_st32(lane_base + G2_COL + half * 64, pk);
+                tmem_wait_st();
             }
-            tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_ready);
         }
@@ -345,10 +395,48 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
 }
 
 // ---------------------------------------------------------------------------
+// Row statistics for the backward: delta = rowsum(O * dO)
+// (flash_attn_triton_cached.py:249-292), stored pre-multiplied by the softmax
+// scale, and lse * log2(e).  Rows in [Tq, Tq128) get +inf / 0 so that query
+// positions past the end need no masking in the main kernels.  One warp per row.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __grid_constant__ AttnParams p, float *lse2, float *delta_s,
+                                                            int Tq128) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i = blockIdx.x * 8 + warp;
+    const int bh = blockIdx.y;
+    if (i >= Tq128) return;
+    const int b = bh / p.H, h = bh - b * p.H;
+    float a = 0.f;
+    if (i < p.Tq) {
+        const T *o = reinterpret_cast<const T *>(p.o) + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)i * p.o_sn;
+        const T *g = reinterpret_cast<const T *>(p.d_o) + (int64_t)b * p.do_sb + (int64_t)h * p.do_sh +
+                     (int64_t)i * p.do_sn;
+        for (int c = lane * 8; c < p.d; c += 256) {     // d is 64 or 128, rows 16-byte aligned
+            const Vec<T, 8> ov = load_vec<T, 8>(o + c), gv = load_vec<T, 8>(g + c);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a += to_f32<T>(ov.v[e]) * to_f32<T>(gv.v[e]);
+        }
+    }
+    a = warp_group_sum(a, 32);
+    if (lane == 0) {
+        const int64_t idx = (int64_t)bh * Tq128 + i;
+        delta_s[idx] = a * p.scale;
+        lse2[idx] = i < p.Tq ? p.lse[(int64_t)bh * p.Tq_rounded + i] * LOG2E : INFINITY;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Host
 // ---------------------------------------------------------------------------
+int64_t tmem_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq) {
+    const int64_t Tq128 = (Tq + 127) / 128 * 128;
+    return 2 * B * H * Tq128 * (int64_t)sizeof(float);
+}
+
 bool tmem_bwd_eligible(const AttnParams &p) {
-    return (p.d == 64 || p.d == 128) && p.Tq >= 1 && p.Tk >= 1 && p.vec_q && p.vec_k && p.vec_v && p.vec_do &&
+    return (p.d == 64 || p.d == 128) && p.Tq >= 1 && p.Tk >= 1 && p.vec_q && p.vec_k && p.vec_v && p.vec_o && p.vec_do &&
            p.vec_dq && p.vec_dk && p.vec_dv;
 }
 
@@ -375,18 +463,27 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     return launch_bwd_tmem<D, BF16, false>(bp, (p.Tq + BT - 1) / BT, BH, st);
 }
 
-// delta must already be in p.delta (the caller runs the delta kernel first).
+// p.delta points at the caller's workspace (tmem_bwd_workspace_bytes).
 int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st) {
     BwdTmaParams bp{};
     const bool bf16 = dtype == RGD_BF16;
+    const int Tq128 = (p.Tq + 127) / 128 * 128;
+    float *lse2 = p.delta, *delta_s = p.delta + (int64_t)p.B * p.H * Tq128;
+    {
+        dim3 grid((Tq128 + 7) / 8, p.B * p.H);
+        if (bf16) attn_bwd_prep_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, lse2, delta_s, Tq128);
+        else attn_bwd_prep_kernel<__half><<<grid, 256, 0, st>>>(p, lse2, delta_s, Tq128);
+        count_launch();
+        if (int e = check_launch()) return e;
+    }
     if (int e = encode_heads_map(&bp.mq, p.q, p.B, p.H, p.Tq, p.d, p.q_sb, p.q_sh, p.q_sn, 64, BT, bf16)) return e;
     if (int e = encode_heads_map(&bp.mk, p.k, p.B, p.H, p.Tk, p.d, p.k_sb, p.k_sh, p.k_sn, 64, BT, bf16)) return e;
     if (int e = encode_heads_map(&bp.mv, p.v, p.B, p.H, p.Tk, p.d, p.v_sb, p.v_sh, p.v_sn, 64, BT, bf16)) return e;
     if (int e = encode_heads_map(&bp.mdo, p.d_o, p.B, p.H, p.Tq, p.d, p.do_sb, p.do_sh, p.do_sn, 64, BT, bf16)) return e;
     bp.bias = p.bias; bp.b_sb = p.b_sb; bp.b_sh = p.b_sh; bp.b_sq = p.b_sq;
     bp.bias_kind = p.bias_kind; bp.bias_f32 = p.bias_f32; bp.bias_vec = 0;
-    bp.lse = p.lse; bp.delta = p.delta;
-    bp.H = p.H; bp.Tq = p.Tq; bp.Tk = p.Tk; bp.Tq_rounded = p.Tq_rounded; bp.causal = p.causal;
+    bp.lse2 = lse2; bp.delta_s = delta_s;
+    bp.H = p.H; bp.Tq = p.Tq; bp.Tk = p.Tk; bp.Tq128 = Tq128; bp.causal = p.causal;
     bp.scale = p.scale; bp.scale_log2 = p.scale * LOG2E;
     bp.status = tmem_status_ptr();
     if (!bp.status) return RGD_E_DEVICE;

@@ -397,20 +397,6 @@ static int bwd_dispatch(const AttnParams &p, cudaStream_t st) {
     return bwd_launch<T, 128>(p, st);
 }
 
-template <typename T>
-static int delta_launch(const AttnParams &p, cudaStream_t st) {
-    if (p.Tq_rounded == 0 || p.B * p.H == 0) return RGD_OK;
-    dim3 grid((p.Tq_rounded + 7) / 8, p.B * p.H);
-    attn_delta_kernel<T><<<grid, 256, 0, st>>>(p);
-    count_launch();
-    return check_launch();
-}
-
-// delta = rowsum(O * dO) alone, for the tensor-memory backward.
-int delta_only(const AttnParams &p, int dtype, cudaStream_t st) {
-    return dtype == RGD_F16 ? delta_launch<__half>(p, st) : delta_launch<__nv_bfloat16>(p, st);
-}
-
 int general_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
     if (p.B == 0 || p.H == 0 || p.Tq == 0) return RGD_OK;
     return dtype == RGD_F16 ? fwd_dispatch<__half>(p, st) : fwd_dispatch<__nv_bfloat16>(p, st);
