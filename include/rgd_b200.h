@@ -119,6 +119,32 @@ int rgd_rmsnorm_bwd(int nstreams, const rgd_rows *x, const void *const *w,
                     int w_dtype, void *workspace, int64_t workspace_bytes,
                     void *stream);
 
+/* Capacity of the built-in scratch of rgd_rmsnorm_bwd_static: 16 MiB of device
+ * memory per GPU, held from library load to process exit. */
+#define RGD_RMSNORM_BWD_STATIC_SCRATCH_BYTES (16ll << 20)
+/* rgd_rmsnorm_bwd for callers that cannot allocate device memory (no
+ * counterpart in the reference, which allocates its scratch with torch on
+ * every call).  Same arguments and results as rgd_rmsnorm_bwd minus the
+ * workspace: the dweight partial rows go to a fixed device array inside the
+ * library.  The call itself allocates nothing — no cudaMalloc / cudaFree, no
+ * allocating library routine.
+ *   - Limit: rgd_rmsnorm_bwd_workspace_bytes(...) for the call must not exceed
+ *     RGD_RMSNORM_BWD_STATIC_SCRATCH_BYTES, otherwise RGD_E_WORKSPACE is
+ *     returned and nothing is launched (e.g. two streams of 3072 channels fit,
+ *     two streams of 4096 channels do not).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     before starting any stream capture on the device.
+ *   - All calls on a device share the one array, which keeps the previous
+ *     call's contents; nothing in it needs clearing between calls, but two
+ *     calls that overlap on the GPU (different streams) race on it. */
+int rgd_rmsnorm_bwd_static(int nstreams, const rgd_rows *x, const void *const *w,
+                           const int64_t *w_stride_b, const rgd_rows *dy,
+                           const rgd_rows *dx, void *const *dw,
+                           const int *dw_per_batch, const int64_t *N,
+                           const int64_t *C, int64_t B, float eps, int x_dtype,
+                           int w_dtype, void *stream);
+
 /* ---- per-head LayerNorm (no affine) on Q and K in one launch ----------- */
 /* Replaces _fused_ln_qk_fwd / _fused_ln_qk_bwd
  * (head_layernorm_cached.py:204-308, :310-408).  head_dim <= 256. */

@@ -59,6 +59,8 @@ SIGNATURES = {
     "rgd_rmsnorm_bwd_workspace_bytes": (_i64, [_i32, _pi64, _pi64, _i64]),
     "rgd_rmsnorm_bwd": (_i32, [_i32, _pRows, _pvp, _pi64, _pRows, _pRows, _pvp, _pi32, _pi64, _pi64, _i64, _f32,
                                _i32, _i32, _vp, _i64, _vp]),
+    "rgd_rmsnorm_bwd_static": (_i32, [_i32, _pRows, _pvp, _pi64, _pRows, _pRows, _pvp, _pi32, _pi64, _pi64, _i64, _f32,
+                                      _i32, _i32, _vp]),
     "rgd_headln_fwd": (_i32, [_pHeads, _pHeads, _pHeads, _pHeads, _i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "rgd_headln_bwd": (_i32, [_pHeads] * 6 + [_i64, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "rgd_rope": (_i32, [_pHeads, _pHeads, _vp, _i64, _i64, _pHeads, _pHeads] + [_i64] * 9 + [_i32, _i32, _i32, _vp]),

@@ -14,6 +14,8 @@
 // CTA; a second kernel adds the partial rows in a fixed order.  That replaces
 // the reference's spin-lock accumulation (rmsnorm_cached.py:245-264) by a
 // deterministic two-stage reduce.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace rgd {
@@ -552,4 +554,66 @@ extern "C" int rgd_rmsnorm_bwd(int nstreams, const rgd_rows *x, const void *cons
     dw_reduce_kernel<<<grid, block, 0, st>>>(rp);
     count_launch();
     return check_launch();
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm backward without any allocation by anybody.
+//
+// rgd_rmsnorm_bwd needs a scratch buffer for its per-CTA dweight partial rows,
+// which the caller normally allocates.  Some callers cannot allocate device
+// memory at the point where they need the backward: a plugin inside a host
+// application that hands out all device memory at start-up and forbids
+// cudaMalloc afterwards, or a section of a serving / training loop that must
+// not incur the implicit device synchronisation and latency of an allocation.
+// For them the scratch lives in this fixed-size device array, which every GPU
+// that loads the library holds from load until the process exits.
+//
+// The array's name is usable directly only in device code.  On the host it is a
+// stand-in, not a device address, so the address is fetched once per device
+// with cudaGetSymbolAddress (with that device current) and passed on.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_rms_bwd_static_scratch[RGD_RMSNORM_BWD_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+void *g_static_scratch_addr[64] = {nullptr};
+
+// Device address of the static scratch on the CURRENT device; looked up on the
+// first call per device, cached afterwards.  Returns a status code.
+int static_scratch_address(void **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (dev < 0 || dev >= 64) return RGD_E_DEVICE;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress((void **)&ptr, g_rms_bwd_static_scratch);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            return cuda_status(e);
+        }
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return RGD_OK;
+}
+}  // namespace
+
+extern "C" int rgd_rmsnorm_bwd_static(int nstreams, const rgd_rows *x, const void *const *w,
+                                      const int64_t *w_stride_b, const rgd_rows *dy, const rgd_rows *dx,
+                                      void *const *dw, const int *dw_per_batch, const int64_t *N,
+                                      const int64_t *C, int64_t B, float eps, int x_dtype, int w_dtype,
+                                      void *stream) {
+    if (nstreams < 1 || nstreams > 2 || !N || !C || B < 0) return RGD_E_INVALID;
+    const int64_t need = rgd_rmsnorm_bwd_workspace_bytes(nstreams, N, C, B);
+    if (need < 0) return (int)need;
+    // Sizes whose partial rows do not fit the fixed array are refused, not truncated.
+    if (need > (int64_t)RGD_RMSNORM_BWD_STATIC_SCRATCH_BYTES) return RGD_E_WORKSPACE;
+    void *scratch = nullptr;
+    if (int e = static_scratch_address(&scratch)) return e;
+    // Nothing in the scratch has to start at zero: every partial row the reduce
+    // reads is first written in full by the CTA that owns it.
+    return rgd_rmsnorm_bwd(nstreams, x, w, w_stride_b, dy, dx, dw, dw_per_batch, N, C, B, eps, x_dtype, w_dtype,
+                           scratch, (int64_t)RGD_RMSNORM_BWD_STATIC_SCRATCH_BYTES, stream);
 }
