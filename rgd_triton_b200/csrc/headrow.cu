@@ -33,15 +33,24 @@ struct HeadTensor {
     int64_t rows;       // B * D1 * D2
 };
 
+// Fast division of a 31-bit unsigned value by a runtime constant
+// (q = umulhi(n, mul) >> shr), precomputed on the host.
+struct FastDiv {
+    uint32_t mul, shr, div;
+};
+
 struct HeadParams {
     HeadTensor t[2];
-    int64_t split;      // CTAs that belong to tensor 0
+    int64_t split;      // tiles that belong to tensor 0
+    int64_t tiles1;     // tiles that belong to tensor 1
+    FastDiv f1[2], f2[2];   // fast divisors by D1 / D2 of each tensor
     int d;              // head_dim
     int tpr;            // threads per row (power of two <= 32)
     int R;              // rotary channels
     const void *pos;    // [2, P, R]: sin, cos
     int64_t pos_ss, pos_sn;
     int transposed;     // rotary: apply the inverse rotation
+    int flat;           // every tensor is densely packed rows of d channels in walk order
     float eps;
 };
 
@@ -65,10 +74,36 @@ __device__ __forceinline__ void load_table(const TP *row, int col, int R, bool v
     }
 }
 
-// T: tensor element type.  TP: table element type (T or float).  VE: elements
-// per access (16 / sizeof(T), or 1).  VPT: column slots per thread.
-template <typename T, typename TP, int VE, int VPT, int OP>
-__global__ void __launch_bounds__(HEAD_THREADS, (OP == LN_BWD || OP == LNROPE_BWD) ? 3 : 4) head_kernel(const __grid_constant__ HeadParams p) {
+__device__ __forceinline__ uint32_t fdiv(uint32_t n, const FastDiv &f) {
+    return f.div == 1 ? n : (__umulhi(n, f.mul) >> f.shr);
+}
+
+// Row id -> (batch, outer, inner) indices of a head tensor.
+__device__ __forceinline__ void row_index(const HeadTensor &ht, const FastDiv &f1, const FastDiv &f2, int64_t rid,
+                                          int64_t &b, int &i1, int &i2) {
+    if (ht.rows <= 0x7fffffffLL) {
+        const uint32_t r32 = (uint32_t)rid;
+        const uint32_t q1 = fdiv(r32, f2);
+        i2 = (int)(r32 - q1 * f2.div);
+        const uint32_t q2 = fdiv(q1, f1);
+        i1 = (int)(q1 - q2 * f1.div);
+        b = q2;
+    } else {
+        i2 = (int)(rid % ht.D2);
+        const int64_t q1 = rid / ht.D2;
+        i1 = (int)(q1 % ht.D1);
+        b = q1 / ht.D1;
+    }
+}
+
+// One row: xq (and gq, the upstream gradient) hold this thread's packed slots;
+// the result comes back packed in `out`.  T: tensor element type.  TP: table
+// element type (T or float).  VE: elements per access (16 / sizeof(T), or 1).
+// VPT: column slots per thread.
+template <typename T, typename TP, int VE, int VPT, int OP, int DFIX = 0>
+__device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE> (&xq)[VPT],
+                                            const Vec<T, VE> (&gq)[VPT], int tok, int cut, int t, bool pos_vec_ok,
+                                            Vec<T, VE> (&out)[VPT]) {
     constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
     constexpr bool HAS_ROPE = (OP == ROPE || OP == LNROPE_FWD || OP == LNROPE_BWD);
     constexpr bool HAS_LN = (OP != ROPE);
@@ -76,172 +111,70 @@ __global__ void __launch_bounds__(HEAD_THREADS, (OP == LN_BWD || OP == LNROPE_BW
     // (head_rope_cached.py:48,142): 16-bit x with a 16-bit table rounds after
     // every multiply and add; anything else is plain fp32.
     constexpr bool ROUND_EACH = (OP == ROPE) && (sizeof(T) == 2) && (sizeof(TP) == 2);
-    using V = Vec<T, VE>;
     constexpr int NE = VPT * VE;
-
-    const int ti = (int64_t)blockIdx.x >= p.split ? 1 : 0;
-    const HeadTensor &ht = p.t[ti];
-    const int64_t local = (int64_t)blockIdx.x - (ti ? p.split : 0);
-    const int tpr = p.tpr;
-    const int rpc = HEAD_THREADS / tpr;                 // rows per CTA pass
-    const int rg = (int)threadIdx.x / tpr;
-    const int t = (int)threadIdx.x - rg * tpr;
-    const int d = p.d;
+    // DFIX > 0: head_dim is a compile-time constant that fills the slots exactly,
+    // so the group width and every bounds check fold away.
+    const int tpr = DFIX > 0 ? DFIX / NE : p.tpr;
+    const int d = DFIX > 0 ? DFIX : p.d;
     const float invd = 1.0f / (float)d;
-    const bool pos_vec_ok = (reinterpret_cast<uintptr_t>(p.pos) % 16 == 0) &&
-                            (p.pos_ss % (16 / (int)sizeof(TP)) == 0) && (p.pos_sn % (16 / (int)sizeof(TP)) == 0);
 
-    // Loaded rows stay packed (16 bytes per slot) until their turn to be
-    // processed: that keeps the register count low enough for 4 CTAs per SM.
-    V xq[ROWS_PER_THREAD][VPT];
-    V gq[HAS_DY ? ROWS_PER_THREAD : 1][VPT];
-    int64_t ooff[ROWS_PER_THREAD];
-    int tok[ROWS_PER_THREAD];
-    bool valid[ROWS_PER_THREAD];
-
-    // ---- issue all loads first --------------------------------------------
+    float xv[NE];
+    float dv[HAS_DY ? NE : 1];
 #pragma unroll
-    for (int r = 0; r < ROWS_PER_THREAD; ++r) {
-        const int64_t rid = (local * ROWS_PER_THREAD + r) * rpc + rg;
-        valid[r] = rid < ht.rows;
-        const int64_t rr = valid[r] ? rid : 0;
-        int i1, i2;
-        int64_t b;
-        if (ht.rows <= 0x7fffffffLL) {             // 32-bit divisions for every realistic size
-            const unsigned r32 = (unsigned)rr;
-            const unsigned q1 = r32 / (unsigned)ht.D2;
-            i2 = (int)(r32 - q1 * (unsigned)ht.D2);
-            const unsigned q2 = q1 / (unsigned)ht.D1;
-            i1 = (int)(q1 - q2 * (unsigned)ht.D1);
-            b = q2;
-        } else {
-            i2 = (int)(rr % ht.D2);
-            const int64_t q1 = rr / ht.D2;
-            i1 = (int)(q1 % ht.D1);
-            b = q1 / ht.D1;
+    for (int j = 0; j < VPT; ++j)
+#pragma unroll
+        for (int e = 0; e < VE; ++e) {
+            xv[j * VE + e] = to_f32<T>(xq[j].v[e]);
+            if constexpr (HAS_DY) dv[j * VE + e] = to_f32<T>(gq[j].v[e]);
         }
-        tok[r] = ht.seq_inner ? i2 : i1;
-        const T *xr = reinterpret_cast<const T *>(ht.x) + b * ht.xb + (int64_t)i1 * ht.x1 + (int64_t)i2 * ht.x2;
-        const T *dr = HAS_DY ? reinterpret_cast<const T *>(ht.dy) + b * ht.db + (int64_t)i1 * ht.d1 + (int64_t)i2 * ht.d2
-                             : nullptr;
-        ooff[r] = b * ht.ob + (int64_t)i1 * ht.o1 + (int64_t)i2 * ht.o2;
+    float mean = 0.f, rstd = 1.f;
+    if (HAS_LN) {
+        // head_layernorm_cached.py:85-99 / fused_ln_rope_cached.py:66-74
+        float s = 0.f;
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            const int col = (t + j * tpr) * VE;
-            if (valid[r] && col < d) {
-                xq[r][j] = load_vec_stream<T, VE>(xr + col);
-                if constexpr (HAS_DY) gq[r][j] = load_vec_stream<T, VE>(dr + col);
-            } else {
-#pragma unroll
-                for (int e = 0; e < VE; ++e) {
-                    xq[r][j].v[e] = from_f32<T>(0.f);
-                    if constexpr (HAS_DY) gq[r][j].v[e] = from_f32<T>(0.f);
-                }
-            }
-        }
-    }
-
-    // ---- per row -------------------------------------------------------------
-#pragma unroll
-    for (int r = 0; r < ROWS_PER_THREAD; ++r) {
-        float xv[NE];
-        float dv[HAS_DY ? NE : 1];
+        for (int i = 0; i < NE; ++i) s += xv[i];
+        mean = warp_group_sum(s, tpr) * invd;
+        float s2 = 0.f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j)
 #pragma unroll
             for (int e = 0; e < VE; ++e) {
-                xv[j * VE + e] = to_f32<T>(xq[r][j].v[e]);
-                if constexpr (HAS_DY) dv[j * VE + e] = to_f32<T>(gq[r][j].v[e]);
+                const int col = (t + j * tpr) * VE + e;
+                const float c = col < d ? xv[j * VE + e] - mean : 0.f;
+                xv[j * VE + e] = c;           // centred
+                s2 += c * c;
             }
-        float mean = 0.f, rstd = 1.f;
-        if (HAS_LN) {
-            // head_layernorm_cached.py:85-99 / fused_ln_rope_cached.py:66-74
-            float s = 0.f;
+        rstd = rsqrtf(warp_group_sum(s2, tpr) * invd + p.eps);
 #pragma unroll
-            for (int i = 0; i < NE; ++i) s += xv[i];
-            mean = warp_group_sum(s, tpr) * invd;
-            float s2 = 0.f;
+        for (int i = 0; i < NE; ++i) xv[i] *= rstd;   // xhat
+    }
+
+    const bool rot_row = HAS_ROPE && tok < cut;
+    float res[NE];
+
+    // Scalar mode: the rotation partner (channel c ^ 1) lives in the
+    // neighbouring lane.  Exchange it unconditionally so that every lane
+    // of the warp takes part in the shuffle.
+    float oth[(VE == 1 && HAS_ROPE) ? NE : 1];
+    if constexpr (VE == 1 && HAS_ROPE) {
 #pragma unroll
-            for (int j = 0; j < VPT; ++j)
-#pragma unroll
-                for (int e = 0; e < VE; ++e) {
-                    const int col = (t + j * tpr) * VE + e;
-                    const float c = col < d ? xv[j * VE + e] - mean : 0.f;
-                    xv[j * VE + e] = c;           // centred
-                    s2 += c * c;
-                }
-            rstd = rsqrtf(warp_group_sum(s2, tpr) * invd + p.eps);
-#pragma unroll
-            for (int i = 0; i < NE; ++i) xv[i] *= rstd;   // xhat
+        for (int j = 0; j < NE; ++j) {
+            float mine;
+            if constexpr (OP == LNROPE_BWD) mine = dv[j]; else mine = xv[j];
+            oth[j] = __shfl_xor_sync(0xffffffffu, mine, 1);
         }
+    }
 
-        const bool rot_row = HAS_ROPE && tok[r] < ht.cut;
-        float res[NE];
-
-        // Scalar mode: the rotation partner (channel c ^ 1) lives in the
-        // neighbouring lane.  Exchange it unconditionally so that every lane
-        // of the warp takes part in the shuffle.
-        float oth[(VE == 1 && HAS_ROPE) ? NE : 1];
-        if constexpr (VE == 1 && HAS_ROPE) {
+    if constexpr (OP == LN_FWD) {
 #pragma unroll
-            for (int j = 0; j < NE; ++j) {
-                float mine;
-                if constexpr (OP == LNROPE_BWD) mine = dv[j]; else mine = xv[j];
-                oth[j] = __shfl_xor_sync(0xffffffffu, mine, 1);
-            }
-        }
-
-        if constexpr (OP == LN_FWD) {
-#pragma unroll
-            for (int i = 0; i < NE; ++i) res[i] = xv[i];
-        } else if constexpr (OP == LN_BWD || OP == LNROPE_BWD) {
-            float *g = dv;
-            if constexpr (OP == LNROPE_BWD) {
-                if (rot_row) {
-                    // Inverse rotation of the upstream gradient (fused_ln_rope_cached.py:349-360).
-                    const TP *srow = reinterpret_cast<const TP *>(p.pos) + (int64_t)tok[r] * p.pos_sn;
-                    const TP *crow = srow + p.pos_ss;
-#pragma unroll
-                    for (int j = 0; j < VPT; ++j) {
-                        const int col = (t + j * tpr) * VE;
-                        if (col < p.R) {
-                            float sn[VE], cs[VE];
-                            load_table<TP, VE>(srow, col, p.R, pos_vec_ok, sn);
-                            load_table<TP, VE>(crow, col, p.R, pos_vec_ok, cs);
-                            if constexpr (VE > 1) {
-#pragma unroll
-                                for (int e = 0; e < VE; e += 2) {
-                                    const float ge = g[j * VE + e], go = g[j * VE + e + 1];
-                                    if (col + e < p.R) g[j * VE + e] = ge * cs[e] + go * sn[e];
-                                    if (col + e + 1 < p.R) g[j * VE + e + 1] = go * cs[e + 1] - ge * sn[e + 1];
-                                }
-                            } else {
-                                const float me = g[j];
-                                g[j] = (col & 1) ? me * cs[0] - oth[j] * sn[0] : me * cs[0] + oth[j] * sn[0];
-                            }
-                        }
-                    }
-                }
-            }
-            // head_layernorm_cached.py:193-199 / fused_ln_rope_cached.py:100-114
-            float sa = 0.f, sb = 0.f;
-#pragma unroll
-            for (int i = 0; i < NE; ++i) {
-                sa += xv[i] * g[i];
-                sb += g[i];
-            }
-            const float a = warp_group_sum(sa, tpr) * invd;
-            const float bm = warp_group_sum(sb, tpr) * invd;
-#pragma unroll
-            for (int i = 0; i < NE; ++i) res[i] = (g[i] - xv[i] * a - bm) * rstd;
-        } else {
-            // ROPE or LNROPE_FWD: rotate xv (raw x, or xhat).
-#pragma unroll
-            for (int i = 0; i < NE; ++i) res[i] = xv[i];
+        for (int i = 0; i < NE; ++i) res[i] = xv[i];
+    } else if constexpr (OP == LN_BWD || OP == LNROPE_BWD) {
+        float *g = dv;
+        if constexpr (OP == LNROPE_BWD) {
             if (rot_row) {
-                const TP *srow = reinterpret_cast<const TP *>(p.pos) + (int64_t)tok[r] * p.pos_sn;
+                // Inverse rotation of the upstream gradient (fused_ln_rope_cached.py:349-360).
+                const TP *srow = reinterpret_cast<const TP *>(p.pos) + (int64_t)tok * p.pos_sn;
                 const TP *crow = srow + p.pos_ss;
-                const bool inv = (OP == ROPE) && p.transposed;
 #pragma unroll
                 for (int j = 0; j < VPT; ++j) {
                     const int col = (t + j * tpr) * VE;
@@ -252,49 +185,376 @@ __global__ void __launch_bounds__(HEAD_THREADS, (OP == LN_BWD || OP == LNROPE_BW
                         if constexpr (VE > 1) {
 #pragma unroll
                             for (int e = 0; e < VE; e += 2) {
-                                const float xe = xv[j * VE + e], xo = xv[j * VE + e + 1];
-                                // rotated partner: (-x_odd, x_even), sign flipped for the inverse
-                                const float re = inv ? xo : -xo;
-                                const float ro = inv ? -xe : xe;
-                                float oe, oo;
-                                if constexpr (ROUND_EACH) {
-                                    oe = round_to<T>(round_to<T>(xe * cs[e]) + round_to<T>(re * sn[e]));
-                                    oo = round_to<T>(round_to<T>(xo * cs[e + 1]) + round_to<T>(ro * sn[e + 1]));
-                                } else {
-                                    oe = xe * cs[e] + re * sn[e];
-                                    oo = xo * cs[e + 1] + ro * sn[e + 1];
-                                }
-                                if (col + e < p.R) res[j * VE + e] = oe;
-                                if (col + e + 1 < p.R) res[j * VE + e + 1] = oo;
+                                const float ge = g[j * VE + e], go = g[j * VE + e + 1];
+                                if (col + e < p.R) g[j * VE + e] = ge * cs[e] + go * sn[e];
+                                if (col + e + 1 < p.R) g[j * VE + e + 1] = go * cs[e + 1] - ge * sn[e + 1];
                             }
                         } else {
-                            const float me = xv[j];
-                            float rot = (col & 1) ? oth[j] : -oth[j];
-                            if (inv) rot = -rot;
-                            if constexpr (ROUND_EACH)
-                                res[j] = round_to<T>(round_to<T>(me * cs[0]) + round_to<T>(rot * sn[0]));
-                            else
-                                res[j] = me * cs[0] + rot * sn[0];
+                            const float me = g[j];
+                            g[j] = (col & 1) ? me * cs[0] - oth[j] * sn[0] : me * cs[0] + oth[j] * sn[0];
                         }
                     }
                 }
             }
         }
-
-        if (valid[r]) {
-            T *orow = reinterpret_cast<T *>(ht.out) + ooff[r];
+        // head_layernorm_cached.py:193-199 / fused_ln_rope_cached.py:100-114
+        float sa = 0.f, sb = 0.f;
+#pragma unroll
+        for (int i = 0; i < NE; ++i) {
+            sa += xv[i] * g[i];
+            sb += g[i];
+        }
+        const float a = warp_group_sum(sa, tpr) * invd;
+        const float bm = warp_group_sum(sb, tpr) * invd;
+#pragma unroll
+        for (int i = 0; i < NE; ++i) res[i] = (g[i] - xv[i] * a - bm) * rstd;
+    } else {
+        // ROPE or LNROPE_FWD: rotate xv (raw x, or xhat).
+#pragma unroll
+        for (int i = 0; i < NE; ++i) res[i] = xv[i];
+        if (rot_row) {
+            const TP *srow = reinterpret_cast<const TP *>(p.pos) + (int64_t)tok * p.pos_sn;
+            const TP *crow = srow + p.pos_ss;
+            const bool inv = (OP == ROPE) && p.transposed;
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const int col = (t + j * tpr) * VE;
-                if (col < d) {
-                    V o;
+                if (col < p.R) {
+                    float sn[VE], cs[VE];
+                    load_table<TP, VE>(srow, col, p.R, pos_vec_ok, sn);
+                    load_table<TP, VE>(crow, col, p.R, pos_vec_ok, cs);
+                    if constexpr (VE > 1) {
 #pragma unroll
-                    for (int e = 0; e < VE; ++e) o.v[e] = from_f32<T>(res[j * VE + e]);
-                    store_vec_stream<T, VE>(orow + col, o);
+                        for (int e = 0; e < VE; e += 2) {
+                            const float xe = xv[j * VE + e], xo = xv[j * VE + e + 1];
+                            // rotated partner: (-x_odd, x_even), sign flipped for the inverse
+                            const float re = inv ? xo : -xo;
+                            const float ro = inv ? -xe : xe;
+                            float oe, oo;
+                            if constexpr (ROUND_EACH) {
+                                oe = round_to<T>(round_to<T>(xe * cs[e]) + round_to<T>(re * sn[e]));
+                                oo = round_to<T>(round_to<T>(xo * cs[e + 1]) + round_to<T>(ro * sn[e + 1]));
+                            } else {
+                                oe = xe * cs[e] + re * sn[e];
+                                oo = xo * cs[e + 1] + ro * sn[e + 1];
+                            }
+                            if (col + e < p.R) res[j * VE + e] = oe;
+                            if (col + e + 1 < p.R) res[j * VE + e + 1] = oo;
+                        }
+                    } else {
+                        const float me = xv[j];
+                        float rot = (col & 1) ? oth[j] : -oth[j];
+                        if (inv) rot = -rot;
+                        if constexpr (ROUND_EACH)
+                            res[j] = round_to<T>(round_to<T>(me * cs[0]) + round_to<T>(rot * sn[0]));
+                        else
+                            res[j] = me * cs[0] + rot * sn[0];
+                    }
                 }
             }
         }
     }
+
+
+#pragma unroll
+    for (int j = 0; j < VPT; ++j)
+#pragma unroll
+        for (int e = 0; e < VE; ++e) out[j].v[e] = from_f32<T>(res[j * VE + e]);
+}
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+                 "l"(gsrc)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Direct kernel: one tile (rows-per-CTA x ROWS_PER_THREAD rows) per CTA, loads
+// straight into registers.  Used for rows that are not 16-byte addressable.
+template <typename T, typename TP, int VE, int VPT, int OP>
+__global__ void __launch_bounds__(HEAD_THREADS) head_kernel(const __grid_constant__ HeadParams p) {
+    constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
+    using V = Vec<T, VE>;
+
+    const int ti = (int64_t)blockIdx.x >= p.split ? 1 : 0;
+    const HeadTensor &ht = p.t[ti];
+    const int64_t local = (int64_t)blockIdx.x - (ti ? p.split : 0);
+    const int tpr = p.tpr;
+    const int rpc = HEAD_THREADS / tpr;                 // rows per CTA pass
+    const int rg = (int)threadIdx.x / tpr;
+    const int t = (int)threadIdx.x - rg * tpr;
+    const int d = p.d;
+    const bool pos_vec_ok = (reinterpret_cast<uintptr_t>(p.pos) % 16 == 0) &&
+                            (p.pos_ss % (16 / (int)sizeof(TP)) == 0) && (p.pos_sn % (16 / (int)sizeof(TP)) == 0);
+
+#pragma unroll 1
+    for (int r = 0; r < ROWS_PER_THREAD; ++r) {
+        const int64_t rid = (local * ROWS_PER_THREAD + r) * rpc + rg;
+        const bool valid = rid < ht.rows;
+        int64_t b;
+        int i1, i2;
+        row_index(ht, p.f1[ti], p.f2[ti], valid ? rid : 0, b, i1, i2);
+        const int tok = ht.seq_inner ? i2 : i1;
+        const T *xr = reinterpret_cast<const T *>(ht.x) + b * ht.xb + (int64_t)i1 * ht.x1 + (int64_t)i2 * ht.x2;
+        const T *dr = HAS_DY ? reinterpret_cast<const T *>(ht.dy) + b * ht.db + (int64_t)i1 * ht.d1 + (int64_t)i2 * ht.d2
+                             : nullptr;
+        V xq[VPT], gq[VPT], res[VPT];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int col = (t + j * tpr) * VE;
+            if (valid && col < d) {
+                xq[j] = load_vec<T, VE>(xr + col);
+                if constexpr (HAS_DY) gq[j] = load_vec<T, VE>(dr + col);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    xq[j].v[e] = from_f32<T>(0.f);
+                    gq[j].v[e] = from_f32<T>(0.f);
+                }
+            }
+        }
+        process_row<T, TP, VE, VPT, OP>(p, xq, gq, tok, ht.cut, t, pos_vec_ok, res);
+        if (valid) {
+            T *orow = reinterpret_cast<T *>(ht.out) + b * ht.ob + (int64_t)i1 * ht.o1 + (int64_t)i2 * ht.o2;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int col = (t + j * tpr) * VE;
+                if (col < d) store_vec<T, VE>(orow + col, res[j]);
+            }
+        }
+    }
+}
+
+// Pipelined kernel for 16-byte addressable rows: persistent CTAs walk the tiles
+// of both tensors; the 16-byte pieces of the next PIPE_STAGES-1 tiles are in
+// flight (cp.async) into per-thread shared-memory slots while the current tile
+// is normalised / rotated from registers and stored with streaming stores.
+// Each thread reads back only the slots it filled itself, so no block-level
+// barrier is needed; cp.async.wait_group orders a thread's own copies.
+constexpr int PIPE_STAGES = 3;
+
+template <typename T, typename TP, int VPT, int OP>
+__global__ void __launch_bounds__(HEAD_THREADS) head_kernel_pipelined(const __grid_constant__ HeadParams p) {
+    constexpr int VE = VecElems<T>::value;
+    constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
+    constexpr int NIN = HAS_DY ? 2 : 1;
+    constexpr int SLOTS = NIN * ROWS_PER_THREAD * VPT;   // 16-byte slots per thread and stage
+    using V = Vec<T, VE>;
+    extern __shared__ uint4 slots[];                     // [PIPE_STAGES][SLOTS][HEAD_THREADS]
+
+    const int tpr = p.tpr;
+    const int rpc = HEAD_THREADS / tpr;
+    const int rg = (int)threadIdx.x / tpr;
+    const int t = (int)threadIdx.x - rg * tpr;
+    const int d = p.d;
+    const int64_t total = p.split + p.tiles1;
+    const bool pos_vec_ok = (reinterpret_cast<uintptr_t>(p.pos) % 16 == 0) &&
+                            (p.pos_ss % (16 / (int)sizeof(TP)) == 0) && (p.pos_sn % (16 / (int)sizeof(TP)) == 0);
+    auto slot = [&](int stage, int idx) -> uint4 * {
+        return slots + ((size_t)stage * SLOTS + idx) * HEAD_THREADS + threadIdx.x;
+    };
+
+    auto issue = [&](int64_t tile, int stage) {
+        const int ti = tile >= p.split ? 1 : 0;
+        const HeadTensor &ht = p.t[ti];
+        const int64_t local = tile - (ti ? p.split : 0);
+#pragma unroll
+        for (int r = 0; r < ROWS_PER_THREAD; ++r) {
+            const int64_t rid = (local * ROWS_PER_THREAD + r) * rpc + rg;
+            const bool valid = rid < ht.rows;
+            int64_t b;
+            int i1, i2;
+            row_index(ht, p.f1[ti], p.f2[ti], valid ? rid : 0, b, i1, i2);
+            const T *xr = reinterpret_cast<const T *>(ht.x) + b * ht.xb + (int64_t)i1 * ht.x1 + (int64_t)i2 * ht.x2;
+            const T *dr = HAS_DY ? reinterpret_cast<const T *>(ht.dy) + b * ht.db + (int64_t)i1 * ht.d1 +
+                                       (int64_t)i2 * ht.d2
+                                 : nullptr;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int col = (t + j * tpr) * VE;
+                if (valid && col < d) {
+                    cp_async16(slot(stage, r * VPT + j), xr + col);
+                    if constexpr (HAS_DY) cp_async16(slot(stage, (ROWS_PER_THREAD + r) * VPT + j), dr + col);
+                }
+            }
+        }
+    };
+
+    auto consume = [&](int64_t tile, int stage) {
+        const int ti = tile >= p.split ? 1 : 0;
+        const HeadTensor &ht = p.t[ti];
+        const int64_t local = tile - (ti ? p.split : 0);
+#pragma unroll
+        for (int r = 0; r < ROWS_PER_THREAD; ++r) {
+            const int64_t rid = (local * ROWS_PER_THREAD + r) * rpc + rg;
+            const bool valid = rid < ht.rows;
+            int64_t b;
+            int i1, i2;
+            row_index(ht, p.f1[ti], p.f2[ti], valid ? rid : 0, b, i1, i2);
+            const int tok = ht.seq_inner ? i2 : i1;
+            V xq[VPT], gq[VPT], res[VPT];
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int col = (t + j * tpr) * VE;
+                union { uint4 u; V v; } cx, cg;
+                cx.u = make_uint4(0u, 0u, 0u, 0u);
+                cg.u = make_uint4(0u, 0u, 0u, 0u);
+                if (valid && col < d) {
+                    cx.u = *slot(stage, r * VPT + j);
+                    if constexpr (HAS_DY) cg.u = *slot(stage, (ROWS_PER_THREAD + r) * VPT + j);
+                }
+                xq[j] = cx.v;
+                gq[j] = cg.v;
+            }
+            process_row<T, TP, VE, VPT, OP>(p, xq, gq, tok, ht.cut, t, pos_vec_ok, res);
+            if (valid) {
+                T *orow = reinterpret_cast<T *>(ht.out) + b * ht.ob + (int64_t)i1 * ht.o1 + (int64_t)i2 * ht.o2;
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    const int col = (t + j * tpr) * VE;
+                    if (col < d) store_vec_stream<T, VE>(orow + col, res[j]);
+                }
+            }
+        }
+    };
+
+    const int64_t step = gridDim.x;
+    const int64_t tile0 = blockIdx.x;
+#pragma unroll
+    for (int s = 0; s < PIPE_STAGES - 1; ++s) {
+        if (tile0 + s * step < total) issue(tile0 + s * step, s);
+        cp_async_commit();
+    }
+    int stage = 0;
+    for (int64_t tile = tile0; tile < total; tile += step) {
+        const int64_t ahead = tile + (PIPE_STAGES - 1) * step;
+        int fill = stage + PIPE_STAGES - 1;
+        if (fill >= PIPE_STAGES) fill -= PIPE_STAGES;
+        if (ahead < total) issue(ahead, fill);
+        cp_async_commit();
+        cp_async_wait<PIPE_STAGES - 1>();      // this thread's copies for `tile` have landed
+        consume(tile, stage);
+        if (++stage == PIPE_STAGES) stage = 0;
+    }
+    cp_async_wait<0>();
+}
+
+// Flat kernel: the common case of densely packed tensors (x, dy and out are all
+// [rows, D] with pitch D in the same row order) and head_dim D known at compile
+// time.  Row r lives at base + r * D, so the per-row address arithmetic is one
+// multiply-add and the token index one or two fast divisions.  Same persistent
+// cp.async pipeline as head_kernel_pipelined.
+// Rows per thread and 16-byte slots per thread-row of the flat kernel.
+constexpr int FLAT_RPT = 2;
+constexpr int FLAT_VPT = 2;
+
+template <typename T, typename TP, int VPT, int OP, int D>
+__global__ void __launch_bounds__(HEAD_THREADS) head_kernel_flat(const __grid_constant__ HeadParams p) {
+    constexpr int VE = VecElems<T>::value;
+    constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
+    constexpr bool HAS_ROPE = (OP == ROPE || OP == LNROPE_FWD || OP == LNROPE_BWD);
+    constexpr int NIN = HAS_DY ? 2 : 1;
+    constexpr int TPR = D / (VE * VPT);                  // threads per row
+    constexpr int RPC = HEAD_THREADS / TPR;              // rows per CTA pass
+    constexpr int SLOTS = NIN * FLAT_RPT * VPT;
+    using V = Vec<T, VE>;
+    extern __shared__ uint4 slots[];                     // [PIPE_STAGES][SLOTS][HEAD_THREADS]
+
+    const int rg = (int)threadIdx.x / TPR;
+    const int t = (int)threadIdx.x - rg * TPR;
+    const int64_t total = p.split + p.tiles1;
+    const bool pos_vec_ok = (reinterpret_cast<uintptr_t>(p.pos) % 16 == 0) &&
+                            (p.pos_ss % (16 / (int)sizeof(TP)) == 0) && (p.pos_sn % (16 / (int)sizeof(TP)) == 0);
+    auto slot = [&](int stage, int idx) -> uint4 * {
+        return slots + ((size_t)stage * SLOTS + idx) * HEAD_THREADS + threadIdx.x;
+    };
+
+    auto issue = [&](int64_t tile, int stage) {
+        const int ti = tile >= p.split ? 1 : 0;
+        const HeadTensor &ht = p.t[ti];
+        const int64_t row0 = (tile - (ti ? p.split : 0)) * (FLAT_RPT * RPC) + rg;
+        const T *xb = reinterpret_cast<const T *>(ht.x) + t * VE;
+        const T *gb = HAS_DY ? reinterpret_cast<const T *>(ht.dy) + t * VE : nullptr;
+#pragma unroll
+        for (int r = 0; r < FLAT_RPT; ++r) {
+            const int64_t rid = row0 + r * RPC;
+            if (rid < ht.rows) {
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    cp_async16(slot(stage, r * VPT + j), xb + rid * D + j * TPR * VE);
+                    if constexpr (HAS_DY)
+                        cp_async16(slot(stage, (FLAT_RPT + r) * VPT + j), gb + rid * D + j * TPR * VE);
+                }
+            }
+        }
+    };
+
+    auto consume = [&](int64_t tile, int stage) {
+        const int ti = tile >= p.split ? 1 : 0;
+        const HeadTensor &ht = p.t[ti];
+        const int64_t row0 = (tile - (ti ? p.split : 0)) * (FLAT_RPT * RPC) + rg;
+        T *ob = reinterpret_cast<T *>(ht.out) + t * VE;
+        const FastDiv f2 = p.f2[ti], f1 = p.f1[ti];
+#pragma unroll
+        for (int r = 0; r < FLAT_RPT; ++r) {
+            const int64_t rid = row0 + r * RPC;
+            const bool valid = rid < ht.rows;
+            int tok = 0;
+            if constexpr (HAS_ROPE) {
+                // token index of the row: rows are (batch, outer, inner)-major
+                const uint32_t r32 = (uint32_t)(valid ? rid : 0);
+                const uint32_t q1 = fdiv(r32, f2);
+                if (ht.seq_inner) {
+                    tok = (int)(r32 - q1 * f2.div);
+                } else {
+                    const uint32_t q2 = fdiv(q1, f1);
+                    tok = (int)(q1 - q2 * f1.div);
+                }
+            }
+            V xq[VPT], gq[VPT], res[VPT];
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                union { uint4 u; V v; } cx, cg;
+                cx.u = make_uint4(0u, 0u, 0u, 0u);
+                cg.u = make_uint4(0u, 0u, 0u, 0u);
+                if (valid) {
+                    cx.u = *slot(stage, r * VPT + j);
+                    if constexpr (HAS_DY) cg.u = *slot(stage, (FLAT_RPT + r) * VPT + j);
+                }
+                xq[j] = cx.v;
+                gq[j] = cg.v;
+            }
+            process_row<T, TP, VE, VPT, OP, D>(p, xq, gq, tok, ht.cut, t, pos_vec_ok, res);
+            if (valid) {
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) store_vec_stream<T, VE>(ob + rid * D + j * TPR * VE, res[j]);
+            }
+        }
+    };
+
+    const int64_t step = gridDim.x;
+    const int64_t tile0 = blockIdx.x;
+#pragma unroll
+    for (int s = 0; s < PIPE_STAGES - 1; ++s) {
+        if (tile0 + s * step < total) issue(tile0 + s * step, s);
+        cp_async_commit();
+    }
+    int stage = 0;
+    for (int64_t tile = tile0; tile < total; tile += step) {
+        const int64_t ahead = tile + (PIPE_STAGES - 1) * step;
+        int fill = stage + PIPE_STAGES - 1;
+        if (fill >= PIPE_STAGES) fill -= PIPE_STAGES;
+        if (ahead < total) issue(ahead, fill);
+        cp_async_commit();
+        cp_async_wait<PIPE_STAGES - 1>();
+        consume(tile, stage);
+        if (++stage == PIPE_STAGES) stage = 0;
+    }
+    cp_async_wait<0>();
 }
 
 // ---------------------------------------------------------------------------
@@ -319,17 +579,77 @@ bool heads_vec_ok(const rgd_heads &v, int esize) {
     return is_aligned(v.ptr, 16) && v.stride_b % ve == 0 && v.stride_h % ve == 0 && v.stride_n % ve == 0;
 }
 
+FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f{0, 0, d};
+    if (d <= 1) return f;
+    uint32_t lg = 0;
+    while ((1ull << lg) < d) ++lg;                 // ceil(log2 d)
+    const uint32_t pw = 31 + lg;
+    f.mul = (uint32_t)(((1ull << pw) + d - 1) / d);
+    f.shr = pw - 32;
+    return f;
+}
+
+template <typename T, typename TP, int VPT, int OP>
+int launch_pipelined(const HeadParams &p, int64_t tiles, cudaStream_t st) {
+    constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
+    constexpr int SLOTS = (HAS_DY ? 2 : 1) * ROWS_PER_THREAD * VPT;
+    const size_t smem = (size_t)PIPE_STAGES * SLOTS * HEAD_THREADS * 16;
+    auto kernel = head_kernel_pipelined<T, TP, VPT, OP>;
+    if (smem > 32 * 1024)   // static shared memory counts towards the 48 KB default limit too
+        if (int e = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+            return e;
+    // Persistent grid: as many CTAs as fit (shared memory bound), never more than tiles.
+    int per_sm = (int)((200 * 1024) / smem);
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 8) per_sm = 8;
+    int64_t grid = (int64_t)num_sms() * per_sm;
+    if (grid > tiles) grid = tiles;
+    kernel<<<(unsigned)grid, HEAD_THREADS, smem, st>>>(p);
+    count_launch();
+    return check_launch();
+}
+
+template <typename T, typename TP, int VPT, int OP, int D>
+int launch_flat(const HeadParams &p, int64_t tiles, cudaStream_t st) {
+    constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
+    constexpr int SLOTS = (HAS_DY ? 2 : 1) * FLAT_RPT * VPT;
+    const size_t smem = (size_t)PIPE_STAGES * SLOTS * HEAD_THREADS * 16;
+    auto kernel = head_kernel_flat<T, TP, VPT, OP, D>;
+    if (smem > 32 * 1024)
+        if (int e = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+            return e;
+    int per_sm = (int)((200 * 1024) / smem);
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 8) per_sm = 8;
+    int64_t grid = (int64_t)num_sms() * per_sm;
+    if (grid > tiles) grid = tiles;
+    kernel<<<(unsigned)grid, HEAD_THREADS, smem, st>>>(p);
+    count_launch();
+    return check_launch();
+}
+
 template <typename T, typename TP, int OP>
 int launch_head(const HeadParams &p, bool vec, int vpt, int64_t grid, cudaStream_t st) {
-    constexpr int VE = VecElems<T>::value;
     if (grid > INT32_MAX) return RGD_E_SIZE;
+    if (p.flat && (p.d == 64 || p.d == 128)) {
+        // tiles were counted for p.tpr threads per row; recount for the flat geometry
+        constexpr int VE = VecElems<T>::value;
+        int64_t tiles[2];
+        HeadParams q = p;
+        for (int i = 0; i < 2; ++i) {
+            const int rows_per_tile = (HEAD_THREADS / (p.d / (VE * FLAT_VPT))) * FLAT_RPT;
+            tiles[i] = ceil_div64(p.t[i].rows, rows_per_tile);
+        }
+        q.split = tiles[0];
+        q.tiles1 = tiles[1];
+        if (p.d == 128) return launch_flat<T, TP, FLAT_VPT, OP, 128>(q, tiles[0] + tiles[1], st);
+        return launch_flat<T, TP, FLAT_VPT, OP, 64>(q, tiles[0] + tiles[1], st);
+    }
     if (vec) {
-        if (vpt == 1)
-            head_kernel<T, TP, VE, 1, OP><<<(unsigned)grid, HEAD_THREADS, 0, st>>>(p);
-        else if (vpt == 2)
-            head_kernel<T, TP, VE, 2, OP><<<(unsigned)grid, HEAD_THREADS, 0, st>>>(p);
-        else
-            return RGD_E_SIZE;
+        if (vpt == 1) return launch_pipelined<T, TP, 1, OP>(p, grid, st);
+        if (vpt == 2) return launch_pipelined<T, TP, 2, OP>(p, grid, st);
+        return RGD_E_SIZE;
     } else {
         if (vpt <= 4)
             head_kernel<T, TP, 1, 4, OP><<<(unsigned)grid, HEAD_THREADS, 0, st>>>(p);
@@ -415,6 +735,7 @@ int run_head(const HeadCall &c, cudaStream_t st) {
 
     const int rows_per_cta = (HEAD_THREADS / p.tpr) * ROWS_PER_THREAD;
     int64_t grid = 0;
+    bool all_flat = vec && (c.d * esize) % (16 * FLAT_VPT) == 0;
     for (int i = 0; i < 2; ++i) {
         HeadTensor &ht = p.t[i];
         const rgd_heads &x = *c.x[i];
@@ -443,11 +764,23 @@ int run_head(const HeadCall &c, cudaStream_t st) {
         ht.rows = c.B * c.H * c.N[i];
         if (ht.D1 == 0) ht.D1 = 1;
         if (ht.D2 == 0) ht.D2 = 1;
+        {
+            // dense [B][D1][D2][d] in walk order, for x, out and (backward) dy alike
+            auto dense = [&](int64_t sb, int64_t s1, int64_t s2) {
+                return s2 == c.d && s1 == (int64_t)ht.D2 * c.d && sb == (int64_t)ht.D1 * ht.D2 * c.d;
+            };
+            bool f = dense(ht.xb, ht.x1, ht.x2) && dense(ht.ob, ht.o1, ht.o2) && ht.rows <= 0x7fffffffLL;
+            if (HAS_DY) f = f && dense(ht.db, ht.d1, ht.d2);
+            if (c.N[i] > 0 && !f) all_flat = false;
+        }
+        p.f1[i] = make_fastdiv((uint32_t)ht.D1);
+        p.f2[i] = make_fastdiv((uint32_t)ht.D2);
         const int64_t ctas = ceil_div64(ht.rows, rows_per_cta);
-        if (i == 0) p.split = ctas;
+        if (i == 0) p.split = ctas; else p.tiles1 = ctas;
         grid += ctas;
     }
     if (grid == 0) return RGD_OK;
+    p.flat = all_flat ? 1 : 0;
     return dispatch_head<OP>(c, p, vec, vpt, grid, st);
 }
 

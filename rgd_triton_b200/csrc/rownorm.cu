@@ -62,11 +62,24 @@ __device__ __forceinline__ float group_sum(float v, int tpr, float (*red)[8], in
 
 // T: element type.  VE: elements per access (16 bytes / sizeof(T), or 1 for
 // rows that are not 16-byte addressable).  VPT: column slots per thread.
-template <typename T, int VE, int VPT, int OP>
+// PIPE: the 16-byte pieces of the next ROW_STAGES-1 rows are kept in flight with
+// cp.async into per-thread shared-memory slots while the current row is
+// processed (each thread reads back only slots it filled itself).
+constexpr int ROW_STAGES = 3;
+
+__device__ __forceinline__ void row_cp_async16(void *smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+                 "l"(gsrc)
+                 : "memory");
+}
+
+template <typename T, int VE, int VPT, int OP, bool PIPE>
 __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant__ RowParams p) {
     constexpr bool BWD = (OP == L2_BWD || OP == RMS_BWD);
     constexpr bool RMS = (OP == RMS_FWD || OP == RMS_BWD);
+    constexpr int SLOTS = (BWD ? 2 : 1) * VPT;
     using V = Vec<T, VE>;
+    extern __shared__ uint4 row_slots[];                 // PIPE: [ROW_STAGES][SLOTS][ROW_THREADS]
 
     __shared__ float red[2][8];
     __shared__ float dwred[OP == RMS_BWD ? ROW_THREADS * VE : 1];
@@ -106,6 +119,31 @@ __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant_
 
     const int step = s.P * rpc;
     const int iters = (s.N + step - 1) / step;
+    auto slot = [&](int stage, int idx) -> uint4 * {
+        return row_slots + ((size_t)stage * SLOTS + idx) * ROW_THREADS + threadIdx.x;
+    };
+    auto issue = [&](int it, int stage) {
+        const int n = it * step + chunk * rpc + rg;
+        if (n >= s.N) return;
+        const T *xr = xb + (int64_t)n * s.sxn;
+        const T *dr = BWD ? db + (int64_t)n * s.sdn : nullptr;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int col = (t + j * tpr) * VE;
+            if (col < C) {
+                row_cp_async16(slot(stage, j), xr + col);
+                if (BWD) row_cp_async16(slot(stage, VPT + j), dr + col);
+            }
+        }
+    };
+    if constexpr (PIPE) {
+#pragma unroll
+        for (int st = 0; st < ROW_STAGES - 1; ++st) {
+            if (st < iters) issue(st, st);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+    }
+    int stage = 0;
     for (int it = 0; it < iters; ++it) {
         const int n = it * step + chunk * rpc + rg;
         const bool valid = n < s.N;
@@ -114,12 +152,29 @@ __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant_
 
         V xq[VPT];
         V dq[BWD ? VPT : 1];
+        if constexpr (PIPE) {
+            int fill = stage + ROW_STAGES - 1;
+            if (fill >= ROW_STAGES) fill -= ROW_STAGES;
+            if (it + ROW_STAGES - 1 < iters) issue(it + ROW_STAGES - 1, fill);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group %0;" ::"n"(ROW_STAGES - 1) : "memory");
+        }
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int col = (t + j * tpr) * VE;
             if (valid && col < C) {
-                xq[j] = load_vec<T, VE>(xr + col);
-                if (BWD) dq[j] = load_vec<T, VE>(dr + col);
+                if constexpr (PIPE) {
+                    union { uint4 u; V v; } cx;
+                    cx.u = *slot(stage, j);
+                    xq[j] = cx.v;
+                    if (BWD) {
+                        cx.u = *slot(stage, VPT + j);
+                        dq[j] = cx.v;
+                    }
+                } else {
+                    xq[j] = load_vec<T, VE>(xr + col);
+                    if (BWD) dq[j] = load_vec<T, VE>(dr + col);
+                }
             } else {
 #pragma unroll
                 for (int e = 0; e < VE; ++e) {
@@ -127,6 +182,9 @@ __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant_
                     if (BWD) dq[j].v[e] = from_f32<T>(0.f);
                 }
             }
+        }
+        if constexpr (PIPE) {
+            if (++stage == ROW_STAGES) stage = 0;
         }
 
         float ss = 0.f;
@@ -160,7 +218,7 @@ __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant_
                     if (RMS) v = v * wv[j * VE + e];
                     yo.v[e] = from_f32<T>(v);
                 }
-                if (valid && col < C) store_vec<T, VE>(orow + col, yo);
+                if (valid && col < C) store_vec_stream<T, VE>(orow + col, yo);
             }
         } else {
             // g = sum(xhat * dy * w) [/ C for RMS]: rmsnorm_cached.py:213-231,
@@ -195,7 +253,7 @@ __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant_
                     }
                     yo.v[e] = from_f32<T>(v);
                 }
-                if (valid && col < C) store_vec<T, VE>(orow + col, yo);
+                if (valid && col < C) store_vec_stream<T, VE>(orow + col, yo);
             }
         }
     }
@@ -295,36 +353,41 @@ bool plan_rows(int cmax, int esize, bool vector_ok, RowPlan &pl) {
     return true;
 }
 
-template <typename T, int VE, int OP>
-int launch_rows_vpt(const RowParams &p, int vpt, int grid, cudaStream_t st) {
-    switch (vpt) {
-#define RGD_CASE(N)                                                   \
-    case N:                                                           \
-        row_kernel<T, VE, N, OP><<<grid, ROW_THREADS, 0, st>>>(p);    \
-        break;
-        RGD_CASE(1)
-        RGD_CASE(2)
-        RGD_CASE(3)
-        RGD_CASE(4)
-        RGD_CASE(8)
-#undef RGD_CASE
-        default:
-            return RGD_E_SIZE;
-    }
+// Shared memory of the pipelined kernel for VPT slots per thread.
+template <int OP>
+constexpr size_t row_pipe_smem(int vpt) {
+    return (size_t)ROW_STAGES * ((OP == L2_BWD || OP == RMS_BWD) ? 2 : 1) * vpt * ROW_THREADS * 16;
+}
+
+template <typename T, int VE, int VPT, int OP, bool PIPE>
+int launch_row_kernel(const RowParams &p, int grid, cudaStream_t st) {
+    auto kernel = row_kernel<T, VE, VPT, OP, PIPE>;
+    const size_t smem = PIPE ? row_pipe_smem<OP>(VPT) : 0;
+    if (smem > 32 * 1024)   // static shared memory counts towards the 48 KB default limit too
+        if (int e = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+            return e;
+    kernel<<<grid, ROW_THREADS, smem, st>>>(p);
     count_launch();
     return check_launch();
 }
 
+template <typename T, int VE, int OP>
+int launch_rows_vpt(const RowParams &p, int vpt, int grid, cudaStream_t st) {
+    switch (vpt) {
+        case 1: return launch_row_kernel<T, VE, 1, OP, true>(p, grid, st);
+        case 2: return launch_row_kernel<T, VE, 2, OP, true>(p, grid, st);
+        case 3: return launch_row_kernel<T, VE, 3, OP, true>(p, grid, st);
+        case 4: return launch_row_kernel<T, VE, 4, OP, true>(p, grid, st);
+        case 8: return launch_row_kernel<T, VE, 8, OP, false>(p, grid, st);
+    }
+    return RGD_E_SIZE;
+}
+
 template <typename T, int OP>
 int launch_rows_scalar(const RowParams &p, int vpt, int grid, cudaStream_t st) {
-    if (vpt == 4)
-        row_kernel<T, 1, 4, OP><<<grid, ROW_THREADS, 0, st>>>(p);
-    else if (vpt == 32)
-        row_kernel<T, 1, 32, OP><<<grid, ROW_THREADS, 0, st>>>(p);
-    else
-        return RGD_E_SIZE;
-    count_launch();
-    return check_launch();
+    if (vpt == 4) return launch_row_kernel<T, 1, 4, OP, false>(p, grid, st);
+    if (vpt == 32) return launch_row_kernel<T, 1, 32, OP, false>(p, grid, st);
+    return RGD_E_SIZE;
 }
 
 template <typename T, int OP>
@@ -419,6 +482,15 @@ int run_rows(const RowCall &c, float *dw_part0, float *dw_part1, int budget, cud
     p.w_dtype = c.w_dtype;
     p.eps = c.eps;
     int P[2] = {0, 0};
+    if (pl.ve > 1 && pl.vpt <= 4) {
+        // Pipelined kernel: launch what is resident at once (shared-memory bound), so every
+        // CTA streams several rows and the copy pipeline stays full.
+        int per_sm = (int)((200 * 1024) / row_pipe_smem<OP>(pl.vpt));
+        if (per_sm > 8) per_sm = 8;
+        if (per_sm < 1) per_sm = 1;
+        const int resident = per_sm * num_sms();
+        if (OP != RMS_BWD || resident < budget) budget = resident;
+    }
     split_ctas(c.nstreams, c.N, c.B, ROW_THREADS / pl.tpr, budget, P);
     int64_t grid = 0;
     for (int s = 0; s < c.nstreams; ++s) {
