@@ -96,6 +96,48 @@ __device__ __forceinline__ void row_index(const HeadTensor &ht, const FastDiv &f
     }
 }
 
+// Native packed 16-bit arithmetic: one correctly rounded result per operation,
+// which is exactly the stand-alone rotary's "promoted dtype" evaluation for a
+// 16-bit tensor with a table of the same type.
+template <typename T> struct Packed2;
+template <> struct Packed2<__half> {
+    static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+        __half2 r = __hmul2_rn(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
+    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
+        __half2 r = __hadd2_rn(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
+};
+template <> struct Packed2<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+        __nv_bfloat162 r = __hmul2_rn(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
+    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
+        __nv_bfloat162 r = __hadd2_rn(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
+};
+template <> struct Packed2<float> {   // never used (fp32 tensors take the fp32 path)
+    static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t) { return a; }
+    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t) { return a; }
+};
+
+// VE table entries as fp32 from 16-byte words fetched earlier.
+template <typename TP, int VE>
+__device__ __forceinline__ void table_from_raw(const uint4 *raw, float *out) {
+    constexpr int PER = 16 / sizeof(TP);
+#pragma unroll
+    for (int a = 0; a < (VE + PER - 1) / PER; ++a) {
+        union { uint4 u; TP v[PER]; } c;
+        c.u = raw[a];
+#pragma unroll
+        for (int e = 0; e < PER && a * PER + e < VE; ++e) out[a * PER + e] = to_f32<TP>(c.v[e]);
+    }
+}
+
 // One row: xq (and gq, the upstream gradient) hold this thread's packed slots;
 // the result comes back packed in `out`.  T: tensor element type.  TP: table
 // element type (T or float).  VE: elements per access (16 / sizeof(T), or 1).
@@ -117,6 +159,64 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
     const int tpr = DFIX > 0 ? DFIX / NE : p.tpr;
     const int d = DFIX > 0 ? DFIX : p.d;
     const float invd = 1.0f / (float)d;
+
+    // Rotary tables: fetch the 16-byte words of every fully rotated slot first,
+    // so their latency overlaps the normalisation arithmetic below.
+    constexpr int TW = (VE * (int)sizeof(TP) + 15) / 16;        // 16-byte words per slot of the table
+    const bool rot_row = HAS_ROPE && tok < cut;
+    uint4 sraw[HAS_ROPE ? VPT : 1][TW], craw[HAS_ROPE ? VPT : 1][TW];
+    bool pre[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        pre[j] = false;
+        if constexpr (HAS_ROPE && VE > 1) {
+            const int col = (t + j * tpr) * VE;
+            pre[j] = rot_row && pos_vec_ok && col + VE <= p.R;
+            if (pre[j]) {
+                const TP *srow = reinterpret_cast<const TP *>(p.pos) + (int64_t)tok * p.pos_sn + col;
+#pragma unroll
+                for (int a = 0; a < TW; ++a) {
+                    sraw[j][a] = __ldg(reinterpret_cast<const uint4 *>(srow) + a);
+                    craw[j][a] = __ldg(reinterpret_cast<const uint4 *>(srow + p.pos_ss) + a);
+                }
+            }
+        }
+    }
+
+    if constexpr (OP == ROPE && ROUND_EACH && VE == 8) {
+        // Stand-alone rotary on a 16-bit tensor with a table of the same type: when
+        // every slot of this thread is either fully rotated or untouched, evaluate
+        // out = x*cos + rot(x)*sin with packed 16-bit instructions (one rounding per
+        // operation, no fp32 round trip).
+        bool simple = true;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int col = (t + j * tpr) * VE;
+            if (rot_row && col < p.R && col < d && !pre[j]) simple = false;
+        }
+        if (simple) {
+            const uint32_t flip = sizeof(T) == 2 ? (p.transposed ? 0x80000000u : 0x00008000u) : 0u;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                if (pre[j]) {
+                    union { Vec<T, VE> v; uint32_t w[4]; } cx, co;
+                    cx.v = xq[j];
+                    const uint32_t sw[4] = {sraw[j][0].x, sraw[j][0].y, sraw[j][0].z, sraw[j][0].w};
+                    const uint32_t cw[4] = {craw[j][0].x, craw[j][0].y, craw[j][0].z, craw[j][0].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        // (x_even, x_odd) -> (-x_odd, x_even); the inverse negates the other half
+                        const uint32_t rot = __byte_perm(cx.w[i], 0, 0x1032) ^ flip;
+                        co.w[i] = Packed2<T>::add(Packed2<T>::mul(cx.w[i], cw[i]), Packed2<T>::mul(rot, sw[i]));
+                    }
+                    out[j] = co.v;
+                } else {
+                    out[j] = xq[j];
+                }
+            }
+            return;
+        }
+    }
 
     float xv[NE];
     float dv[HAS_DY ? NE : 1];
@@ -149,7 +249,6 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
         for (int i = 0; i < NE; ++i) xv[i] *= rstd;   // xhat
     }
 
-    const bool rot_row = HAS_ROPE && tok < cut;
     float res[NE];
 
     // Scalar mode: the rotation partner (channel c ^ 1) lives in the
@@ -180,8 +279,13 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
                     const int col = (t + j * tpr) * VE;
                     if (col < p.R) {
                         float sn[VE], cs[VE];
-                        load_table<TP, VE>(srow, col, p.R, pos_vec_ok, sn);
-                        load_table<TP, VE>(crow, col, p.R, pos_vec_ok, cs);
+                        if (pre[j]) {
+                            table_from_raw<TP, VE>(sraw[j], sn);
+                            table_from_raw<TP, VE>(craw[j], cs);
+                        } else {
+                            load_table<TP, VE>(srow, col, p.R, pos_vec_ok, sn);
+                            load_table<TP, VE>(crow, col, p.R, pos_vec_ok, cs);
+                        }
                         if constexpr (VE > 1) {
 #pragma unroll
                             for (int e = 0; e < VE; e += 2) {
@@ -221,8 +325,13 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
                 const int col = (t + j * tpr) * VE;
                 if (col < p.R) {
                     float sn[VE], cs[VE];
-                    load_table<TP, VE>(srow, col, p.R, pos_vec_ok, sn);
-                    load_table<TP, VE>(crow, col, p.R, pos_vec_ok, cs);
+                    if (pre[j]) {
+                        table_from_raw<TP, VE>(sraw[j], sn);
+                        table_from_raw<TP, VE>(craw[j], cs);
+                    } else {
+                        load_table<TP, VE>(srow, col, p.R, pos_vec_ok, sn);
+                        load_table<TP, VE>(crow, col, p.R, pos_vec_ok, cs);
+                    }
                     if constexpr (VE > 1) {
 #pragma unroll
                         for (int e = 0; e < VE; e += 2) {
