@@ -708,10 +708,13 @@ int launch_pipelined(const HeadParams &p, int64_t tiles, cudaStream_t st) {
     if (smem > 32 * 1024)   // static shared memory counts towards the 48 KB default limit too
         if (int e = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
             return e;
-    // Persistent grid: as many CTAs as fit (shared memory bound), never more than tiles.
-    int per_sm = (int)((200 * 1024) / smem);
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > 8) per_sm = 8;
+    // Persistent grid, never more CTAs than tiles:
+    // one resident wave of persistent CTAs
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, HEAD_THREADS, smem) != cudaSuccess || per_sm < 1) {
+        (void)cudaGetLastError();
+        per_sm = 1;
+    }
     int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > tiles) grid = tiles;
     kernel<<<(unsigned)grid, HEAD_THREADS, smem, st>>>(p);
@@ -728,9 +731,12 @@ int launch_flat(const HeadParams &p, int64_t tiles, cudaStream_t st) {
     if (smem > 32 * 1024)
         if (int e = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
             return e;
-    int per_sm = (int)((200 * 1024) / smem);
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > 8) per_sm = 8;
+    // one resident wave of persistent CTAs
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, HEAD_THREADS, smem) != cudaSuccess || per_sm < 1) {
+        (void)cudaGetLastError();
+        per_sm = 1;
+    }
     int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > tiles) grid = tiles;
     kernel<<<(unsigned)grid, HEAD_THREADS, smem, st>>>(p);

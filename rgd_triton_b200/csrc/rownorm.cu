@@ -371,6 +371,44 @@ int launch_row_kernel(const RowParams &p, int grid, cudaStream_t st) {
     return check_launch();
 }
 
+// CTAs of this instantiation that are resident on one SM at the same time.
+template <typename T, int VE, int VPT, int OP, bool PIPE>
+int row_kernel_occupancy() {
+    auto kernel = row_kernel<T, VE, VPT, OP, PIPE>;
+    const size_t smem = PIPE ? row_pipe_smem<OP>(VPT) : 0;
+    if (smem > 32 * 1024)
+        (void)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, ROW_THREADS, smem) != cudaSuccess || n < 1) {
+        (void)cudaGetLastError();
+        n = 1;
+    }
+    return n;
+}
+
+template <typename T, int OP>
+int rows_occupancy(const RowPlan &pl) {
+    constexpr int VE = VecElems<T>::value;
+    if (pl.ve == 1) return 0;
+    switch (pl.vpt) {
+        case 1: return row_kernel_occupancy<T, VE, 1, OP, true>();
+        case 2: return row_kernel_occupancy<T, VE, 2, OP, true>();
+        case 3: return row_kernel_occupancy<T, VE, 3, OP, true>();
+        case 4: return row_kernel_occupancy<T, VE, 4, OP, true>();
+    }
+    return 0;
+}
+
+template <int OP>
+int rows_occupancy_dtype(int dtype, const RowPlan &pl) {
+    switch (dtype) {
+        case RGD_F32: return rows_occupancy<float, OP>(pl);
+        case RGD_F16: return rows_occupancy<__half, OP>(pl);
+        case RGD_BF16: return rows_occupancy<__nv_bfloat16, OP>(pl);
+    }
+    return 0;
+}
+
 template <typename T, int VE, int OP>
 int launch_rows_vpt(const RowParams &p, int vpt, int grid, cudaStream_t st) {
     switch (vpt) {
@@ -421,7 +459,9 @@ void split_ctas(int nstreams, const int64_t *N, int64_t B, int rpc, int budget, 
     for (int s = 0; s < nstreams; ++s) {
         int64_t ps = groups[s];
         if (total > budget) {
-            ps = (groups[s] * budget + total - 1) / total;   // proportional share per batch
+            // proportional share per batch, rounded DOWN so the whole grid stays within
+            // the budget (one resident wave; a few CTAs over it would cost a second wave)
+            ps = groups[s] * budget / total;
             if (ps < 1) ps = 1;
             if (ps > groups[s]) ps = groups[s];
         }
@@ -483,13 +523,13 @@ int run_rows(const RowCall &c, float *dw_part0, float *dw_part1, int budget, cud
     p.eps = c.eps;
     int P[2] = {0, 0};
     if (pl.ve > 1 && pl.vpt <= 4) {
-        // Pipelined kernel: launch what is resident at once (shared-memory bound), so every
-        // CTA streams several rows and the copy pipeline stays full.
-        int per_sm = (int)((200 * 1024) / row_pipe_smem<OP>(pl.vpt));
-        if (per_sm > 8) per_sm = 8;
-        if (per_sm < 1) per_sm = 1;
-        const int resident = per_sm * num_sms();
-        if (OP != RMS_BWD || resident < budget) budget = resident;
+        // Pipelined kernel: launch exactly one resident wave, so every CTA streams
+        // several rows and the copy pipeline stays full.
+        const int per_sm = rows_occupancy_dtype<OP>(c.x_dtype, pl);
+        if (per_sm > 0) {
+            const int resident = per_sm * num_sms();
+            if (OP != RMS_BWD || resident < budget) budget = resident;
+        }
     }
     split_ctas(c.nstreams, c.N, c.B, ROW_THREADS / pl.tpr, budget, P);
     int64_t grid = 0;
