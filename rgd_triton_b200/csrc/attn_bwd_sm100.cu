@@ -403,24 +403,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
 template <typename T>
 __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __grid_constant__ AttnParams p, float *lse2, float *delta_s,
                                                             int Tq128) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int i = blockIdx.x * 8 + warp;
+    // d / 8 lanes per row (d is 64 or 128, rows 16-byte aligned): 2 or 4 rows per warp
+    const int lpr = p.d >> 3;
+    const int rows_per_cta = 256 / lpr;
+    const int i = blockIdx.x * rows_per_cta + (int)threadIdx.x / lpr;
+    const int l = (int)threadIdx.x % lpr;
     const int bh = blockIdx.y;
-    if (i >= Tq128) return;
     const int b = bh / p.H, h = bh - b * p.H;
     float a = 0.f;
     if (i < p.Tq) {
         const T *o = reinterpret_cast<const T *>(p.o) + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)i * p.o_sn;
         const T *g = reinterpret_cast<const T *>(p.d_o) + (int64_t)b * p.do_sb + (int64_t)h * p.do_sh +
                      (int64_t)i * p.do_sn;
-        for (int c = lane * 8; c < p.d; c += 256) {     // d is 64 or 128, rows 16-byte aligned
-            const Vec<T, 8> ov = load_vec<T, 8>(o + c), gv = load_vec<T, 8>(g + c);
+        const Vec<T, 8> ov = load_vec_stream<T, 8>(o + l * 8), gv = load_vec<T, 8>(g + l * 8);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) a += to_f32<T>(ov.v[e]) * to_f32<T>(gv.v[e]);
-        }
+        for (int e = 0; e < 8; ++e) a += to_f32<T>(ov.v[e]) * to_f32<T>(gv.v[e]);
     }
-    a = warp_group_sum(a, 32);
-    if (lane == 0) {
+    a = warp_group_sum(a, lpr);
+    if (l == 0 && i < Tq128) {
         const int64_t idx = (int64_t)bh * Tq128 + i;
         delta_s[idx] = a * p.scale;
         lse2[idx] = i < p.Tq ? p.lse[(int64_t)bh * p.Tq_rounded + i] * LOG2E : INFINITY;
@@ -470,7 +470,8 @@ int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st) {
     const int Tq128 = (p.Tq + 127) / 128 * 128;
     float *lse2 = p.delta, *delta_s = p.delta + (int64_t)p.B * p.H * Tq128;
     {
-        dim3 grid((Tq128 + 7) / 8, p.B * p.H);
+        const int rows_per_cta = 256 / (p.d / 8);
+        dim3 grid((Tq128 + rows_per_cta - 1) / rows_per_cta, p.B * p.H);
         if (bf16) attn_bwd_prep_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, lse2, delta_s, Tq128);
         else attn_bwd_prep_kernel<__half><<<grid, 256, 0, st>>>(p, lse2, delta_s, Tq128);
         count_launch();
