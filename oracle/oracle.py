@@ -171,14 +171,20 @@ def _rotate_pairs(x: torch.Tensor, inverse: bool) -> torch.Tensor:
 
 
 def _rope_apply(x: torch.Tensor, pos_emb: torch.Tensor, cutoff: int, heads_second: bool, inverse: bool,
-                compute_dtype: torch.dtype) -> torch.Tensor:
+                compute_dtype: torch.dtype, fused: bool = False) -> torch.Tensor:
     """out = x*cos + rot(x)*sin on channels < R of tokens < cutoff, evaluated in
-    `compute_dtype` with one rounding per multiply and per add (:46-51)."""
+    `compute_dtype` (:46-51): one rounding per multiply and per add, or, with
+    `fused`, rn(fma(rot, sin, rn(x*cos))) — the order the reference's compiled
+    kernel uses for 16-bit types (rot*sin is exact in fp32 there)."""
     n = x.shape[2] if heads_second else x.shape[1]
     d = x.shape[-1]
     sin, cos, Rc = _rope_tables(pos_emb, n, d, heads_second, compute_dtype)
     xc = x.to(compute_dtype)
-    out = xc * cos + _rotate_pairs(xc, inverse) * sin
+    if fused and compute_dtype in (torch.float16, torch.bfloat16):
+        p1 = (xc * cos).double()
+        out = (_rotate_pairs(xc, inverse).double() * sin.double() + p1).to(compute_dtype)   # exact sum, one rounding
+    else:
+        out = xc * cos + _rotate_pairs(xc, inverse) * sin
     tok = torch.arange(n)
     tok = tok[None, None, :, None] if heads_second else tok[None, :, None, None]
     mask = (tok < cutoff) & (torch.arange(d) < Rc)
@@ -186,14 +192,22 @@ def _rope_apply(x: torch.Tensor, pos_emb: torch.Tensor, cutoff: int, heads_secon
 
 
 def rope(x: torch.Tensor, pos_emb: torch.Tensor, cutoff: int | None = None, heads_second: bool = True,
-         transposed: bool = False) -> torch.Tensor:
+         transposed: bool = False, mode: str = "compiled") -> torch.Tensor:
     """Stand-alone rotary.  The reference computes in the promoted dtype of x
-    and the table without an fp32 upcast (head_rope_cached.py:127-142), i.e.
-    16-bit x with a 16-bit table of the same type rounds after every operation."""
+    and the table without an fp32 upcast (head_rope_cached.py:127-142).  For a
+    16-bit x with a table of the same type the result depends on how the
+    expression is evaluated:
+      mode="compiled"     rn(fma(rot, sin, rn(x*cos))): what the reference's
+                          kernel does when compiled for a GPU (checked on B200:
+                          bit-equal with its output for bf16, 99.999 % for fp16);
+      mode="interpreted"  one rounding per operation: what Triton's interpreter
+                          (the golden vectors) and torch eager do.
+    The two differ by at most one unit in the last place of the larger product."""
     n = x.shape[2] if heads_second else x.shape[1]
     cutoff = n if cutoff is None else cutoff
     cd = torch.promote_types(x.dtype, pos_emb.dtype)
-    return _rope_apply(x.detach(), pos_emb.detach(), cutoff, heads_second, transposed, cd).to(x.dtype)
+    return _rope_apply(x.detach(), pos_emb.detach(), cutoff, heads_second, transposed, cd,
+                       fused=(mode == "compiled")).to(x.dtype)
 
 
 # --------------------------------------------------------------------------

@@ -96,17 +96,20 @@ __device__ __forceinline__ void row_index(const HeadTensor &ht, const FastDiv &f
     }
 }
 
-// Native packed 16-bit arithmetic: one correctly rounded result per operation,
-// which is exactly the stand-alone rotary's "promoted dtype" evaluation for a
-// 16-bit tensor with a table of the same type.
+// Native packed 16-bit arithmetic for the stand-alone rotary on a 16-bit tensor
+// with a table of the same type.  The reference evaluates x*cos + rot(x)*sin in
+// that type (head_rope_cached.py:48); its compiled kernel contracts the second
+// product into the sum, i.e. out = rn(fma(rot, sin, rn(x*cos))) — measured
+// bit-equal on B200 — which is what mul + fma below reproduce.
 template <typename T> struct Packed2;
 template <> struct Packed2<__half> {
     static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
         __half2 r = __hmul2_rn(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
         return *reinterpret_cast<uint32_t *>(&r);
     }
-    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
-        __half2 r = __hadd2_rn(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+    static __device__ __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+        __half2 r = __hfma2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b),
+                            *reinterpret_cast<__half2 *>(&c));
         return *reinterpret_cast<uint32_t *>(&r);
     }
 };
@@ -115,14 +118,15 @@ template <> struct Packed2<__nv_bfloat16> {
         __nv_bfloat162 r = __hmul2_rn(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
         return *reinterpret_cast<uint32_t *>(&r);
     }
-    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
-        __nv_bfloat162 r = __hadd2_rn(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
+    static __device__ __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+        __nv_bfloat162 r = __hfma2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b),
+                                   *reinterpret_cast<__nv_bfloat162 *>(&c));
         return *reinterpret_cast<uint32_t *>(&r);
     }
 };
 template <> struct Packed2<float> {   // never used (fp32 tensors take the fp32 path)
     static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t) { return a; }
-    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t) { return a; }
+    static __device__ __forceinline__ uint32_t fma(uint32_t a, uint32_t, uint32_t) { return a; }
 };
 
 // VE table entries as fp32 from 16-byte words fetched earlier.
@@ -150,8 +154,8 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
     constexpr bool HAS_ROPE = (OP == ROPE || OP == LNROPE_FWD || OP == LNROPE_BWD);
     constexpr bool HAS_LN = (OP != ROPE);
     // The stand-alone rotary computes in the promoted type of x and the table
-    // (head_rope_cached.py:48,142): 16-bit x with a 16-bit table rounds after
-    // every multiply and add; anything else is plain fp32.
+    // (head_rope_cached.py:48,142): 16-bit x with a 16-bit table rounds x*cos to
+    // that type and then fuses rot*sin into the sum; anything else is plain fp32.
     constexpr bool ROUND_EACH = (OP == ROPE) && (sizeof(T) == 2) && (sizeof(TP) == 2);
     constexpr int NE = VPT * VE;
     // DFIX > 0: head_dim is a compile-time constant that fills the slots exactly,
@@ -186,8 +190,7 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
     if constexpr (OP == ROPE && ROUND_EACH && VE == 8) {
         // Stand-alone rotary on a 16-bit tensor with a table of the same type: when
         // every slot of this thread is either fully rotated or untouched, evaluate
-        // out = x*cos + rot(x)*sin with packed 16-bit instructions (one rounding per
-        // operation, no fp32 round trip).
+        // out = fma(rot(x), sin, x*cos) with packed 16-bit instructions (no fp32 round trip).
         bool simple = true;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -207,7 +210,7 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
                     for (int i = 0; i < 4; ++i) {
                         // (x_even, x_odd) -> (-x_odd, x_even); the inverse negates the other half
                         const uint32_t rot = __byte_perm(cx.w[i], 0, 0x1032) ^ flip;
-                        co.w[i] = Packed2<T>::add(Packed2<T>::mul(cx.w[i], cw[i]), Packed2<T>::mul(rot, sw[i]));
+                        co.w[i] = Packed2<T>::fma(rot, sw[i], Packed2<T>::mul(cx.w[i], cw[i]));
                     }
                     out[j] = co.v;
                 } else {
@@ -341,8 +344,9 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
                             const float ro = inv ? -xe : xe;
                             float oe, oo;
                             if constexpr (ROUND_EACH) {
-                                oe = round_to<T>(round_to<T>(xe * cs[e]) + round_to<T>(re * sn[e]));
-                                oo = round_to<T>(round_to<T>(xo * cs[e + 1]) + round_to<T>(ro * sn[e + 1]));
+                                // rot*sin is exact in fp32 for 16-bit operands
+                                oe = round_to<T>(fmaf(re, sn[e], round_to<T>(xe * cs[e])));
+                                oo = round_to<T>(fmaf(ro, sn[e + 1], round_to<T>(xo * cs[e + 1])));
                             } else {
                                 oe = xe * cs[e] + re * sn[e];
                                 oo = xo * cs[e + 1] + ro * sn[e + 1];
@@ -355,7 +359,7 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
                         float rot = (col & 1) ? oth[j] : -oth[j];
                         if (inv) rot = -rot;
                         if constexpr (ROUND_EACH)
-                            res[j] = round_to<T>(round_to<T>(me * cs[0]) + round_to<T>(rot * sn[0]));
+                            res[j] = round_to<T>(fmaf(rot, sn[0], round_to<T>(me * cs[0])));
                         else
                             res[j] = me * cs[0] + rot * sn[0];
                     }

@@ -113,11 +113,13 @@ def test_golden_vectors(golden, dt, hs):
     pos, eps, cuts = T(g["pos"]), float(g["eps"]), (int(g["cut_q"]), int(g["cut_k"]))
     q, k, gq, gk = (T(g[f"{n}_{s}"]) for n in ("q", "k", "gq", "gk"))
     for name, fn, tol in (("l", lambda a, b: F_.triton_fused_ln_func_fn(a, b, hs, eps), 1e-5),
-                          ("r", lambda a, b: F_.triton_rope_fn(a, b, pos.cuda(), cuts, hs), 2e-6),
+                          # the interpreter rounds after every operation, the GPU kernels (the reference's
+                          # and ours) fuse rot*sin into the sum: up to 1 ulp of the larger product apart
+                          ("r", lambda a, b: F_.triton_rope_fn(a, b, pos.cuda(), cuts, hs), 2e-6 if dt == "f32" else 1e-3),
                           ("f", lambda a, b: F_.triton_fused_ln_rope_fn(a, b, pos.cuda(), cuts, hs, eps), 1e-5)):
         qo, ko, dq, dk = _run(fn, q, k, gq, gk)
-        assert_parity(qo, T(g[f"{name}q_{s}"]), f"golden {name}q")
-        assert_parity(ko, T(g[f"{name}k_{s}"]), f"golden {name}k")
+        assert_parity(qo, T(g[f"{name}q_{s}"]), f"golden {name}q", atol_rel=tol if name == "r" else 2e-6)
+        assert_parity(ko, T(g[f"{name}k_{s}"]), f"golden {name}k", atol_rel=tol if name == "r" else 2e-6)
         assert_parity(dq, T(g[f"d{name}q_{s}"]), f"golden d{name}q", atol_rel=tol)
         assert_parity(dk, T(g[f"d{name}k_{s}"]), f"golden d{name}k", atol_rel=tol)
 
