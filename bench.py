@@ -322,6 +322,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ops-only", action="store_true", help="only the per-operator norm / RoPE table")
+    ap.add_argument("--no-config4", action="store_true", help="skip the dense-bias attention measurement")
     ap.add_argument("--profile", default=None, choices=["attn", "attn64", "lnrope", "rms2"],
                     help="run a small fixed case of one operator (1 warm-up + 2 fwd+bwd passes) for ncu captures")
     args = ap.parse_args()
@@ -411,7 +412,10 @@ def main():
           ("attention forward kernel", f_fwd, fwd_ms)
     achieved = dom[1] / (dom[2] * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": dom[0], "achieved": achieved, "peak": tf_burst, "unit": "TFLOP/s",
-                "frac": achieved / tf_burst, "peak_source": peak_src, "traffic": None,
+                "frac": achieved / tf_burst, "peak_source": peak_src,
+                # DRAM bytes of the dK/dV + dQ launches: ncu capture of the quarter-size case (16 of the 64
+                # (batch, head) pairs, profiles/attention_tmem_kernels_small_case.md) scaled x4
+                "traffic": 4 * (67.74e6 + 5.86e6 + 67.71e6 + 4.66e6),
                 "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
                 "fwd_tflops": f_fwd / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": f_bwd / (bwd_ms * 1e-3) / 1e12}
 
@@ -489,6 +493,39 @@ def main():
     del q2, k2, gq2, gk2
     norm_rope["ops"] = op_table(dev, min(args.steps, 10), hbm_peak)
 
+    # ---------------- attention with a dense additive bias, config 4 ----------------
+    def config4(broadcast):
+        g4 = torch.Generator().manual_seed(4)
+        B4, T4, H4, D4 = 2, 4096, 24, 64
+        q4, k4, v4, do4 = (torch.randn(B4, T4, H4, D4, generator=g4).to(torch.float16).to(dev) for _ in range(4))
+        bb = 1 if broadcast else B4
+        bias = torch.randn(bb, H4, T4, T4, generator=g4, dtype=torch.float16)
+        blk = (torch.rand(bb, H4, T4 // 64, T4 // 64, generator=g4) < 0.1) & ~torch.eye(T4 // 64, dtype=torch.bool)
+        bias = (bias.float() - 1e4 * blk.repeat_interleave(64, 2).repeat_interleave(64, 3)).to(torch.float16).to(dev)
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(max(3, min(args.steps, 10)))]
+        for i in range(-2, len(ev)):
+            qi, ki, vi = q4.requires_grad_(True), k4.requires_grad_(True), v4.requires_grad_(True)
+            if i >= 0:
+                ev[i][0].record()
+            o = attn(qi, ki, vi, bias)
+            if i >= 0:
+                ev[i][1].record()
+            torch.autograd.grad(o, (qi, ki, vi), do4)
+            if i >= 0:
+                ev[i][2].record()
+        torch.cuda.synchronize()
+        fwd = statistics.median(e[0].elapsed_time(e[1]) for e in ev)
+        bwd = statistics.median(e[1].elapsed_time(e[2]) for e in ev)
+        ff, fb = attn_flops(B4, T4, H4, D4)
+        nbias = bias.numel() * 2
+        return {"workload": f"config4 FlashAttention fwd+bwd fp16 q/k/v [2,4096,24,64] bias [{bb},24,4096,4096]",
+                "fwd_ms": fwd, "bwd_ms": bwd, "tflops": (ff + fb) / ((fwd + bwd) * 1e-3) / 1e12,
+                "fwd_bias_gbs": nbias / (fwd * 1e-3) / 1e9, "bias_bytes_per_pass": nbias,
+                "roofline_ms": sum(max(f / (tf_burst * 1e12), nbias / (hbm_peak * 1e9)) for f in (ff, fb)) * 1e3}
+
+    cfg4 = [config4(False), config4(True)] if not args.no_config4 else None
+    torch.cuda.empty_cache()
+
     base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         base = cpu_baseline(cfg)
@@ -504,6 +541,8 @@ def main():
             "roofline": roofline, "norm_rope": norm_rope, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if cfg4 is not None:
+            line["config4"] = cfg4
         if base is not None:
             line["cpu_baseline"] = base
         print(json.dumps(line), flush=True)

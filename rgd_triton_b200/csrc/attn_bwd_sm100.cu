@@ -74,7 +74,9 @@ __device__ __forceinline__ uint32_t pack16b(float a, float b) {
     }
 }
 
-template <int D, bool BF16, bool DKDV>
+// BIAS: whether an additive bias exists; the no-bias instantiation carries none of
+// the bias code (and none of its register pressure).
+template <int D, bool BF16, bool DKDV, bool BIAS>
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_constant__ BwdTmaParams p) {
     constexpr int HALVES = D / 64;
     constexpr uint32_t PANEL = 128 * 64 * 2;
@@ -218,7 +220,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
         const float *lse2_bh = p.lse2 + (int64_t)bh * p.Tq128;
         const float *ds_bh = p.delta_s + (int64_t)bh * p.Tq128;
         const char *bias_bh = nullptr;
-        if (p.bias_kind != RGD_BIAS_NONE)
+        if constexpr (BIAS)
             bias_bh = reinterpret_cast<const char *>(p.bias) +
                       ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
 
@@ -239,8 +241,44 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
             // mask, and any block touching the end of the keys.  Rows / columns past
             // the end of the QUERIES need nothing: their lse2 is +inf.
             const bool diag = p.causal && (DKDV ? (blk0 == r0) : (blk0 + BT > r0));
-            const bool slow = diag || cta_key_tail || (!DKDV && blk0 + BT > p.Tk) || bias_bh != nullptr;
+            const bool slow = BIAS || diag || cta_key_tail || (!DKDV && blk0 + BT > p.Tk);
             float pv[64];
+
+            // Bias for this thread's 64 elements, fetched before waiting for the score tile so
+            // the loads overlap the wait.  Indices are clamped to stay in bounds; elements
+            // past the ends are masked below.
+            float bv[BIAS ? 64 : 1];
+            if constexpr (BIAS) {
+                if (DKDV) {
+                    const int kj = min(row, p.Tk - 1);
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int qi = min(c0 + i, p.Tq - 1);
+                        const int64_t off = (p.bias_kind == RGD_BIAS_MATRIX ? (int64_t)qi * p.b_sq : 0) + kj;
+                        bv[i] = p.bias_f32 ? __ldg(reinterpret_cast<const float *>(bias_bh) + off)
+                                           : to_f32<T>(reinterpret_cast<const T *>(bias_bh)[off]);
+                    }
+                } else {
+                    const int qi = min(row, p.Tq - 1);
+                    const int64_t off = (p.bias_kind == RGD_BIAS_MATRIX ? (int64_t)qi * p.b_sq : 0) + c0;
+                    if (!p.bias_f32 && p.bias_vec && c0 + 64 <= p.Tk) {
+                        const T *src = reinterpret_cast<const T *>(bias_bh) + off;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const Vec<T, 8> v = load_vec<T, 8>(src + 8 * i);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) bv[8 * i + e] = to_f32<T>(v.v[e]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 64; ++i) {
+                            const int64_t o2 = off + min(i, p.Tk - 1 - c0 < 0 ? 0 : p.Tk - 1 - c0);
+                            bv[i] = p.bias_f32 ? __ldg(reinterpret_cast<const float *>(bias_bh) + o2)
+                                               : to_f32<T>(reinterpret_cast<const T *>(bias_bh)[o2]);
+                        }
+                    }
+                }
+            }
 
             ok = mbar_wait(&sm.g1_full, par, status, 61);
             if (!ok) break;
@@ -282,12 +320,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                         const int qi = DKDV ? col : row, kj = DKDV ? row : col;
                         float x = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]) * p.scale_log2;
                         const bool masked = kj >= p.Tk || qi >= p.Tq || (p.causal && kj > qi);
-                        const float l2 = DKDV ? __ldg(lse2_bh + qi) : lse_row;
-                        if (bias_bh != nullptr && !masked) {
-                            const int64_t off = (p.bias_kind == RGD_BIAS_MATRIX ? (int64_t)qi * p.b_sq : 0) + kj;
-                            x += (p.bias_f32 ? reinterpret_cast<const float *>(bias_bh)[off]
-                                             : to_f32<T>(reinterpret_cast<const T *>(bias_bh)[off])) * LOG2E;
-                        }
+                        const float l2 = DKDV ? __ldg(lse2_bh + qi) : lse_row;     // qi < Tq128 always
+                        if constexpr (BIAS) x = fmaf(bv[i], LOG2E, x);
                         pv[i] = masked ? 0.f : ex2b(x - l2);
                     }
                 }
@@ -440,16 +474,22 @@ bool tmem_bwd_eligible(const AttnParams &p) {
            p.vec_dq && p.vec_dk && p.vec_dv;
 }
 
-template <int D, bool BF16, bool DKDV>
-static int launch_bwd_tmem(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
+template <int D, bool BF16, bool DKDV, bool BIAS>
+static int launch_bwd_one(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
     const size_t smem = sizeof(BwdTmaSmem<D>) + 1024;
-    if (int e = cuda_status(cudaFuncSetAttribute(attn_bwd_tmem<D, BF16, DKDV>,
+    if (int e = cuda_status(cudaFuncSetAttribute(attn_bwd_tmem<D, BF16, DKDV, BIAS>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
         return e;
     dim3 grid(nblocks, BH);
-    attn_bwd_tmem<D, BF16, DKDV><<<grid, BWD_THREADS, smem, st>>>(bp);
+    attn_bwd_tmem<D, BF16, DKDV, BIAS><<<grid, BWD_THREADS, smem, st>>>(bp);
     count_launch();
     return check_launch();
+}
+
+template <int D, bool BF16, bool DKDV>
+static int launch_bwd_tmem(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
+    if (bp.bias_kind != RGD_BIAS_NONE) return launch_bwd_one<D, BF16, DKDV, true>(bp, nblocks, BH, st);
+    return launch_bwd_one<D, BF16, DKDV, false>(bp, nblocks, BH, st);
 }
 
 template <int D, bool BF16>

@@ -116,7 +116,7 @@ __device__ __forceinline__ void load_bias32(const FwdTmaParams &p, const char *b
     }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_constant__ FwdTmaParams p) {
     constexpr int HALVES = D / 64;                 // 64-channel (128-byte) swizzle panels per tile
     constexpr uint32_t PANEL = 128 * 64 * 2;       // bytes of one 128-row panel
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
         const uint32_t s_col = t * 128, o_col = 256 + t * 128;
         const int my_nb = nb[t];
         const char *bias_bh = nullptr;
-        if (p.bias_kind != RGD_BIAS_NONE)
+        if constexpr (BIAS)
             bias_bh = reinterpret_cast<const char *>(p.bias) +
                       ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
         const int brow = row < p.Tq ? row : (p.Tq - 1);     // rows past the end read a valid bias row
@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 uint32_t r0[32], r1[32];
                 tmem_ld32(lane_base + s_col + c * 64, r0);
                 tmem_ld32(lane_base + s_col + c * 64 + 32, r1);
-                if (bias_bh == nullptr && !need_mask) {
+                if (!BIAS && !need_mask) {
                     tmem_wait_ld();
                     float a = -INFINITY, bq = -INFINITY;
 #pragma unroll
@@ -301,12 +301,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf) {
                         float bb[32];
-                        if (bias_bh != nullptr) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
+                        if constexpr (BIAS) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
                         if (hf == 0) tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             float x = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
-                            if (bias_bh != nullptr) x += bb[i];
+                            if constexpr (BIAS) x += bb[i];
                             if (need_mask) {
                                 const int col = n0 + c * 64 + hf * 32 + i;
                                 if (col >= p.Tk || (p.causal && col > row)) x = -INFINITY;
@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 tmem_ld32(lane_base + s_col + c * 64 + 32, r1);
                 uint32_t pk[32];
                 float ls0 = 0.f, ls1 = 0.f;
-                if (bias_bh == nullptr && !need_mask) {
+                if (!BIAS && !need_mask) {
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
@@ -362,13 +362,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf) {
                         float bb[32];
-                        if (bias_bh != nullptr) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
+                        if constexpr (BIAS) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
                         if (hf == 0) tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
                             float x0 = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
                             float x1 = __uint_as_float(hf ? r1[i + 1] : r0[i + 1]) * p.scale_log2;
-                            if (bias_bh != nullptr) {
+                            if constexpr (BIAS) {
                                 x0 += bb[i];
                                 x1 += bb[i + 1];
                             }
@@ -455,16 +455,22 @@ bool tmem_fwd_eligible(const AttnParams &p) {
     return (p.d == 64 || p.d == 128) && p.Tq >= 1 && p.Tk >= 1 && p.vec_q && p.vec_k && p.vec_v && p.vec_o;
 }
 
-template <int D, bool BF16>
-static int launch_fwd_tmem(const FwdTmaParams &fp, int nq_tiles, int BH, cudaStream_t st) {
+template <int D, bool BF16, bool BIAS>
+static int launch_fwd_one(const FwdTmaParams &fp, int nq_tiles, int BH, cudaStream_t st) {
     const size_t smem = sizeof(FwdTmaSmem<D>) + 1024;
-    if (int e = cuda_status(cudaFuncSetAttribute(attn_fwd_tmem<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)smem)))
+    if (int e = cuda_status(cudaFuncSetAttribute(attn_fwd_tmem<D, BF16, BIAS>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
         return e;
     dim3 grid(nq_tiles, BH);
-    attn_fwd_tmem<D, BF16><<<grid, FWD_THREADS, smem, st>>>(fp);
+    attn_fwd_tmem<D, BF16, BIAS><<<grid, FWD_THREADS, smem, st>>>(fp);
     count_launch();
     return check_launch();
+}
+
+template <int D, bool BF16>
+static int launch_fwd_tmem(const FwdTmaParams &fp, int nq_tiles, int BH, cudaStream_t st) {
+    if (fp.bias_kind != RGD_BIAS_NONE) return launch_fwd_one<D, BF16, true>(fp, nq_tiles, BH, st);
+    return launch_fwd_one<D, BF16, false>(fp, nq_tiles, BH, st);
 }
 
 int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
