@@ -32,6 +32,8 @@ namespace attn {
 using namespace rgd::sm100;
 
 int *tmem_status_ptr();   // attn_fwd_sm100.cu
+bool bias_tma_ok(const AttnParams &p);
+int encode_bias_map(CUtensorMap *out, const AttnParams &p, bool bf16);
 
 constexpr int BWD_THREADS = 320;
 constexpr int BT = 128;   // tile edge (queries and keys)
@@ -43,18 +45,24 @@ struct BwdTmaParams {
     const void *bias;
     int64_t b_sb, b_sh, b_sq;
     int bias_kind, bias_f32, bias_vec;
+    CUtensorMap mbias;                  // BIAS == 2: (Tk, Tq, H or 1, B or 1) map over the bias, box 64 x 128
+    int bias_h0, bias_b0;               // bias broadcast over heads / batch: coordinate 0
     const float *lse2, *delta_s;        // [B, H, Tq128]: lse * log2(e) (+inf past Tq), delta * scale (0 past Tq)
     int H, Tq, Tk, Tq128, causal;
     float scale, scale_log2;
     int *status;
 };
 
-template <int D>
+// BSTAGES: stages of TMA-staged bias tiles (query rows x key columns, 16-bit, two
+// 64-column panels with 128-byte swizzle); 0 when the bias does not go through TMA.
+template <int D, int BSTAGES>
 struct alignas(1024) BwdTmaSmem {
     unsigned char x1[BT * D * 2], x2[BT * D * 2];            // fixed tiles
     unsigned char y1[2][BT * D * 2], y2[2][BT * D * 2];      // looped tiles, 2 stages
+    unsigned char bias[BSTAGES > 0 ? BSTAGES : 1][BSTAGES > 0 ? BT * BT * 2 : 1024];
     uint64_t x_full, g1_full, g2_full, p_ready, ds_ready, acc_full;
     uint64_t y_full[2], y_empty[2];
+    uint64_t bb_full[2], bb_empty[2];
     uint32_t tmem_base;
 };
 
@@ -76,8 +84,11 @@ __device__ __forceinline__ uint32_t pack16b(float a, float b) {
 
 // BIAS: whether an additive bias exists; the no-bias instantiation carries none of
 // the bias code (and none of its register pressure).
-template <int D, bool BF16, bool DKDV, bool BIAS>
+// (BIAS: 0 none, 1 read from global memory by the compute threads, 2 staged through TMA.)
+template <int D, bool BF16, bool DKDV, int BIAS>
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_constant__ BwdTmaParams p) {
+    constexpr int BSTAGES = BIAS == 2 ? (D == 64 ? 2 : 1) : 0;
+    constexpr uint32_t BIAS_BYTES = BT * BT * 2;
     constexpr int HALVES = D / 64;
     constexpr uint32_t PANEL = 128 * 64 * 2;
     constexpr uint32_t TILE_BYTES = BT * D * 2;
@@ -86,7 +97,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
 
     extern __shared__ unsigned char smem_raw[];
-    BwdTmaSmem<D> &sm = *reinterpret_cast<BwdTmaSmem<D> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    BwdTmaSmem<D, BSTAGES> &sm = *reinterpret_cast<BwdTmaSmem<D, BSTAGES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int blk = blockIdx.x, bh = blockIdx.y;
@@ -114,6 +125,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
         for (int s = 0; s < 2; ++s) {
             mbar_init(&sm.y_full[s], 1);
             mbar_init(&sm.y_empty[s], 1);
+            mbar_init(&sm.bb_full[s], 1);
+            mbar_init(&sm.bb_empty[s], 256);
         }
         fence_mbar_init();
     }
@@ -135,6 +148,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
             tma_prefetch_desc(mx2);
             tma_prefetch_desc(my1);
             tma_prefetch_desc(my2);
+            if constexpr (BIAS == 2) tma_prefetch_desc(&p.mbias);
             mbar_expect_tx(&sm.x_full, 2 * TILE_BYTES);
             for (int hh = 0; hh < HALVES; ++hh) {
                 tma_load_4d(sm.x1 + hh * PANEL, mx1, &sm.x_full, hh * 64, r0, h, b);
@@ -151,6 +165,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                 for (int hh = 0; hh < HALVES; ++hh) {
                     tma_load_4d(sm.y1[s] + hh * PANEL, my1, &sm.y_full[s], hh * 64, row, h, b);
                     tma_load_4d(sm.y2[s] + hh * PANEL, my2, &sm.y_full[s], hh * 64, row, h, b);
+                }
+                if constexpr (BIAS == 2) {
+                    const int sb = it % BSTAGES;
+                    ok = mbar_wait(&sm.bb_empty[sb], ((uint32_t)(it / BSTAGES) & 1u) ^ 1u, status, 42);
+                    if (!ok) break;
+                    mbar_expect_tx(&sm.bb_full[sb], BIAS_BYTES);
+                    // tile rows are queries, columns keys
+                    const int qrow = DKDV ? row : r0, kcol = DKDV ? r0 : row;
+                    for (int pn = 0; pn < 2; ++pn)
+                        tma_load_4d(sm.bias[sb] + pn * (BT * 128), &p.mbias, &sm.bb_full[sb], kcol + pn * 64, qrow,
+                                    p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
                 }
             }
             if (!ok)
@@ -220,7 +245,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
         const float *lse2_bh = p.lse2 + (int64_t)bh * p.Tq128;
         const float *ds_bh = p.delta_s + (int64_t)bh * p.Tq128;
         const char *bias_bh = nullptr;
-        if constexpr (BIAS)
+        if constexpr (BIAS == 1)
             bias_bh = reinterpret_cast<const char *>(p.bias) +
                       ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
 
@@ -241,14 +266,41 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
             // mask, and any block touching the end of the keys.  Rows / columns past
             // the end of the QUERIES need nothing: their lse2 is +inf.
             const bool diag = p.causal && (DKDV ? (blk0 == r0) : (blk0 + BT > r0));
-            const bool slow = BIAS || diag || cta_key_tail || (!DKDV && blk0 + BT > p.Tk);
+            const bool slow = BIAS != 0 || diag || cta_key_tail || (!DKDV && blk0 + BT > p.Tk);
             float pv[64];
 
             // Bias for this thread's 64 elements, fetched before waiting for the score tile so
             // the loads overlap the wait.  Indices are clamped to stay in bounds; elements
             // past the ends are masked below.
-            float bv[BIAS ? 64 : 1];
-            if constexpr (BIAS) {
+            float bv[BIAS != 0 ? 64 : 1];
+            if constexpr (BIAS == 2) {
+                const int sb = it % BSTAGES;
+                ok = mbar_wait(&sm.bb_full[sb], (uint32_t)(it / BSTAGES) & 1u, status, 65);
+                if (!ok) break;
+                const unsigned char *tile = sm.bias[sb];
+                if (DKDV) {
+                    // thread = key column row_l of the tile, 64 query rows half*64 .. +63
+                    const unsigned char *colp = tile + (row_l >> 6) * (BT * 128) + (row_l & 7) * 2;
+                    const int kc = (row_l & 63) >> 3;
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int qr = half * 64 + i;
+                        bv[i] = to_f32<T>(*reinterpret_cast<const T *>(colp + qr * 128 + ((kc ^ (qr & 7)) << 4)));
+                    }
+                } else {
+                    // thread = query row row_l, 64 key columns = the whole 128-byte row of panel `half`
+                    const unsigned char *rowp = tile + half * (BT * 128) + row_l * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        union { uint4 u; T v[8]; } cv;
+                        cv.u = *reinterpret_cast<const uint4 *>(rowp + ((c ^ (row_l & 7)) << 4));
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) bv[8 * c + e] = to_f32<T>(cv.v[e]);
+                    }
+                }
+                mbar_arrive(&sm.bb_empty[sb]);      // values are in registers: the stage can be refilled
+            }
+            if constexpr (BIAS == 1) {
                 if (DKDV) {
                     const int kj = min(row, p.Tk - 1);
 #pragma unroll
@@ -321,7 +373,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                         float x = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]) * p.scale_log2;
                         const bool masked = kj >= p.Tk || qi >= p.Tq || (p.causal && kj > qi);
                         const float l2 = DKDV ? __ldg(lse2_bh + qi) : lse_row;     // qi < Tq128 always
-                        if constexpr (BIAS) x = fmaf(bv[i], LOG2E, x);
+                        if constexpr (BIAS != 0) x = fmaf(bv[i], LOG2E, x);
                         pv[i] = masked ? 0.f : ex2b(x - l2);
                     }
                 }
@@ -474,9 +526,10 @@ bool tmem_bwd_eligible(const AttnParams &p) {
            p.vec_dq && p.vec_dk && p.vec_dv;
 }
 
-template <int D, bool BF16, bool DKDV, bool BIAS>
+template <int D, bool BF16, bool DKDV, int BIAS>
 static int launch_bwd_one(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
-    const size_t smem = sizeof(BwdTmaSmem<D>) + 1024;
+    constexpr int BSTAGES = BIAS == 2 ? (D == 64 ? 2 : 1) : 0;
+    const size_t smem = sizeof(BwdTmaSmem<D, BSTAGES>) + 1024;
     if (int e = cuda_status(cudaFuncSetAttribute(attn_bwd_tmem<D, BF16, DKDV, BIAS>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
         return e;
@@ -488,8 +541,9 @@ static int launch_bwd_one(const BwdTmaParams &bp, int nblocks, int BH, cudaStrea
 
 template <int D, bool BF16, bool DKDV>
 static int launch_bwd_tmem(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
-    if (bp.bias_kind != RGD_BIAS_NONE) return launch_bwd_one<D, BF16, DKDV, true>(bp, nblocks, BH, st);
-    return launch_bwd_one<D, BF16, DKDV, false>(bp, nblocks, BH, st);
+    if (bp.bias_kind != RGD_BIAS_NONE && bp.bias_vec == 2) return launch_bwd_one<D, BF16, DKDV, 2>(bp, nblocks, BH, st);
+    if (bp.bias_kind != RGD_BIAS_NONE) return launch_bwd_one<D, BF16, DKDV, 1>(bp, nblocks, BH, st);
+    return launch_bwd_one<D, BF16, DKDV, 0>(bp, nblocks, BH, st);
 }
 
 template <int D, bool BF16>
@@ -522,7 +576,17 @@ int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st) {
     if (int e = encode_heads_map(&bp.mv, p.v, p.B, p.H, p.Tk, p.d, p.v_sb, p.v_sh, p.v_sn, 64, BT, bf16)) return e;
     if (int e = encode_heads_map(&bp.mdo, p.d_o, p.B, p.H, p.Tq, p.d, p.do_sb, p.do_sh, p.do_sn, 64, BT, bf16)) return e;
     bp.bias = p.bias; bp.b_sb = p.b_sb; bp.b_sh = p.b_sh; bp.b_sq = p.b_sq;
-    bp.bias_kind = p.bias_kind; bp.bias_f32 = p.bias_f32; bp.bias_vec = 0;
+    bp.bias_kind = p.bias_kind; bp.bias_f32 = p.bias_f32;
+    // bias_vec: 0 scalar loads, 1 rows are 16-byte addressable (vector loads), 2 staged through TMA
+    bp.bias_vec = 0;
+    if (p.bias_kind != RGD_BIAS_NONE && !p.bias_f32 && is_aligned(p.bias, 16) && p.b_sb % 8 == 0 && p.b_sh % 8 == 0 &&
+        (p.bias_kind != RGD_BIAS_MATRIX || p.b_sq % 8 == 0))
+        bp.bias_vec = 1;
+    if (bias_tma_ok(p) && encode_bias_map(&bp.mbias, p, bf16) == RGD_OK) {
+        bp.bias_vec = 2;
+        bp.bias_h0 = p.b_sh == 0;
+        bp.bias_b0 = p.b_sb == 0;
+    }
     bp.lse2 = lse2; bp.delta_s = delta_s;
     bp.H = p.H; bp.Tq = p.Tq; bp.Tk = p.Tk; bp.Tq128 = Tq128; bp.causal = p.causal;
     bp.scale = p.scale; bp.scale_log2 = p.scale * LOG2E;

@@ -48,22 +48,44 @@ struct FwdTmaParams {
     const void *bias;
     int64_t b_sb, b_sh, b_sq;
     int bias_kind, bias_f32, bias_vec;
+    CUtensorMap mbias;          // BIAS == 2: (Tk, Tq, H or 1, B or 1) map over the bias, box 64 x 128
+    int bias_h0, bias_b0;       // bias broadcast over heads / batch: always coordinate 0
     float *lse;
     int H, Tq, Tk, Tq_rounded, causal;
     float scale_log2;   // softmax_scale * log2(e)
     int *status;        // device status word (bounded waits report here)
 };
 
-template <int D>
+// NT: query tiles per CTA.  BTMA: bias tiles (128 x 128, 16-bit, two 64-column
+// panels with 128-byte swizzle) staged by TMA, two stages per query tile.
+template <int D, int NT, bool BTMA>
 struct alignas(1024) FwdTmaSmem {
-    unsigned char q[2][TM * D * 2];
+    unsigned char q[NT][TM * D * 2];
     unsigned char k[2][TN * D * 2];
     unsigned char v[2][TN * D * 2];
+    unsigned char bias[BTMA ? NT * 2 : 1][BTMA ? TM * TN * 2 : 1024];
     uint64_t q_full, o_full;
     uint64_t s_full[2], p_full[2];
     uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    uint64_t b_full[2][2], b_empty[2][2];      // [tile][stage]
     uint32_t tmem_base;
 };
+
+// 32 bias values (times log2 e) of tile row `row_l`, tile columns [col0, col0+32), from a
+// TMA-staged tile: panel = col / 64, 16-byte chunk index XOR (row mod 8) inside the 128-byte row.
+template <bool BF16>
+__device__ __forceinline__ void bias_from_smem(const unsigned char *tile, int row_l, int col0, float (&b)[32]) {
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    const unsigned char *rowp = tile + (col0 >> 6) * (TM * 128) + row_l * 128;
+    const int c0 = (col0 & 63) >> 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        union { uint4 u; T v[8]; } cv;
+        cv.u = *reinterpret_cast<const uint4 *>(rowp + (((c0 + i) ^ (row_l & 7)) << 4));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) b[8 * i + e] = to_f32<T>(cv.v[e]) * LOG2E;
+    }
+}
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -116,8 +138,13 @@ __device__ __forceinline__ void load_bias32(const FwdTmaParams &p, const char *b
     }
 }
 
-template <int D, bool BF16, bool BIAS>
+// BIAS: 0 none, 1 read straight from global memory by the softmax threads (vector
+// bias, fp32 bias, unaligned views), 2 matrix bias staged tile by tile through TMA.
+template <int D, bool BF16, int BIAS>
 __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_constant__ FwdTmaParams p) {
+    // With staged bias tiles and head_dim 128 only one query tile fits in shared memory.
+    constexpr int NT = (BIAS == 2 && D == 128) ? 1 : 2;
+    constexpr uint32_t BIAS_BYTES = TM * TN * 2;
     constexpr int HALVES = D / 64;                 // 64-channel (128-byte) swizzle panels per tile
     constexpr uint32_t PANEL = 128 * 64 * 2;       // bytes of one 128-row panel
     constexpr uint32_t TILE_BYTES = TM * D * 2;
@@ -125,13 +152,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
 
     extern __shared__ unsigned char smem_raw[];
-    FwdTmaSmem<D> &sm = *reinterpret_cast<FwdTmaSmem<D> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    using Smem = FwdTmaSmem<D, NT, BIAS == 2>;
+    Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mblk = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;   // heavy causal tiles first
     const int bh = blockIdx.y;
     const int b = bh / p.H, h = bh - b * p.H;
-    const int m0 = mblk * 2 * TM;
+    const int m0 = mblk * NT * TM;
     // Key blocks each tile visits (a tile past the end of Q visits none; under
     // the causal mask tile 0 stops one block earlier than tile 1).
     int nb[2];
@@ -139,7 +167,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
     for (int t = 0; t < 2; ++t) {
         const int mt = m0 + t * TM;
         const int n_end = p.causal ? min(p.Tk, mt + TM) : p.Tk;
-        nb[t] = mt < p.Tq ? (n_end + TN - 1) / TN : 0;
+        nb[t] = (t < NT && mt < p.Tq) ? (n_end + TN - 1) / TN : 0;
     }
     const int nblk = max(nb[0], nb[1]);
     int *status = p.status;
@@ -154,6 +182,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
             mbar_init(&sm.k_empty[s], 1);
             mbar_init(&sm.v_full[s], 1);
             mbar_init(&sm.v_empty[s], 1);
+            for (int t = 0; t < 2; ++t) {
+                mbar_init(&sm.b_full[t][s], 1);
+                mbar_init(&sm.b_empty[t][s], 128);
+            }
         }
         fence_mbar_init();
     }
@@ -172,8 +204,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
             tma_prefetch_desc(&p.mq);
             tma_prefetch_desc(&p.mk);
             tma_prefetch_desc(&p.mv);
-            mbar_expect_tx(&sm.q_full, 2 * TILE_BYTES);
-            for (int t = 0; t < 2; ++t)
+            if constexpr (BIAS == 2) tma_prefetch_desc(&p.mbias);
+            mbar_expect_tx(&sm.q_full, NT * TILE_BYTES);
+            for (int t = 0; t < NT; ++t)
                 for (int hh = 0; hh < HALVES; ++hh)
                     tma_load_4d(sm.q[t] + hh * PANEL, &p.mq, &sm.q_full, hh * 64, m0 + t * TM, h, b);
             bool ok = true;
@@ -190,6 +223,17 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
                 for (int hh = 0; hh < HALVES; ++hh)
                     tma_load_4d(sm.v[s] + hh * PANEL, &p.mv, &sm.v_full[s], hh * 64, j * TN, h, b);
+                if constexpr (BIAS == 2) {
+                    for (int t = 0; t < NT && ok; ++t) {
+                        if (j >= nb[t]) continue;
+                        ok = mbar_wait(&sm.b_empty[t][s], ph ^ 1u, status, 13);
+                        if (!ok) break;
+                        mbar_expect_tx(&sm.b_full[t][s], BIAS_BYTES);
+                        for (int pn = 0; pn < 2; ++pn)
+                            tma_load_4d(sm.bias[t * 2 + s] + pn * (TM * 128), &p.mbias, &sm.b_full[t][s], j * TN + pn * 64,
+                                        m0 + t * TM, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                    }
+                }
             }
             if (!ok) {
                 // Give copies already in flight time to land before the CTA goes away.
@@ -267,7 +311,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
         const uint32_t s_col = t * 128, o_col = 256 + t * 128;
         const int my_nb = nb[t];
         const char *bias_bh = nullptr;
-        if constexpr (BIAS)
+        if constexpr (BIAS == 1)
             bias_bh = reinterpret_cast<const char *>(p.bias) +
                       ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
         const int brow = row < p.Tq ? row : (p.Tq - 1);     // rows past the end read a valid bias row
@@ -278,6 +322,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
             ok = mbar_wait(&sm.s_full[t], (uint32_t)j & 1u, status, 31);
             if (!ok) break;
             tc_fence_after_sync();
+            const unsigned char *btile = nullptr;
+            if constexpr (BIAS == 2) {
+                ok = mbar_wait(&sm.b_full[t][j & 1], (uint32_t)(j >> 1) & 1u, status, 33);
+                if (!ok) break;
+                btile = sm.bias[t * 2 + (j & 1)];
+            }
             const int n0 = j * TN;
             const bool need_mask = (n0 + TN > p.Tk) || (p.causal && n0 + TN > m0 + t * TM);
 
@@ -288,7 +338,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 uint32_t r0[32], r1[32];
                 tmem_ld32(lane_base + s_col + c * 64, r0);
                 tmem_ld32(lane_base + s_col + c * 64 + 32, r1);
-                if (!BIAS && !need_mask) {
+                if (BIAS == 0 && !need_mask) {
                     tmem_wait_ld();
                     float a = -INFINITY, bq = -INFINITY;
 #pragma unroll
@@ -301,12 +351,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf) {
                         float bb[32];
-                        if constexpr (BIAS) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
+                        if constexpr (BIAS == 1) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
+                        if constexpr (BIAS == 2) bias_from_smem<BF16>(btile, row_l, c * 64 + hf * 32, bb);
                         if (hf == 0) tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             float x = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
-                            if constexpr (BIAS) x += bb[i];
+                            if constexpr (BIAS != 0) x += bb[i];
                             if (need_mask) {
                                 const int col = n0 + c * 64 + hf * 32 + i;
                                 if (col >= p.Tk || (p.causal && col > row)) x = -INFINITY;
@@ -345,7 +396,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 tmem_ld32(lane_base + s_col + c * 64 + 32, r1);
                 uint32_t pk[32];
                 float ls0 = 0.f, ls1 = 0.f;
-                if (!BIAS && !need_mask) {
+                if (BIAS == 0 && !need_mask) {
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
@@ -362,13 +413,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf) {
                         float bb[32];
-                        if constexpr (BIAS) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
+                        if constexpr (BIAS == 1) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
+                        if constexpr (BIAS == 2) bias_from_smem<BF16>(btile, row_l, c * 64 + hf * 32, bb);
                         if (hf == 0) tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
                             float x0 = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
                             float x1 = __uint_as_float(hf ? r1[i + 1] : r0[i + 1]) * p.scale_log2;
-                            if constexpr (BIAS) {
+                            if constexpr (BIAS != 0) {
                                 x0 += bb[i];
                                 x1 += bb[i + 1];
                             }
@@ -389,6 +441,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&sm.p_full[t]);
+            if constexpr (BIAS == 2) mbar_arrive(&sm.b_empty[t][j & 1]);   // bias tile read twice, now free
         }
 
         // epilogue: O / l, LSE
@@ -455,22 +508,38 @@ bool tmem_fwd_eligible(const AttnParams &p) {
     return (p.d == 64 || p.d == 128) && p.Tq >= 1 && p.Tk >= 1 && p.vec_q && p.vec_k && p.vec_v && p.vec_o;
 }
 
-template <int D, bool BF16, bool BIAS>
-static int launch_fwd_one(const FwdTmaParams &fp, int nq_tiles, int BH, cudaStream_t st) {
-    const size_t smem = sizeof(FwdTmaSmem<D>) + 1024;
+template <int D, bool BF16, int BIAS>
+static int launch_fwd_one(const FwdTmaParams &fp, int Tq, int BH, cudaStream_t st) {
+    constexpr int NT = (BIAS == 2 && D == 128) ? 1 : 2;
+    const size_t smem = sizeof(FwdTmaSmem<D, NT, BIAS == 2>) + 1024;
     if (int e = cuda_status(cudaFuncSetAttribute(attn_fwd_tmem<D, BF16, BIAS>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
         return e;
-    dim3 grid(nq_tiles, BH);
+    dim3 grid((Tq + NT * TM - 1) / (NT * TM), BH);
     attn_fwd_tmem<D, BF16, BIAS><<<grid, FWD_THREADS, smem, st>>>(fp);
     count_launch();
     return check_launch();
 }
 
 template <int D, bool BF16>
-static int launch_fwd_tmem(const FwdTmaParams &fp, int nq_tiles, int BH, cudaStream_t st) {
-    if (fp.bias_kind != RGD_BIAS_NONE) return launch_fwd_one<D, BF16, true>(fp, nq_tiles, BH, st);
-    return launch_fwd_one<D, BF16, false>(fp, nq_tiles, BH, st);
+static int launch_fwd_tmem(const FwdTmaParams &fp, int bias_mode, int Tq, int BH, cudaStream_t st) {
+    if (bias_mode == 2) return launch_fwd_one<D, BF16, 2>(fp, Tq, BH, st);
+    if (bias_mode == 1) return launch_fwd_one<D, BF16, 1>(fp, Tq, BH, st);
+    return launch_fwd_one<D, BF16, 0>(fp, Tq, BH, st);
+}
+
+// A matrix bias in the tensor dtype whose rows are 16-byte addressable goes through TMA.
+bool bias_tma_ok(const AttnParams &p) {
+    if (p.bias_kind != RGD_BIAS_MATRIX || p.bias_f32) return false;
+    if (!is_aligned(p.bias, 16) || p.b_sq % 8 != 0 || p.b_sq <= 0 || p.Tk % 8 != 0) return false;
+    if (p.b_sh % 8 != 0 || p.b_sb % 8 != 0 || p.b_sh < 0 || p.b_sb < 0) return false;
+    return true;
+}
+
+// (Tk, Tq, H or 1, B or 1) map over the bias; broadcast dims (stride 0) become extent 1.
+int encode_bias_map(CUtensorMap *out, const AttnParams &p, bool bf16) {
+    const int64_t Hb = p.b_sh == 0 ? 1 : p.H, Bb = p.b_sb == 0 ? 1 : p.B;
+    return encode_heads_map(out, p.bias, Bb, Hb, p.Tq, p.Tk, p.b_sb, p.b_sh, p.b_sq, 64, TM, bf16);
 }
 
 int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
@@ -485,14 +554,21 @@ int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
     const int bel = p.bias_f32 ? 4 : 8;   // bias elements per 16 bytes
     fp.bias_vec = p.bias_kind != RGD_BIAS_NONE && is_aligned(p.bias, 16) && p.b_sb % bel == 0 && p.b_sh % bel == 0 &&
                   (p.bias_kind != RGD_BIAS_MATRIX || p.b_sq % bel == 0);
+    int bias_mode = p.bias_kind == RGD_BIAS_NONE ? 0 : 1;
+    if (bias_mode == 1 && bias_tma_ok(p) && encode_bias_map(&fp.mbias, p, bf16) == RGD_OK) {
+        bias_mode = 2;
+        fp.bias_h0 = p.b_sh == 0;
+        fp.bias_b0 = p.b_sb == 0;
+    }
     fp.lse = p.lse;
     fp.H = p.H; fp.Tq = p.Tq; fp.Tk = p.Tk; fp.Tq_rounded = p.Tq_rounded; fp.causal = p.causal;
     fp.scale_log2 = p.scale * LOG2E;
     fp.status = tmem_status_ptr();
     if (!fp.status) return RGD_E_DEVICE;
-    const int nq = (p.Tq + 2 * TM - 1) / (2 * TM), BH = p.B * p.H;
-    if (p.d == 128) return bf16 ? launch_fwd_tmem<128, true>(fp, nq, BH, st) : launch_fwd_tmem<128, false>(fp, nq, BH, st);
-    return bf16 ? launch_fwd_tmem<64, true>(fp, nq, BH, st) : launch_fwd_tmem<64, false>(fp, nq, BH, st);
+    const int BH = p.B * p.H;
+    if (p.d == 128)
+        return bf16 ? launch_fwd_tmem<128, true>(fp, bias_mode, p.Tq, BH, st) : launch_fwd_tmem<128, false>(fp, bias_mode, p.Tq, BH, st);
+    return bf16 ? launch_fwd_tmem<64, true>(fp, bias_mode, p.Tq, BH, st) : launch_fwd_tmem<64, false>(fp, bias_mode, p.Tq, BH, st);
 }
 
 // Read and clear the sticky device status word of the tensor-memory kernels
