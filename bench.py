@@ -69,7 +69,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.index), "-lms", "20"], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.t.start()
         except OSError:
@@ -78,7 +78,7 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(0.05)
             self.proc.terminate()
             self.proc.wait(timeout=5)
             self.t.join(timeout=2)
@@ -387,12 +387,14 @@ def main():
             ev[2].record()
         return o, grads
 
-    for _ in range(args.warmup):
-        attn_step(q, k, v, do)
-    barrier()
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    launches0 = lib.rgd_launch_count()
+    # the sampler starts before the warm-up (same load as the timed steps), so that short
+    # timed regions still get clock samples under load
     with ClockSampler(local) as clk:
+        for _ in range(args.warmup):
+            attn_step(q, k, v, do)
+        barrier()
+        launches0 = lib.rgd_launch_count()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         start.record()
