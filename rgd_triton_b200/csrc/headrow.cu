@@ -243,7 +243,7 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
 #pragma unroll
             for (int e = 0; e < VE; ++e) {
                 const int col = (t + j * tpr) * VE + e;
-                const float c = col < d ? xv[j * VE + e] - mean : 0.f;
+                const float c = (DFIX > 0 || col < d) ? xv[j * VE + e] - mean : 0.f;
                 xv[j * VE + e] = c;           // centred
                 s2 += c * c;
             }
@@ -293,8 +293,8 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
 #pragma unroll
                             for (int e = 0; e < VE; e += 2) {
                                 const float ge = g[j * VE + e], go = g[j * VE + e + 1];
-                                if (col + e < p.R) g[j * VE + e] = ge * cs[e] + go * sn[e];
-                                if (col + e + 1 < p.R) g[j * VE + e + 1] = go * cs[e + 1] - ge * sn[e + 1];
+                                if (pre[j] || col + e < p.R) g[j * VE + e] = ge * cs[e] + go * sn[e];
+                                if (pre[j] || col + e + 1 < p.R) g[j * VE + e + 1] = go * cs[e + 1] - ge * sn[e + 1];
                             }
                         } else {
                             const float me = g[j];
@@ -351,8 +351,8 @@ __device__ __forceinline__ void process_row(const HeadParams &p, const Vec<T, VE
                                 oe = xe * cs[e] + re * sn[e];
                                 oo = xo * cs[e + 1] + ro * sn[e + 1];
                             }
-                            if (col + e < p.R) res[j * VE + e] = oe;
-                            if (col + e + 1 < p.R) res[j * VE + e + 1] = oo;
+                            if (pre[j] || col + e < p.R) res[j * VE + e] = oe;
+                            if (pre[j] || col + e + 1 < p.R) res[j * VE + e + 1] = oo;
                         }
                     } else {
                         const float me = xv[j];
@@ -561,11 +561,17 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel_pipelined(const __gr
 // time.  Row r lives at base + r * D, so the per-row address arithmetic is one
 // multiply-add and the token index one or two fast divisions.  Same persistent
 // cp.async pipeline as head_kernel_pipelined.
-// Rows per thread and 16-byte slots per thread-row of the flat kernel.
-constexpr int FLAT_RPT = 2;
-constexpr int FLAT_VPT = 2;
+// Geometry of the flat kernel (16-byte slots per thread-row, rows per thread), chosen by
+// measurement: forward operators run best with a quarter row per thread (fewer shuffle
+// rounds and index computations per byte), the backward ones, which hold x and dy, with
+// an eighth of a row and two rows in flight.
+template <int OP> struct FlatGeom {
+    static constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
+    static constexpr int VPT = HAS_DY ? 2 : 4;
+    static constexpr int RPT = HAS_DY ? 2 : 1;
+};
 
-template <typename T, typename TP, int VPT, int OP, int D>
+template <typename T, typename TP, int VPT, int FLAT_RPT, int OP, int D>
 __global__ void __launch_bounds__(HEAD_THREADS) head_kernel_flat(const __grid_constant__ HeadParams p) {
     constexpr int VE = VecElems<T>::value;
     constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
@@ -726,12 +732,13 @@ int launch_pipelined(const HeadParams &p, int64_t tiles, cudaStream_t st) {
     return check_launch();
 }
 
-template <typename T, typename TP, int VPT, int OP, int D>
+template <typename T, typename TP, int OP, int D>
 int launch_flat(const HeadParams &p, int64_t tiles, cudaStream_t st) {
     constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
-    constexpr int SLOTS = (HAS_DY ? 2 : 1) * FLAT_RPT * VPT;
+    constexpr int VPT = FlatGeom<OP>::VPT, RPT = FlatGeom<OP>::RPT;
+    constexpr int SLOTS = (HAS_DY ? 2 : 1) * RPT * VPT;
     const size_t smem = (size_t)PIPE_STAGES * SLOTS * HEAD_THREADS * 16;
-    auto kernel = head_kernel_flat<T, TP, VPT, OP, D>;
+    auto kernel = head_kernel_flat<T, TP, VPT, RPT, OP, D>;
     if (smem > 32 * 1024)
         if (int e = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
             return e;
@@ -757,13 +764,13 @@ int launch_head(const HeadParams &p, bool vec, int vpt, int64_t grid, cudaStream
         int64_t tiles[2];
         HeadParams q = p;
         for (int i = 0; i < 2; ++i) {
-            const int rows_per_tile = (HEAD_THREADS / (p.d / (VE * FLAT_VPT))) * FLAT_RPT;
+            const int rows_per_tile = (HEAD_THREADS / (p.d / (VE * FlatGeom<OP>::VPT))) * FlatGeom<OP>::RPT;
             tiles[i] = ceil_div64(p.t[i].rows, rows_per_tile);
         }
         q.split = tiles[0];
         q.tiles1 = tiles[1];
-        if (p.d == 128) return launch_flat<T, TP, FLAT_VPT, OP, 128>(q, tiles[0] + tiles[1], st);
-        return launch_flat<T, TP, FLAT_VPT, OP, 64>(q, tiles[0] + tiles[1], st);
+        if (p.d == 128) return launch_flat<T, TP, OP, 128>(q, tiles[0] + tiles[1], st);
+        return launch_flat<T, TP, OP, 64>(q, tiles[0] + tiles[1], st);
     }
     if (vec) {
         if (vpt == 1) return launch_pipelined<T, TP, 1, OP>(p, grid, st);
@@ -854,7 +861,7 @@ int run_head(const HeadCall &c, cudaStream_t st) {
 
     const int rows_per_cta = (HEAD_THREADS / p.tpr) * ROWS_PER_THREAD;
     int64_t grid = 0;
-    bool all_flat = vec && (c.d * esize) % (16 * FLAT_VPT) == 0;
+    bool all_flat = vec && (c.d * esize) % (16 * FlatGeom<OP>::VPT) == 0;
     for (int i = 0; i < 2; ++i) {
         HeadTensor &ht = p.t[i];
         const rgd_heads &x = *c.x[i];
