@@ -187,14 +187,21 @@ __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant_
             if (++stage == ROW_STAGES) stage = 0;
         }
 
-        float ss = 0.f;
+        // fp32 copies, converted once
+        constexpr int NE = VPT * VE;
+        float xf[NE];
+        float df[BWD ? NE : 1];
 #pragma unroll
         for (int j = 0; j < VPT; ++j)
 #pragma unroll
             for (int e = 0; e < VE; ++e) {
-                const float v = to_f32<T>(xq[j].v[e]);
-                ss += v * v;
+                xf[j * VE + e] = to_f32<T>(xq[j].v[e]);
+                if (BWD) df[j * VE + e] = to_f32<T>(dq[j].v[e]);
             }
+
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NE; ++i) ss = fmaf(xf[i], xf[i], ss);
         ss = group_sum(ss, tpr, red, phase);
 
         // Row scale: rmsnorm_cached.py:75-76, l2normalize_cached.py:72-77.
@@ -206,50 +213,44 @@ __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant_
             r = (len < p.eps) ? (1.0f / p.eps) : (1.0f / len);
         }
 
+        T *orow = ob + (int64_t)n * s.son;
         if (!BWD) {
-            T *orow = ob + (int64_t)n * s.son;
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const int col = (t + j * tpr) * VE;
                 V yo;
 #pragma unroll
                 for (int e = 0; e < VE; ++e) {
-                    float v = to_f32<T>(xq[j].v[e]) * r;
+                    float v = xf[j * VE + e] * r;
                     if (RMS) v = v * wv[j * VE + e];
                     yo.v[e] = from_f32<T>(v);
                 }
                 if (valid && col < C) store_vec_stream<T, VE>(orow + col, yo);
             }
         } else {
-            // g = sum(xhat * dy * w) [/ C for RMS]: rmsnorm_cached.py:213-231,
+            // xhat, then g = sum(xhat * dy * w) [/ C for RMS]: rmsnorm_cached.py:213-231,
             // l2normalize_cached.py:214-226.
             float g = 0.f;
 #pragma unroll
-            for (int j = 0; j < VPT; ++j)
-#pragma unroll
-                for (int e = 0; e < VE; ++e) {
-                    const float xh = to_f32<T>(xq[j].v[e]) * r;
-                    const float d = to_f32<T>(dq[j].v[e]);
-                    g += RMS ? xh * d * wv[j * VE + e] : xh * d;
-                }
+            for (int i = 0; i < NE; ++i) {
+                xf[i] *= r;
+                g += RMS ? xf[i] * df[i] * wv[i] : xf[i] * df[i];
+            }
             g = group_sum(g, tpr, red, phase);
             if (RMS) g *= invC;
-
-            T *orow = ob + (int64_t)n * s.son;
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const int col = (t + j * tpr) * VE;
                 V yo;
 #pragma unroll
                 for (int e = 0; e < VE; ++e) {
-                    const float xh = to_f32<T>(xq[j].v[e]) * r;
-                    const float d = to_f32<T>(dq[j].v[e]);
+                    const int i = j * VE + e;
                     float v;
                     if (RMS) {
-                        v = (d * wv[j * VE + e] - xh * g) * r;
-                        if (OP == RMS_BWD) dwacc[j * VE + e] += xh * d;   // zero for padded rows
+                        v = (df[i] * wv[i] - xf[i] * g) * r;
+                        if (OP == RMS_BWD) dwacc[i] += xf[i] * df[i];   // zero for padded rows
                     } else {
-                        v = (d - xh * g) * r;
+                        v = (df[i] - xf[i] * g) * r;
                     }
                     yo.v[e] = from_f32<T>(v);
                 }
