@@ -36,6 +36,7 @@ bool bias_tma_ok(const AttnParams &p);
 int encode_bias_map(CUtensorMap *out, const AttnParams &p, bool bf16);
 
 constexpr int BWD_THREADS = 320;
+constexpr int DKDV_SUB_THREADS = 352;   // 8 compute warps, TMA producer, two MMA issuers
 constexpr int BT = 128;   // tile edge (queries and keys)
 
 struct BwdTmaParams {
@@ -481,6 +482,372 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
 }
 
 // ---------------------------------------------------------------------------
+// dK / dV without bias, sub-block pipelined.  Same roles and tiles as MODE 1 above,
+// but each 128-query block is processed as two 64-query sub-blocks whose score
+// columns are double-buffered in tensor memory: G1 / P of sub-block parity b in
+// columns [b*64, b*64+64), G2 / dS in [128 + b*64, ...).  While the compute warps
+// turn sub-block u's scores into P and dS, the tensor cores run the accumulation
+// GEMMs of sub-block u-1 and the score GEMMs of sub-block u+1, so the exponentials
+// leave the critical path (at the price of N = 64 score GEMMs).
+// ---------------------------------------------------------------------------
+template <int D>
+struct alignas(1024) DkdvSubSmem {
+    unsigned char x1[BT * D * 2], x2[BT * D * 2];            // K, V
+    unsigned char y1[2][BT * D * 2], y2[2][BT * D * 2];      // Q, dO, 2 stages
+    alignas(16) float lse_s[2][BT], dsc_s[2][BT];            // row statistics of the staged query block
+    uint64_t x_full, acc_full;
+    uint64_t y_full[2], y_empty[2];
+    uint64_t g1_full[2], g2_full[2], p_ready[2], ds_ready[2];   // per sub-block parity
+    uint64_t g1_free[2], g2_free[2];                            // accumulation GEMM has read P / dS
+    uint32_t tmem_base;
+};
+
+#ifdef RGD_ATTN_TIMING
+__device__ long long g_dbg[64];
+#define DBG_T(var) const long long var = clock64()
+#define DBG_ACC(slot, t0, t1) dbg[slot] += (t1) - (t0)
+#else
+#define DBG_T(var)
+#define DBG_ACC(slot, t0, t1)
+#endif
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const __grid_constant__ BwdTmaParams p) {
+    constexpr int HALVES = D / 64;
+    constexpr uint32_t PANEL = 128 * 64 * 2;
+    constexpr uint32_t TILE_BYTES = BT * D * 2;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t G1_COL = 0, G2_COL = 128, ACC1_COL = 256, ACC2_COL = 384;
+    constexpr uint32_t SUB_ROWS = 64 * 128;          // byte offset of query row 64 inside a panel
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+
+    extern __shared__ unsigned char smem_raw[];
+    DkdvSubSmem<D> &sm = *reinterpret_cast<DkdvSubSmem<D> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blk = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / p.H, h = bh - b * p.H;
+    const int r0 = blk * BT;                               // first key of this CTA
+    const int i_begin = p.causal ? r0 / BT : 0;
+    const int i_end = (p.Tq + BT - 1) / BT;
+    const int nit = max(i_end - i_begin, 0);
+    const int nsub = 2 * nit;
+    int *status = p.status;
+#ifdef RGD_ATTN_TIMING
+    long long dbg[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.x_full, 1);
+        mbar_init(&sm.acc_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.y_full[s], 1);
+            mbar_init(&sm.y_empty[s], 1);
+            mbar_init(&sm.g1_full[s], 1);
+            mbar_init(&sm.g2_full[s], 1);
+            mbar_init(&sm.g1_free[s], 1);
+            mbar_init(&sm.g2_free[s], 1);
+            mbar_init(&sm.p_ready[s], 128);
+            mbar_init(&sm.ds_ready[s], 128);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&sm.tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tbase = sm.tmem_base;
+
+#ifdef RGD_ATTN_TIMING
+    const long long k0 = clock64();
+#endif
+    if (warp == 8) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0 && nit > 0) {
+            tma_prefetch_desc(&p.mk);
+            tma_prefetch_desc(&p.mv);
+            tma_prefetch_desc(&p.mq);
+            tma_prefetch_desc(&p.mdo);
+            mbar_expect_tx(&sm.x_full, 2 * TILE_BYTES);
+            for (int hh = 0; hh < HALVES; ++hh) {
+                tma_load_4d(sm.x1 + hh * PANEL, &p.mk, &sm.x_full, hh * 64, r0, h, b);
+                tma_load_4d(sm.x2 + hh * PANEL, &p.mv, &sm.x_full, hh * 64, r0, h, b);
+            }
+            bool ok = true;
+            for (int it = 0; it < nit; ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+                ok = mbar_wait(&sm.y_empty[s], ph ^ 1u, status, 71);
+                if (!ok) break;
+                mbar_expect_tx(&sm.y_full[s], 2 * TILE_BYTES + 2 * BT * 4);
+                const int row = (i_begin + it) * BT;
+                bulk_load_1d(sm.lse_s[s], p.lse2 + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
+                bulk_load_1d(sm.dsc_s[s], p.delta_s + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
+                for (int hh = 0; hh < HALVES; ++hh) {
+                    tma_load_4d(sm.y1[s] + hh * PANEL, &p.mq, &sm.y_full[s], hh * 64, row, h, b);
+                    tma_load_4d(sm.y2[s] + hh * PANEL, &p.mdo, &sm.y_full[s], hh * 64, row, h, b);
+                }
+            }
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 9) {
+        // ---------------------- MMA issuer A: the score GEMMs ----------------------
+        // One thread can issue an MMA only every ~54 clocks whatever its size, which is as long
+        // as these N = 64 MMAs take to run, so the two kinds of GEMM get an issuing thread each.
+        if (lane == 0 && nit > 0) {
+            constexpr uint32_t idesc_g = make_idesc(BF16, BT, 64, false, false);
+            // Descriptors of every operand tile, encoded once; the loops below only add offsets.
+            const uint64_t dx1 = make_sdesc(smem_u32(sm.x1), 16, 1024), dx2 = make_sdesc(smem_u32(sm.x2), 16, 1024);
+            uint64_t dy1k[2], dy2k[2];                       // Q / dO per stage, K-major view
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                dy1k[s] = make_sdesc(smem_u32(sm.y1[s]), 16, 1024);
+                dy2k[s] = make_sdesc(smem_u32(sm.y2[s]), 16, 1024);
+            }
+            // score GEMM of sub-block u: [128 keys] x [64 queries], contraction over channels
+            auto issue_g = [&](int u, uint32_t col, uint64_t xd, uint64_t yd) {
+                const uint64_t ydu = sdesc_advance(yd, (u & 1) * SUB_ROWS);
+                const uint32_t dcol = tbase + col + (u & 1) * 64;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * PANEL + (kk % 4) * 32;
+                    umma_ss(dcol, sdesc_advance(xd, off), sdesc_advance(ydu, off), idesc_g, kk > 0);
+                }
+            };
+            bool ok = mbar_wait(&sm.x_full, 0, status, 81);
+            for (int u = 0; u < nsub && ok; ++u) {
+                const int sb = u & 1, it = u >> 1, s = it & 1;
+                if (sb == 0) {
+                    ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 82);
+                    if (!ok) break;
+                }
+                // the columns are free once the accumulation GEMM of sub-block u - 2 has read them
+                if (u >= 2) {
+                    ok = mbar_wait(&sm.g1_free[sb], (uint32_t)(it - 1) & 1u, status, 85);
+                    if (!ok) break;
+                }
+                tc_fence_after_sync();
+                issue_g(u, G1_COL, dx1, dy1k[s]);
+                umma_commit(&sm.g1_full[sb]);
+                if (u >= 2) {
+                    ok = mbar_wait(&sm.g2_free[sb], (uint32_t)(it - 1) & 1u, status, 86);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                }
+                issue_g(u, G2_COL, dx2, dy2k[s]);
+                umma_commit(&sm.g2_full[sb]);
+            }
+        }
+    } else if (warp == 10) {
+        // ------------------- MMA issuer B: the accumulation GEMMs -------------------
+        // All MMAs that add into dV / dK come from this one thread, in sub-block order, so the
+        // order of the floating-point sums is fixed.
+        if (lane == 0 && nit > 0) {
+            constexpr uint32_t idesc_acc = make_idesc(BF16, BT, D, false, true);
+            uint64_t dy1m[2], dy2m[2];                       // Q / dO per stage, MN-major view
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                dy1m[s] = make_sdesc(smem_u32(sm.y1[s]), PANEL, 1024);
+                dy2m[s] = make_sdesc(smem_u32(sm.y2[s]), PANEL, 1024);
+            }
+            // accumulation GEMM of sub-block u: contraction over its 64 queries (4 steps of 16),
+            // packed two per column into the first 32 columns of the sub-block's score columns
+            auto issue_acc = [&](int u, uint32_t acc_col, uint32_t a_col, uint64_t yd) {
+                const uint64_t ydu = sdesc_advance(yd, (u & 1) * SUB_ROWS);
+                const uint32_t acol = tbase + a_col + (u & 1) * 64;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma_ts(tbase + acc_col, acol + kk * 8, sdesc_advance(ydu, kk * 2048), idesc_acc, u > 0 || kk > 0);
+            };
+            bool ok = true;
+            for (int u = 0; u < nsub && ok; ++u) {
+                const int sb = u & 1, it = u >> 1, s = it & 1;
+                const uint32_t par = (uint32_t)it & 1u;
+                if (sb == 0) {
+                    ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 87);
+                    if (!ok) break;
+                }
+                ok = mbar_wait(&sm.p_ready[sb], par, status, 83);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_acc(u, ACC1_COL, G1_COL, dy2m[s]);            // dV += P^T dO
+                umma_commit(&sm.g1_free[sb]);
+                ok = mbar_wait(&sm.ds_ready[sb], par, status, 84);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_acc(u, ACC2_COL, G2_COL, dy1m[s]);            // dK += dS^T Q
+                umma_commit(&sm.g2_free[sb]);
+                if (sb == 1) umma_commit(&sm.y_empty[s]);            // both sub-blocks of this block consumed
+            }
+            umma_commit(&sm.acc_full);
+        }
+    } else {
+        // ------------------------------ compute warps ------------------------------
+        // Warps 0-3 own the even sub-blocks, warps 4-7 the odd ones: each thread handles one
+        // key row and all 64 queries of its sub-block, and the two groups run half a period
+        // apart, so one group's exponentials overlap the other's tensor-memory round trips.
+        const int row_l = (warp & 3) * 32 + lane;          // key row of the tile == TMEM lane
+        const int sb = warp >> 2;                          // sub-block parity this warp group owns
+        const int half = sb;                               // epilogue: which half of the channels
+        const int row = r0 + row_l;
+        const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+        const bool cta_key_tail = r0 + BT > p.Tk;
+        const uint32_t col = sb * 64;                      // this group's columns inside G1 / G2
+
+        bool ok = true;
+        for (int it = 0; it < nit; ++it) {
+            const uint32_t par = (uint32_t)it & 1u;
+            const int blk0 = (i_begin + it) * BT;
+            const int c0 = blk0 + sb * 64;                 // first query of the sub-block
+            const bool slow = cta_key_tail || (p.causal && blk0 == r0);
+            const int s = it & 1;
+            const float4 *lse4 = reinterpret_cast<const float4 *>(&sm.lse_s[s][sb * 64]);
+            const float4 *dsc4 = reinterpret_cast<const float4 *>(&sm.dsc_s[s][sb * 64]);
+            float pv[64];
+
+            // row statistics of this block have landed
+            DBG_T(c0t);
+            ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
+            if (!ok) break;
+            ok = mbar_wait(&sm.g1_full[sb], par, status, 91);
+            if (!ok) break;
+            DBG_T(c1t);
+            DBG_ACC(0, c0t, c1t);
+            tc_fence_after_sync();
+#ifndef RGD_DBG_NOCOMPUTE
+            {
+                uint32_t ra[32], rb[32];
+                tmem_ld32(lane_base + G1_COL + col, ra);
+                tmem_ld32(lane_base + G1_COL + col + 32, rb);
+                tmem_wait_ld();
+                if (!slow) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 l = lse4[i];
+                        pv[4 * i + 0] = ex2b(fmaf(__uint_as_float(ra[4 * i + 0]), p.scale_log2, -l.x));
+                        pv[4 * i + 1] = ex2b(fmaf(__uint_as_float(ra[4 * i + 1]), p.scale_log2, -l.y));
+                        pv[4 * i + 2] = ex2b(fmaf(__uint_as_float(ra[4 * i + 2]), p.scale_log2, -l.z));
+                        pv[4 * i + 3] = ex2b(fmaf(__uint_as_float(ra[4 * i + 3]), p.scale_log2, -l.w));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 l = lse4[8 + i];
+                        pv[32 + 4 * i + 0] = ex2b(fmaf(__uint_as_float(rb[4 * i + 0]), p.scale_log2, -l.x));
+                        pv[32 + 4 * i + 1] = ex2b(fmaf(__uint_as_float(rb[4 * i + 1]), p.scale_log2, -l.y));
+                        pv[32 + 4 * i + 2] = ex2b(fmaf(__uint_as_float(rb[4 * i + 2]), p.scale_log2, -l.z));
+                        pv[32 + 4 * i + 3] = ex2b(fmaf(__uint_as_float(rb[4 * i + 3]), p.scale_log2, -l.w));
+                    }
+                } else {
+                    const float *lf = &sm.lse_s[s][sb * 64];
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int qi = c0 + i;
+                        const bool masked = row >= p.Tk || qi >= p.Tq || (p.causal && row > qi);
+                        const float sv = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]);
+                        pv[i] = masked ? 0.f : ex2b(fmaf(sv, p.scale_log2, -lf[i]));
+                    }
+                }
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) pk[i] = pack16b<BF16>(pv[2 * i], pv[2 * i + 1]);
+                tmem_st32(lane_base + G1_COL + col, pk);
+                tmem_wait_st();
+            }
+#endif
+            tc_fence_before_sync();
+            mbar_arrive(&sm.p_ready[sb]);
+            DBG_T(c2t);
+            DBG_ACC(1, c1t, c2t);
+
+            ok = mbar_wait(&sm.g2_full[sb], par, status, 92);
+            if (!ok) break;
+            DBG_T(c3t);
+            DBG_ACC(2, c2t, c3t);
+            tc_fence_after_sync();
+#ifndef RGD_DBG_NOCOMPUTE
+            {
+                uint32_t ga[32], gb[32];
+                tmem_ld32(lane_base + G2_COL + col, ga);
+                tmem_ld32(lane_base + G2_COL + col + 32, gb);
+                tmem_wait_ld();
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float4 dd = dsc4[i];
+                    const uint32_t *g = i < 8 ? ga : gb;
+                    const int j = (i & 7) * 4;
+                    const float a0 = pv[4 * i + 0] * fmaf(__uint_as_float(g[j + 0]), p.scale, -dd.x);
+                    const float a1 = pv[4 * i + 1] * fmaf(__uint_as_float(g[j + 1]), p.scale, -dd.y);
+                    const float a2 = pv[4 * i + 2] * fmaf(__uint_as_float(g[j + 2]), p.scale, -dd.z);
+                    const float a3 = pv[4 * i + 3] * fmaf(__uint_as_float(g[j + 3]), p.scale, -dd.w);
+                    pk[2 * i] = pack16b<BF16>(a0, a1);
+                    pk[2 * i + 1] = pack16b<BF16>(a2, a3);
+                }
+                tmem_st32(lane_base + G2_COL + col, pk);
+                tmem_wait_st();
+            }
+#endif
+            tc_fence_before_sync();
+            mbar_arrive(&sm.ds_ready[sb]);
+            DBG_T(c4t);
+            DBG_ACC(3, c3t, c4t);
+        }
+#ifdef RGD_ATTN_TIMING
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 127) == 0)
+            for (int i = 0; i < 4; ++i) g_dbg[16 + 8 * sb + i] = dbg[i];
+#endif
+
+        // epilogue: dV, dK -> global
+        if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 93);
+        tc_fence_after_sync();
+        if (ok) {
+#pragma unroll
+            for (int o = 0; o < 2; ++o) {
+                T *base = reinterpret_cast<T *>(o == 0 ? p.out1 : p.out2);
+                const int64_t sb_ = o == 0 ? p.o1_sb : p.o2_sb, sh = o == 0 ? p.o1_sh : p.o2_sh,
+                              sn = o == 0 ? p.o1_sn : p.o2_sn;
+                T *orow = base + (int64_t)b * sb_ + (int64_t)h * sh + (int64_t)row * sn;
+                const uint32_t acc_col = o == 0 ? ACC1_COL : ACC2_COL;
+#pragma unroll 1
+                for (int c = 0; c < D / 64; ++c) {
+                    const int cc = half * (D / 2) + c * 32;
+                    uint32_t r[32];
+                    if (nit > 0) {
+                        tmem_ld32(lane_base + acc_col + cc, r);
+                        tmem_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = 0u;
+                    }
+                    if (row < p.Tk) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 v;
+                            v.x = pack16b<BF16>(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                            v.y = pack16b<BF16>(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                            v.z = pack16b<BF16>(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                            v.w = pack16b<BF16>(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                            *reinterpret_cast<uint4 *>(orow + cc + i) = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+#ifdef RGD_ATTN_TIMING
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_dbg[40] = clock64() - k0;
+#endif
+    if (warp == 0) tmem_dealloc(tbase, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
 // Row statistics for the backward: delta = rowsum(O * dO)
 // (flash_attn_triton_cached.py:249-292), stored pre-multiplied by the softmax
 // scale, and lse * log2(e).  Rows in [Tq, Tq128) get +inf / 0 so that query
@@ -547,11 +914,27 @@ static int launch_bwd_tmem(const BwdTmaParams &bp, int nblocks, int BH, cudaStre
 }
 
 template <int D, bool BF16>
+static int launch_dkdv_sub(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
+    const size_t smem = sizeof(DkdvSubSmem<D>) + 1024;
+    if (int e = cuda_status(cudaFuncSetAttribute(attn_bwd_dkdv_sub<D, BF16>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+        return e;
+    dim3 grid(nblocks, BH);
+    attn_bwd_dkdv_sub<D, BF16><<<grid, DKDV_SUB_THREADS, smem, st>>>(bp);
+    count_launch();
+    return check_launch();
+}
+
+template <int D, bool BF16>
 static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     const int BH = p.B * p.H;
     bp.out1 = p.dv; bp.o1_sb = p.dv_sb; bp.o1_sh = p.dv_sh; bp.o1_sn = p.dv_sn;
     bp.out2 = p.dk; bp.o2_sb = p.dk_sb; bp.o2_sh = p.dk_sh; bp.o2_sn = p.dk_sn;
-    if (int e = launch_bwd_tmem<D, BF16, true>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
+    if (bp.bias_kind == RGD_BIAS_NONE) {
+        if (int e = launch_dkdv_sub<D, BF16>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
+    } else if (int e = launch_bwd_tmem<D, BF16, true>(bp, (p.Tk + BT - 1) / BT, BH, st)) {
+        return e;
+    }
     bp.out1 = p.dq; bp.o1_sb = p.dq_sb; bp.o1_sh = p.dq_sh; bp.o1_sn = p.dq_sn;
     bp.out2 = nullptr;
     return launch_bwd_tmem<D, BF16, false>(bp, (p.Tq + BT - 1) / BT, BH, st);
@@ -598,3 +981,9 @@ int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st) {
 
 }  // namespace attn
 }  // namespace rgd
+
+#ifdef RGD_ATTN_TIMING
+extern "C" int rgd_dbg_fetch(long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, rgd::attn::g_dbg, sizeof(long long) * 64);
+}
+#endif

@@ -81,6 +81,14 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -172,6 +180,14 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_
     d |= 1ull << 46;
     d |= 2ull << 61;
     return d;
+}
+
+// The same descriptor `bytes` further into shared memory.  The start-address field is the
+// low 14 bits in 16-byte units and shared memory ends below 2^18 bytes, so the sum never
+// carries into the next field: one add instead of re-encoding the descriptor per MMA (the
+// issuing thread's instruction count is what bounds the MMA rate of small tiles).
+__device__ __forceinline__ uint64_t sdesc_advance(uint64_t desc, uint32_t bytes) {
+    return desc + (uint64_t)(bytes >> 4);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
