@@ -36,7 +36,7 @@ bool bias_tma_ok(const AttnParams &p);
 int encode_bias_map(CUtensorMap *out, const AttnParams &p, bool bf16);
 
 constexpr int BWD_THREADS = 320;
-constexpr int DKDV_SUB_THREADS = 352;   // 8 compute warps, TMA producer, two MMA issuers
+constexpr int DKDV_SUB_THREADS = 384;   // 8 compute warps, TMA producer, three MMA issuers
 constexpr int BT = 128;   // tile edge (queries and keys)
 
 struct BwdTmaParams {
@@ -340,6 +340,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                 uint32_t ra[32], rb[32];
                 tmem_ld32(lane_base + G1_COL + half * 64, ra);
                 tmem_ld32(lane_base + G1_COL + half * 64 + 32, rb);
+                if (!DKDV) {
+                    // dQ: P stays in registers, so the score columns are free as soon as they
+                    // have been read and the next block's score GEMM runs under the exponentials
+                    tmem_wait_ld();
+                    tc_fence_before_sync();
+                    mbar_arrive(&sm.p_ready);
+                }
                 if (!slow) {
                     if (DKDV) {
                         float4 l4[16];
@@ -384,10 +391,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                     for (int i = 0; i < 32; ++i) pk[i] = pack16b<BF16>(pv[2 * i], pv[2 * i + 1]);
                     tmem_st32(lane_base + G1_COL + half * 64, pk);
                     tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(&sm.p_ready);
                 }
             }
-            tc_fence_before_sync();
-            mbar_arrive(&sm.p_ready);
 
             ok = mbar_wait(&sm.g2_full, par, status, 62);
             if (!ok) break;
@@ -594,30 +601,20 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
             if (!ok)
                 for (int i = 0; i < 64; ++i) __nanosleep(1000);
         }
-    } else if (warp == 9) {
-        // ---------------------- MMA issuer A: the score GEMMs ----------------------
+    } else if (warp == 9 || warp == 10) {
+        // ------------- MMA issuers A1 / A2: the score GEMMs K Q^T and V dO^T -------------
         // One thread can issue an MMA only every ~54 clocks whatever its size, which is as long
-        // as these N = 64 MMAs take to run, so the two kinds of GEMM get an issuing thread each.
+        // as these N = 64 MMAs take to run, so each kind of GEMM gets its own issuing thread.
         if (lane == 0 && nit > 0) {
+            const bool second = warp == 10;
             constexpr uint32_t idesc_g = make_idesc(BF16, BT, 64, false, false);
-            // Descriptors of every operand tile, encoded once; the loops below only add offsets.
-            const uint64_t dx1 = make_sdesc(smem_u32(sm.x1), 16, 1024), dx2 = make_sdesc(smem_u32(sm.x2), 16, 1024);
-            uint64_t dy1k[2], dy2k[2];                       // Q / dO per stage, K-major view
+            // Descriptors of the operand tiles, encoded once; the loop below only adds offsets.
+            const uint64_t dx = make_sdesc(smem_u32(second ? sm.x2 : sm.x1), 16, 1024);
+            uint64_t dyk[2];                                 // Q (or dO) per stage, K-major view
 #pragma unroll
-            for (int s = 0; s < 2; ++s) {
-                dy1k[s] = make_sdesc(smem_u32(sm.y1[s]), 16, 1024);
-                dy2k[s] = make_sdesc(smem_u32(sm.y2[s]), 16, 1024);
-            }
-            // score GEMM of sub-block u: [128 keys] x [64 queries], contraction over channels
-            auto issue_g = [&](int u, uint32_t col, uint64_t xd, uint64_t yd) {
-                const uint64_t ydu = sdesc_advance(yd, (u & 1) * SUB_ROWS);
-                const uint32_t dcol = tbase + col + (u & 1) * 64;
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk / 4) * PANEL + (kk % 4) * 32;
-                    umma_ss(dcol, sdesc_advance(xd, off), sdesc_advance(ydu, off), idesc_g, kk > 0);
-                }
-            };
+            for (int s = 0; s < 2; ++s) dyk[s] = make_sdesc(smem_u32(second ? sm.y2[s] : sm.y1[s]), 16, 1024);
+            const uint32_t gcol = tbase + (second ? G2_COL : G1_COL);
+            uint64_t *full = second ? sm.g2_full : sm.g1_full, *free_ = second ? sm.g2_free : sm.g1_free;
             bool ok = mbar_wait(&sm.x_full, 0, status, 81);
             for (int u = 0; u < nsub && ok; ++u) {
                 const int sb = u & 1, it = u >> 1, s = it & 1;
@@ -627,22 +624,22 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 }
                 // the columns are free once the accumulation GEMM of sub-block u - 2 has read them
                 if (u >= 2) {
-                    ok = mbar_wait(&sm.g1_free[sb], (uint32_t)(it - 1) & 1u, status, 85);
+                    ok = mbar_wait(&free_[sb], (uint32_t)(it - 1) & 1u, status, 85);
                     if (!ok) break;
                 }
                 tc_fence_after_sync();
-                issue_g(u, G1_COL, dx1, dy1k[s]);
-                umma_commit(&sm.g1_full[sb]);
-                if (u >= 2) {
-                    ok = mbar_wait(&sm.g2_free[sb], (uint32_t)(it - 1) & 1u, status, 86);
-                    if (!ok) break;
-                    tc_fence_after_sync();
+                // [128 keys] x [64 queries of sub-block u], contraction over channels
+                const uint64_t ydu = sdesc_advance(dyk[s], sb * SUB_ROWS);
+                const uint32_t dcol = gcol + sb * 64;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * PANEL + (kk % 4) * 32;
+                    umma_ss(dcol, sdesc_advance(dx, off), sdesc_advance(ydu, off), idesc_g, kk > 0);
                 }
-                issue_g(u, G2_COL, dx2, dy2k[s]);
-                umma_commit(&sm.g2_full[sb]);
+                umma_commit(&full[sb]);
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 11) {
         // ------------------- MMA issuer B: the accumulation GEMMs -------------------
         // All MMAs that add into dV / dK come from this one thread, in sub-block order, so the
         // order of the floating-point sums is fixed.
@@ -671,19 +668,32 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                     ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 87);
                     if (!ok) break;
                 }
+                DBG_T(b0);
                 ok = mbar_wait(&sm.p_ready[sb], par, status, 83);
                 if (!ok) break;
+                DBG_T(b1);
+                DBG_ACC(0, b0, b1);
                 tc_fence_after_sync();
                 issue_acc(u, ACC1_COL, G1_COL, dy2m[s]);            // dV += P^T dO
                 umma_commit(&sm.g1_free[sb]);
+                DBG_T(b2);
+                DBG_ACC(1, b1, b2);
                 ok = mbar_wait(&sm.ds_ready[sb], par, status, 84);
                 if (!ok) break;
+                DBG_T(b3);
+                DBG_ACC(2, b2, b3);
                 tc_fence_after_sync();
                 issue_acc(u, ACC2_COL, G2_COL, dy1m[s]);            // dK += dS^T Q
                 umma_commit(&sm.g2_free[sb]);
                 if (sb == 1) umma_commit(&sm.y_empty[s]);            // both sub-blocks of this block consumed
+                DBG_T(b4);
+                DBG_ACC(3, b3, b4);
             }
             umma_commit(&sm.acc_full);
+#ifdef RGD_ATTN_TIMING
+            if (blockIdx.x == 0 && blockIdx.y == 0)
+                for (int i = 0; i < 4; ++i) g_dbg[8 + i] = dbg[i];
+#endif
         }
     } else {
         // ------------------------------ compute warps ------------------------------
