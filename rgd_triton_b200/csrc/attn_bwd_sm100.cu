@@ -86,6 +86,15 @@ __device__ __forceinline__ uint32_t pack16b(float a, float b) {
 // BIAS: whether an additive bias exists; the no-bias instantiation carries none of
 // the bias code (and none of its register pressure).
 // (BIAS: 0 none, 1 read from global memory by the compute threads, 2 staged through TMA.)
+#ifdef RGD_ATTN_TIMING
+__device__ long long g_dbg[64];
+#define DBG_T(var) const long long var = clock64()
+#define DBG_ACC(slot, t0, t1) dbg[slot] += (t1) - (t0)
+#else
+#define DBG_T(var)
+#define DBG_ACC(slot, t0, t1)
+#endif
+
 template <int D, bool BF16, bool DKDV, int BIAS>
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_constant__ BwdTmaParams p) {
     constexpr int BSTAGES = BIAS == 2 ? (D == 64 ? 2 : 1) : 0;
@@ -115,6 +124,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
     }
     const int nit = max(i_end - i_begin, 0);
     int *status = p.status;
+#ifdef RGD_ATTN_TIMING
+    long long dbg[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long k0 = clock64();
+#endif
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.x_full, 1);
@@ -213,20 +226,29 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
             for (int it = 0; it < nit && ok; ++it) {
                 const int s = it & 1, sn = s ^ 1;
                 const uint32_t par = (uint32_t)it & 1u;
+                DBG_T(m0);
                 ok = mbar_wait(&sm.p_ready, par, status, 53);
                 if (!ok) break;
+                DBG_T(m1);
+                DBG_ACC(0, m0, m1);
                 tc_fence_after_sync();
                 if (DKDV) issue_acc(ACC1_COL, G1_COL, smem_u32(sm.y2[s]), it == 0);     // dV += P^T dO
                 const bool more = it + 1 < nit;
                 if (more) {
                     ok = mbar_wait(&sm.y_full[sn], (uint32_t)((it + 1) >> 1) & 1u, status, 54);
                     if (!ok) break;
+                    DBG_T(my);
+                    DBG_ACC(4, m1, my);
                     tc_fence_after_sync();
                     issue_g(G1_COL, x1a, smem_u32(sm.y1[sn]));
                     umma_commit(&sm.g1_full);
                 }
+                DBG_T(m2);
+                DBG_ACC(1, m1, m2);
                 ok = mbar_wait(&sm.ds_ready, par, status, 55);
                 if (!ok) break;
+                DBG_T(m3);
+                DBG_ACC(2, m2, m3);
                 tc_fence_after_sync();
                 issue_acc(DKDV ? ACC2_COL : ACC1_COL, G2_COL, smem_u32(sm.y1[s]), it == 0);   // dK += dS^T Q | dQ += dS K
                 umma_commit(&sm.y_empty[s]);
@@ -234,8 +256,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                     issue_g(G2_COL, x2a, smem_u32(sm.y2[sn]));
                     umma_commit(&sm.g2_full);
                 }
+                DBG_T(m4);
+                DBG_ACC(3, m3, m4);
             }
             umma_commit(&sm.acc_full);
+#ifdef RGD_ATTN_TIMING
+            if (!DKDV && blockIdx.x == 0 && blockIdx.y == 0)
+                { for (int i = 0; i < 4; ++i) g_dbg[48 + i] = dbg[i]; g_dbg[57] = dbg[4]; }
+#endif
         }
     } else {
         // ------------------------------ compute warps ------------------------------
@@ -333,8 +361,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                 }
             }
 
+            DBG_T(c0t);
             ok = mbar_wait(&sm.g1_full, par, status, 61);
             if (!ok) break;
+            DBG_T(c1t);
+            DBG_ACC(0, c0t, c1t);
             tc_fence_after_sync();
             {
                 uint32_t ra[32], rb[32];
@@ -396,8 +427,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                 }
             }
 
+            DBG_T(c2t);
+            DBG_ACC(1, c1t, c2t);
             ok = mbar_wait(&sm.g2_full, par, status, 62);
             if (!ok) break;
+            DBG_T(c3t);
+            DBG_ACC(2, c2t, c3t);
             tc_fence_after_sync();
             {
                 uint32_t ga[32], gb[32];
@@ -441,7 +476,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
             }
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_ready);
+            DBG_T(c4t);
+            DBG_ACC(3, c3t, c4t);
         }
+#ifdef RGD_ATTN_TIMING
+        if (!DKDV && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+            for (int i = 0; i < 4; ++i) g_dbg[52 + i] = dbg[i];
+            g_dbg[56] = clock64() - k0;
+        }
+#endif
 
         // epilogue: accumulators -> global
         if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 63);
@@ -508,15 +551,6 @@ struct alignas(1024) DkdvSubSmem {
     uint64_t g1_free[2], g2_free[2];                            // accumulation GEMM has read P / dS
     uint32_t tmem_base;
 };
-
-#ifdef RGD_ATTN_TIMING
-__device__ long long g_dbg[64];
-#define DBG_T(var) const long long var = clock64()
-#define DBG_ACC(slot, t0, t1) dbg[slot] += (t1) - (t0)
-#else
-#define DBG_T(var)
-#define DBG_ACC(slot, t0, t1)
-#endif
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const __grid_constant__ BwdTmaParams p) {
@@ -858,6 +892,290 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
 }
 
 // ---------------------------------------------------------------------------
+// dQ without bias, pipelined.  One CTA per 128-query tile, looping over key blocks:
+//   S = Q K^T, dP = dO V^T (SS MMAs), P = exp2(S * scale * log2e - lse2) in registers,
+//   dS = P * (dP * scale - delta_s) packed into the dP columns, dQ += dS K (TS MMA).
+// What bounds the loop is latency, not arithmetic, so every hand-off gets slack:
+//  * K tiles sit in a ring of three (a tile is needed from its score GEMM until its dQ GEMM,
+//    one whole block later, so with two the next load would start only when it is already
+//    needed); V tiles, used by one GEMM only, in a ring of two.
+//  * The score columns are double-buffered (tensor-memory columns 0 and 384), so the score
+//    GEMM runs a block ahead of the compute warps.
+//  * Two MMA-issuing threads (score GEMMs / dQ GEMMs): one thread can issue an MMA only
+//    every ~54 clocks whatever its size.  All dQ MMAs come from one thread, in block order,
+//    so the order of the floating-point sums is fixed.
+// ---------------------------------------------------------------------------
+template <int D>
+struct alignas(1024) DqPipeSmem {
+    unsigned char xq[BT * D * 2], xdo[BT * D * 2];           // Q, dO of this CTA's query tile
+    unsigned char k[3][BT * D * 2], v[2][BT * D * 2];
+    uint64_t x_full, g2_full, ds_ready, g2_free, acc_full;
+    uint64_t k_full[3], k_empty[3], v_full[2], v_empty[2];
+    uint64_t g1_full[2], s_read[2];                          // per score-column buffer
+    uint32_t tmem_base;
+};
+constexpr int DQ_PIPE_THREADS = 352;   // 8 compute warps, TMA producer, two MMA issuers
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __grid_constant__ BwdTmaParams p) {
+    constexpr int HALVES = D / 64;
+    constexpr uint32_t PANEL = 128 * 64 * 2;
+    constexpr uint32_t TILE_BYTES = BT * D * 2;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t G1A_COL = 0, G2_COL = 128, ACC_COL = 256, G1B_COL = 384;
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+
+    extern __shared__ unsigned char smem_raw[];
+    DqPipeSmem<D> &sm = *reinterpret_cast<DqPipeSmem<D> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blk = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / p.H, h = bh - b * p.H;
+    const int r0 = blk * BT;                               // first query of this CTA
+    const int i_end = ((p.causal ? min(p.Tk, r0 + BT) : p.Tk) + BT - 1) / BT;
+    const int nit = max(i_end, 0);
+    int *status = p.status;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.x_full, 1);
+        mbar_init(&sm.g2_full, 1);
+        mbar_init(&sm.ds_ready, 256);
+        mbar_init(&sm.g2_free, 1);
+        mbar_init(&sm.acc_full, 1);
+        for (int s = 0; s < 3; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
+            mbar_init(&sm.g1_full[s], 1);
+            mbar_init(&sm.s_read[s], 256);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&sm.tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tbase = sm.tmem_base;
+
+    if (warp == 8) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0 && nit > 0) {
+            tma_prefetch_desc(&p.mq);
+            tma_prefetch_desc(&p.mdo);
+            tma_prefetch_desc(&p.mk);
+            tma_prefetch_desc(&p.mv);
+            mbar_expect_tx(&sm.x_full, 2 * TILE_BYTES);
+            for (int hh = 0; hh < HALVES; ++hh) {
+                tma_load_4d(sm.xq + hh * PANEL, &p.mq, &sm.x_full, hh * 64, r0, h, b);
+                tma_load_4d(sm.xdo + hh * PANEL, &p.mdo, &sm.x_full, hh * 64, r0, h, b);
+            }
+            bool ok = true;
+            int ks = 0;
+            uint32_t kph = 0;                              // phase of the K ring slot's previous use
+            for (int it = 0; it < nit; ++it) {
+                const int row = it * BT;
+                ok = mbar_wait(&sm.k_empty[ks], kph ^ 1u, status, 41);
+                if (!ok) break;
+                mbar_expect_tx(&sm.k_full[ks], TILE_BYTES);
+                for (int hh = 0; hh < HALVES; ++hh)
+                    tma_load_4d(sm.k[ks] + hh * PANEL, &p.mk, &sm.k_full[ks], hh * 64, row, h, b);
+                if (++ks == 3) { ks = 0; kph ^= 1u; }
+                const int vs = it & 1;
+                ok = mbar_wait(&sm.v_empty[vs], ((uint32_t)(it >> 1) & 1u) ^ 1u, status, 42);
+                if (!ok) break;
+                mbar_expect_tx(&sm.v_full[vs], TILE_BYTES);
+                for (int hh = 0; hh < HALVES; ++hh)
+                    tma_load_4d(sm.v[vs] + hh * PANEL, &p.mv, &sm.v_full[vs], hh * 64, row, h, b);
+            }
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 9) {
+        // ---------------------- MMA issuer A: the score GEMMs ----------------------
+        if (lane == 0 && nit > 0) {
+            constexpr uint32_t idesc_g = make_idesc(BF16, BT, BT, false, false);
+            const uint64_t dxq = make_sdesc(smem_u32(sm.xq), 16, 1024), dxdo = make_sdesc(smem_u32(sm.xdo), 16, 1024);
+            auto issue_g = [&](uint32_t col, uint64_t xd, uint64_t yd) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * PANEL + (kk % 4) * 32;
+                    umma_ss(tbase + col, sdesc_advance(xd, off), sdesc_advance(yd, off), idesc_g, kk > 0);
+                }
+            };
+            // S of block j into score buffer j & 1
+            int ks = 0;                                    // K ring slot and phase of block j
+            uint32_t kph = 0;
+            auto issue_g1 = [&](int j) -> bool {
+                if (!mbar_wait(&sm.k_full[ks], kph, status, 52)) return false;
+                if (j >= 2 && !mbar_wait(&sm.s_read[j & 1], (uint32_t)((j >> 1) - 1) & 1u, status, 53)) return false;
+                tc_fence_after_sync();
+                issue_g((j & 1) ? G1B_COL : G1A_COL, dxq, make_sdesc(smem_u32(sm.k[ks]), 16, 1024));
+                umma_commit(&sm.g1_full[j & 1]);
+                if (++ks == 3) { ks = 0; kph ^= 1u; }
+                return true;
+            };
+            bool ok = mbar_wait(&sm.x_full, 0, status, 51);
+            if (ok) ok = issue_g1(0);
+            for (int it = 0; it < nit && ok; ++it) {
+                if (it + 1 < nit) {
+                    ok = issue_g1(it + 1);
+                    if (!ok) break;
+                }
+                const int vs = it & 1;
+                ok = mbar_wait(&sm.v_full[vs], (uint32_t)(it >> 1) & 1u, status, 54);
+                if (!ok) break;
+                // the dP columns are free once the dQ GEMM of the block before has read dS
+                if (it >= 1) {
+                    ok = mbar_wait(&sm.g2_free, (uint32_t)(it - 1) & 1u, status, 55);
+                    if (!ok) break;
+                }
+                tc_fence_after_sync();
+                issue_g(G2_COL, dxdo, make_sdesc(smem_u32(sm.v[vs]), 16, 1024));
+                umma_commit(&sm.g2_full);
+                umma_commit(&sm.v_empty[vs]);
+            }
+        }
+    } else if (warp == 10) {
+        // ---------------------- MMA issuer B: the dQ GEMMs ----------------------
+        if (lane == 0 && nit > 0) {
+            constexpr uint32_t idesc_acc = make_idesc(BF16, BT, D, false, true);
+            bool ok = true;
+            int ks = 0;
+            uint32_t kph = 0;
+            for (int it = 0; it < nit && ok; ++it) {
+                ok = mbar_wait(&sm.k_full[ks], kph, status, 56);
+                if (!ok) break;
+                ok = mbar_wait(&sm.ds_ready, (uint32_t)it & 1u, status, 57);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint64_t dkm = make_sdesc(smem_u32(sm.k[ks]), PANEL, 1024);   // K as [key][channel], MN-major
+                // each half of the compute threads packed its 64 keys into the first 32 of its own 64 columns
+#pragma unroll
+                for (int kk = 0; kk < BT / 16; ++kk)
+                    umma_ts(tbase + ACC_COL, tbase + G2_COL + (kk >> 2) * 64 + (kk & 3) * 8,
+                            sdesc_advance(dkm, kk * 2048), idesc_acc, it > 0 || kk > 0);
+                umma_commit(&sm.g2_free);
+                umma_commit(&sm.k_empty[ks]);
+                if (++ks == 3) { ks = 0; kph ^= 1u; }
+            }
+            umma_commit(&sm.acc_full);
+        }
+    } else {
+        // ------------------------------ compute warps ------------------------------
+        const int row_l = (warp & 3) * 32 + lane;          // query row of the tile == TMEM lane
+        const int half = warp >> 2;                        // which 64 of the block's 128 keys
+        const int row = r0 + row_l;
+        const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+        // rows past Tq hold +inf / 0, so they yield P = 0
+        const float lse_row = p.lse2[(int64_t)bh * p.Tq128 + row];
+        const float dsc_row = p.delta_s[(int64_t)bh * p.Tq128 + row];
+
+        bool ok = true;
+        for (int it = 0; it < nit; ++it) {
+            const int gb = it & 1;
+            const int blk0 = it * BT;
+            const int c0 = blk0 + half * 64;               // first key this thread handles
+            // blocks that need per-element masking: the diagonal blocks under the causal mask
+            // and the block touching the end of the keys
+            const bool slow = (p.causal && blk0 + BT > r0) || blk0 + BT > p.Tk;
+            float pv[64];
+
+            ok = mbar_wait(&sm.g1_full[gb], (uint32_t)(it >> 1) & 1u, status, 61);
+            if (!ok) break;
+            tc_fence_after_sync();
+            {
+                uint32_t ra[32], rb[32];
+                const uint32_t gcol = (gb ? G1B_COL : G1A_COL) + half * 64;
+                tmem_ld32(lane_base + gcol, ra);
+                tmem_ld32(lane_base + gcol + 32, rb);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.s_read[gb]);               // P stays in registers: the buffer is free
+                if (!slow) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        pv[i] = ex2b(fmaf(__uint_as_float(ra[i]), p.scale_log2, -lse_row));
+                        pv[32 + i] = ex2b(fmaf(__uint_as_float(rb[i]), p.scale_log2, -lse_row));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int kj = c0 + i;
+                        const bool masked = kj >= p.Tk || row >= p.Tq || (p.causal && kj > row);
+                        const float x = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]);
+                        pv[i] = masked ? 0.f : ex2b(fmaf(x, p.scale_log2, -lse_row));
+                    }
+                }
+            }
+
+            ok = mbar_wait(&sm.g2_full, (uint32_t)it & 1u, status, 62);
+            if (!ok) break;
+            tc_fence_after_sync();
+            {
+                uint32_t ga[32], gb2[32];
+                tmem_ld32(lane_base + G2_COL + half * 64, ga);
+                tmem_ld32(lane_base + G2_COL + half * 64 + 32, gb2);
+                tmem_wait_ld();
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float a0 = pv[2 * i] * fmaf(__uint_as_float(ga[2 * i]), p.scale, -dsc_row);
+                    const float a1 = pv[2 * i + 1] * fmaf(__uint_as_float(ga[2 * i + 1]), p.scale, -dsc_row);
+                    pk[i] = pack16b<BF16>(a0, a1);
+                    const float b0 = pv[32 + 2 * i] * fmaf(__uint_as_float(gb2[2 * i]), p.scale, -dsc_row);
+                    const float b1 = pv[32 + 2 * i + 1] * fmaf(__uint_as_float(gb2[2 * i + 1]), p.scale, -dsc_row);
+                    pk[16 + i] = pack16b<BF16>(b0, b1);
+                }
+                tmem_st32(lane_base + G2_COL + half * 64, pk);
+                tmem_wait_st();
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&sm.ds_ready);
+        }
+
+        // epilogue: dQ -> global
+        if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 63);
+        tc_fence_after_sync();
+        if (ok) {
+            T *orow = reinterpret_cast<T *>(p.out1) + (int64_t)b * p.o1_sb + (int64_t)h * p.o1_sh + (int64_t)row * p.o1_sn;
+#pragma unroll 1
+            for (int c = 0; c < D / 64; ++c) {
+                const int col = half * (D / 2) + c * 32;
+                uint32_t r[32];
+                if (nit > 0) {
+                    tmem_ld32(lane_base + ACC_COL + col, r);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = 0u;
+                }
+                if (row < p.Tq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack16b<BF16>(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                        v.y = pack16b<BF16>(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                        v.z = pack16b<BF16>(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                        v.w = pack16b<BF16>(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                        *reinterpret_cast<uint4 *>(orow + col + i) = v;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tbase, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
 // Row statistics for the backward: delta = rowsum(O * dO)
 // (flash_attn_triton_cached.py:249-292), stored pre-multiplied by the softmax
 // scale, and lse * log2(e).  Rows in [Tq, Tq128) get +inf / 0 so that query
@@ -947,6 +1265,16 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     }
     bp.out1 = p.dq; bp.o1_sb = p.dq_sb; bp.o1_sh = p.dq_sh; bp.o1_sn = p.dq_sn;
     bp.out2 = nullptr;
+    if (bp.bias_kind == RGD_BIAS_NONE) {
+        const size_t smem = sizeof(DqPipeSmem<D>) + 1024;
+        if (int e = cuda_status(cudaFuncSetAttribute(attn_bwd_dq_pipe<D, BF16>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+            return e;
+        dim3 grid((p.Tq + BT - 1) / BT, BH);
+        attn_bwd_dq_pipe<D, BF16><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp);
+        count_launch();
+        return check_launch();
+    }
     return launch_bwd_tmem<D, BF16, false>(bp, (p.Tq + BT - 1) / BT, BH, st);
 }
 
