@@ -899,8 +899,10 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
 //  * K tiles sit in a ring of three (a tile is needed from its score GEMM until its dQ GEMM,
 //    one whole block later, so with two the next load would start only when it is already
 //    needed); V tiles, used by one GEMM only, in a ring of two.
-//  * The score columns are double-buffered (tensor-memory columns 0 and 384), so the score
-//    GEMM runs a block ahead of the compute warps.
+//  * The compute warps form dS of block i and, in the same pass, P of block i + 1 (which stays
+//    in registers), so the exponentials overlap the dS arithmetic.  The dP / dS columns are
+//    double-buffered (tensor-memory columns 128 and 384): dP of the next block is ready
+//    while the dQ GEMM still reads dS of this one; S runs two blocks ahead of dS.
 //  * Two MMA-issuing threads (score GEMMs / dQ GEMMs): one thread can issue an MMA only
 //    every ~54 clocks whatever its size.  All dQ MMAs come from one thread, in block order,
 //    so the order of the floating-point sums is fixed.
@@ -909,9 +911,9 @@ template <int D>
 struct alignas(1024) DqPipeSmem {
     unsigned char xq[BT * D * 2], xdo[BT * D * 2];           // Q, dO of this CTA's query tile
     unsigned char k[3][BT * D * 2], v[2][BT * D * 2];
-    uint64_t x_full, g2_full, ds_ready, g2_free, acc_full;
+    uint64_t x_full, g1_full, s_read, ds_ready, acc_full;
     uint64_t k_full[3], k_empty[3], v_full[2], v_empty[2];
-    uint64_t g1_full[2], s_read[2];                          // per score-column buffer
+    uint64_t g2_full[2], g2_free[2];                         // per dP / dS column buffer
     uint32_t tmem_base;
 };
 constexpr int DQ_PIPE_THREADS = 352;   // 8 compute warps, TMA producer, two MMA issuers
@@ -922,7 +924,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
     constexpr uint32_t PANEL = 128 * 64 * 2;
     constexpr uint32_t TILE_BYTES = BT * D * 2;
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t G1A_COL = 0, G2_COL = 128, ACC_COL = 256, G1B_COL = 384;
+    constexpr uint32_t G1_COL = 0, G2A_COL = 128, ACC_COL = 256, G2B_COL = 384;
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
 
     extern __shared__ unsigned char smem_raw[];
@@ -935,12 +937,16 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
     const int i_end = ((p.causal ? min(p.Tk, r0 + BT) : p.Tk) + BT - 1) / BT;
     const int nit = max(i_end, 0);
     int *status = p.status;
+#ifdef RGD_ATTN_TIMING
+    long long dbg[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long k0 = clock64();
+#endif
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.x_full, 1);
-        mbar_init(&sm.g2_full, 1);
+        mbar_init(&sm.g1_full, 1);
+        mbar_init(&sm.s_read, 256);
         mbar_init(&sm.ds_ready, 256);
-        mbar_init(&sm.g2_free, 1);
         mbar_init(&sm.acc_full, 1);
         for (int s = 0; s < 3; ++s) {
             mbar_init(&sm.k_full[s], 1);
@@ -949,8 +955,8 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
         for (int s = 0; s < 2; ++s) {
             mbar_init(&sm.v_full[s], 1);
             mbar_init(&sm.v_empty[s], 1);
-            mbar_init(&sm.g1_full[s], 1);
-            mbar_init(&sm.s_read[s], 256);
+            mbar_init(&sm.g2_full[s], 1);
+            mbar_init(&sm.g2_free[s], 1);
         }
         fence_mbar_init();
     }
@@ -1008,37 +1014,40 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
                     umma_ss(tbase + col, sdesc_advance(xd, off), sdesc_advance(yd, off), idesc_g, kk > 0);
                 }
             };
-            // S of block j into score buffer j & 1
-            int ks = 0;                                    // K ring slot and phase of block j
+            // S of block j (K ring slot and phase advance with j)
+            int ks = 0;
             uint32_t kph = 0;
             auto issue_g1 = [&](int j) -> bool {
                 if (!mbar_wait(&sm.k_full[ks], kph, status, 52)) return false;
-                if (j >= 2 && !mbar_wait(&sm.s_read[j & 1], (uint32_t)((j >> 1) - 1) & 1u, status, 53)) return false;
+                // the score columns are free once the compute warps have read S of block j - 1
+                if (j >= 1 && !mbar_wait(&sm.s_read, (uint32_t)(j - 1) & 1u, status, 53)) return false;
                 tc_fence_after_sync();
-                issue_g((j & 1) ? G1B_COL : G1A_COL, dxq, make_sdesc(smem_u32(sm.k[ks]), 16, 1024));
-                umma_commit(&sm.g1_full[j & 1]);
+                issue_g(G1_COL, dxq, make_sdesc(smem_u32(sm.k[ks]), 16, 1024));
+                umma_commit(&sm.g1_full);
                 if (++ks == 3) { ks = 0; kph ^= 1u; }
                 return true;
             };
+            // dP of block j into dP buffer j & 1
+            auto issue_g2 = [&](int j) -> bool {
+                const int vs = j & 1;
+                if (!mbar_wait(&sm.v_full[vs], (uint32_t)(j >> 1) & 1u, status, 54)) return false;
+                // the buffer is free once the dQ GEMM of block j - 2 has read dS from it
+                if (j >= 2 && !mbar_wait(&sm.g2_free[vs], (uint32_t)((j >> 1) - 1) & 1u, status, 55)) return false;
+                tc_fence_after_sync();
+                issue_g(vs ? G2B_COL : G2A_COL, dxdo, make_sdesc(smem_u32(sm.v[vs]), 16, 1024));
+                umma_commit(&sm.g2_full[vs]);
+                umma_commit(&sm.v_empty[vs]);
+                return true;
+            };
+            // Both kinds of GEMM run ahead of the compute warps, which in iteration `it` form dS
+            // of block it and P of block it + 1: dP one block ahead, S two blocks ahead.
             bool ok = mbar_wait(&sm.x_full, 0, status, 51);
             if (ok) ok = issue_g1(0);
+            if (ok) ok = issue_g2(0);
+            if (ok && nit > 1) ok = issue_g1(1);
             for (int it = 0; it < nit && ok; ++it) {
-                if (it + 1 < nit) {
-                    ok = issue_g1(it + 1);
-                    if (!ok) break;
-                }
-                const int vs = it & 1;
-                ok = mbar_wait(&sm.v_full[vs], (uint32_t)(it >> 1) & 1u, status, 54);
-                if (!ok) break;
-                // the dP columns are free once the dQ GEMM of the block before has read dS
-                if (it >= 1) {
-                    ok = mbar_wait(&sm.g2_free, (uint32_t)(it - 1) & 1u, status, 55);
-                    if (!ok) break;
-                }
-                tc_fence_after_sync();
-                issue_g(G2_COL, dxdo, make_sdesc(smem_u32(sm.v[vs]), 16, 1024));
-                umma_commit(&sm.g2_full);
-                umma_commit(&sm.v_empty[vs]);
+                if (it + 1 < nit) ok = issue_g2(it + 1);
+                if (ok && it + 2 < nit) ok = issue_g1(it + 2);
             }
         }
     } else if (warp == 10) {
@@ -1058,9 +1067,9 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
                 // each half of the compute threads packed its 64 keys into the first 32 of its own 64 columns
 #pragma unroll
                 for (int kk = 0; kk < BT / 16; ++kk)
-                    umma_ts(tbase + ACC_COL, tbase + G2_COL + (kk >> 2) * 64 + (kk & 3) * 8,
+                    umma_ts(tbase + ACC_COL, tbase + ((it & 1) ? G2B_COL : G2A_COL) + (kk >> 2) * 64 + (kk & 3) * 8,
                             sdesc_advance(dkm, kk * 2048), idesc_acc, it > 0 || kk > 0);
-                umma_commit(&sm.g2_free);
+                umma_commit(&sm.g2_free[it & 1]);
                 umma_commit(&sm.k_empty[ks]);
                 if (++ks == 3) { ks = 0; kph ^= 1u; }
             }
@@ -1076,68 +1085,107 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
         const float lse_row = p.lse2[(int64_t)bh * p.Tq128 + row];
         const float dsc_row = p.delta_s[(int64_t)bh * p.Tq128 + row];
 
-        bool ok = true;
-        for (int it = 0; it < nit; ++it) {
-            const int gb = it & 1;
-            const int blk0 = it * BT;
-            const int c0 = blk0 + half * 64;               // first key this thread handles
+        // P of block j from its scores (32 columns starting at column c of this thread's 64)
+        auto p_from_s = [&](const uint32_t (&r)[32], float *pv, int j, int c) {
+            const int blk0 = j * BT;
             // blocks that need per-element masking: the diagonal blocks under the causal mask
             // and the block touching the end of the keys
             const bool slow = (p.causal && blk0 + BT > r0) || blk0 + BT > p.Tk;
-            float pv[64];
+            if (!slow) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) pv[i] = ex2b(fmaf(__uint_as_float(r[i]), p.scale_log2, -lse_row));
+            } else {
+                const int c0 = blk0 + half * 64 + c;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int kj = c0 + i;
+                    const bool masked = kj >= p.Tk || row >= p.Tq || (p.causal && kj > row);
+                    pv[i] = masked ? 0.f : ex2b(fmaf(__uint_as_float(r[i]), p.scale_log2, -lse_row));
+                }
+            }
+        };
 
-            ok = mbar_wait(&sm.g1_full[gb], (uint32_t)(it >> 1) & 1u, status, 61);
-            if (!ok) break;
-            tc_fence_after_sync();
-            {
+        bool ok = true;
+        float pv[64];
+        // prologue: P of block 0
+        if (nit > 0) {
+            ok = mbar_wait(&sm.g1_full, 0, status, 60);
+            if (ok) {
+                tc_fence_after_sync();
                 uint32_t ra[32], rb[32];
-                const uint32_t gcol = (gb ? G1B_COL : G1A_COL) + half * 64;
-                tmem_ld32(lane_base + gcol, ra);
-                tmem_ld32(lane_base + gcol + 32, rb);
+                tmem_ld32(lane_base + G1_COL + half * 64, ra);
+                tmem_ld32(lane_base + G1_COL + half * 64 + 32, rb);
                 tmem_wait_ld();
                 tc_fence_before_sync();
-                mbar_arrive(&sm.s_read[gb]);               // P stays in registers: the buffer is free
-                if (!slow) {
+                mbar_arrive(&sm.s_read);                   // P stays in registers: the columns are free
+                p_from_s(ra, pv, 0, 0);
+                p_from_s(rb, pv + 32, 0, 32);
+            }
+        }
+        // Block it: dS from P (registers) and dP; in the same pass, P of block it + 1 from its
+        // scores, so the exponentials (MUFU) overlap the dS arithmetic (FMA pipe) and the waits.
+        for (int it = 0; it < nit && ok; ++it) {
+            const bool next = it + 1 < nit;
+            const uint32_t dcol = ((it & 1) ? G2B_COL : G2A_COL) + half * 64;
+            const bool slow_next = (p.causal && (it + 1) * BT + BT > r0) || (it + 1) * BT + BT > p.Tk;
+            DBG_T(c0t);
+            ok = mbar_wait(&sm.g2_full[it & 1], (uint32_t)(it >> 1) & 1u, status, 62);
+            if (!ok) break;
+            if (next) {
+                ok = mbar_wait(&sm.g1_full, (uint32_t)(it + 1) & 1u, status, 61);
+                if (!ok) break;
+            }
+            DBG_T(c1t);
+            DBG_ACC(0, c0t, c1t);
+            tc_fence_after_sync();
+            const uint32_t scol = G1_COL + half * 64;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        pv[i] = ex2b(fmaf(__uint_as_float(ra[i]), p.scale_log2, -lse_row));
-                        pv[32 + i] = ex2b(fmaf(__uint_as_float(rb[i]), p.scale_log2, -lse_row));
+            for (int c = 0; c < 2; ++c) {
+                uint32_t ga[32], ra[32];
+                tmem_ld32(lane_base + dcol + c * 32, ga);
+                if (next) tmem_ld32(lane_base + scol + c * 32, ra);
+                tmem_wait_ld();
+                if (c == 1 && next) {                      // all of S read: the next score GEMM may start
+                    tc_fence_before_sync();
+                    mbar_arrive(&sm.s_read);
+                }
+                uint32_t pk[16];
+                if (next && !slow_next) {
+                    // element by element, so that the exponentials of the next block (MUFU) and
+                    // the dS arithmetic of this one (FMA pipe) issue side by side
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float a0 = pv[32 * c + 2 * i] * fmaf(__uint_as_float(ga[2 * i]), p.scale, -dsc_row);
+                        const float a1 = pv[32 * c + 2 * i + 1] * fmaf(__uint_as_float(ga[2 * i + 1]), p.scale, -dsc_row);
+                        pv[32 * c + 2 * i] = ex2b(fmaf(__uint_as_float(ra[2 * i]), p.scale_log2, -lse_row));
+                        pv[32 * c + 2 * i + 1] = ex2b(fmaf(__uint_as_float(ra[2 * i + 1]), p.scale_log2, -lse_row));
+                        pk[i] = pack16b<BF16>(a0, a1);
                     }
+                    // packed dS of chunk c goes to columns [c*16, c*16+16) of this thread's 64, all read already
+                    tmem_st16(lane_base + dcol + c * 16, pk);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const int kj = c0 + i;
-                        const bool masked = kj >= p.Tk || row >= p.Tq || (p.causal && kj > row);
-                        const float x = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]);
-                        pv[i] = masked ? 0.f : ex2b(fmaf(x, p.scale_log2, -lse_row));
+                    for (int i = 0; i < 16; ++i) {
+                        const float a0 = pv[32 * c + 2 * i] * fmaf(__uint_as_float(ga[2 * i]), p.scale, -dsc_row);
+                        const float a1 = pv[32 * c + 2 * i + 1] * fmaf(__uint_as_float(ga[2 * i + 1]), p.scale, -dsc_row);
+                        pk[i] = pack16b<BF16>(a0, a1);
                     }
+                    tmem_st16(lane_base + dcol + c * 16, pk);
+                    if (next) p_from_s(ra, pv + 32 * c, it + 1, 32 * c);
                 }
             }
-
-            ok = mbar_wait(&sm.g2_full, (uint32_t)it & 1u, status, 62);
-            if (!ok) break;
-            tc_fence_after_sync();
-            {
-                uint32_t ga[32], gb2[32];
-                tmem_ld32(lane_base + G2_COL + half * 64, ga);
-                tmem_ld32(lane_base + G2_COL + half * 64 + 32, gb2);
-                tmem_wait_ld();
-                uint32_t pk[32];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float a0 = pv[2 * i] * fmaf(__uint_as_float(ga[2 * i]), p.scale, -dsc_row);
-                    const float a1 = pv[2 * i + 1] * fmaf(__uint_as_float(ga[2 * i + 1]), p.scale, -dsc_row);
-                    pk[i] = pack16b<BF16>(a0, a1);
-                    const float b0 = pv[32 + 2 * i] * fmaf(__uint_as_float(gb2[2 * i]), p.scale, -dsc_row);
-                    const float b1 = pv[32 + 2 * i + 1] * fmaf(__uint_as_float(gb2[2 * i + 1]), p.scale, -dsc_row);
-                    pk[16 + i] = pack16b<BF16>(b0, b1);
-                }
-                tmem_st32(lane_base + G2_COL + half * 64, pk);
-                tmem_wait_st();
-            }
+            tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_ready);
+            DBG_T(c4t);
+            DBG_ACC(3, c1t, c4t);
         }
+#ifdef RGD_ATTN_TIMING
+        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+            for (int i = 0; i < 4; ++i) g_dbg[52 + i] = dbg[i];
+            g_dbg[56] = clock64() - k0;
+        }
+#endif
 
         // epilogue: dQ -> global
         if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 63);
