@@ -709,7 +709,8 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 DBG_ACC(0, b0, b1);
                 tc_fence_after_sync();
                 issue_acc(u, ACC1_COL, G1_COL, dy2m[s]);            // dV += P^T dO
-                umma_commit(&sm.g1_free[sb]);
+                tc_fence_before_sync();
+                mbar_arrive(&sm.g1_free[sb]);   // issued, not finished: the tensor pipe runs MMAs in issue order
                 DBG_T(b2);
                 DBG_ACC(1, b1, b2);
                 ok = mbar_wait(&sm.ds_ready[sb], par, status, 84);
@@ -718,7 +719,8 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 DBG_ACC(2, b2, b3);
                 tc_fence_after_sync();
                 issue_acc(u, ACC2_COL, G2_COL, dy1m[s]);            // dK += dS^T Q
-                umma_commit(&sm.g2_free[sb]);
+                tc_fence_before_sync();
+                mbar_arrive(&sm.g2_free[sb]);
                 if (sb == 1) umma_commit(&sm.y_empty[s]);            // both sub-blocks of this block consumed
                 DBG_T(b4);
                 DBG_ACC(3, b3, b4);
@@ -1069,7 +1071,8 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
                 for (int kk = 0; kk < BT / 16; ++kk)
                     umma_ts(tbase + ACC_COL, tbase + ((it & 1) ? G2B_COL : G2A_COL) + (kk >> 2) * 64 + (kk & 3) * 8,
                             sdesc_advance(dkm, kk * 2048), idesc_acc, it > 0 || kk > 0);
-                umma_commit(&sm.g2_free[it & 1]);
+                tc_fence_before_sync();
+                mbar_arrive(&sm.g2_free[it & 1]);   // issued, not finished: the tensor pipe runs MMAs in issue order
                 umma_commit(&sm.k_empty[ks]);
                 if (++ks == 3) { ks = 0; kph ^= 1u; }
             }
