@@ -232,9 +232,17 @@ def op_table(dev, steps, hbm_peak):
             t_f = timed(lambda: fwd(*ins))
         wrt = ins + grads_of
         t_b = timed(lambda: torch.autograd.grad(outs, wrt, upstream, retain_graph=True))
+        # Yardstick: a plain device copy moving the same number of bytes as the forward (half
+        # read, half written), timed the same way.  The measured peak comes from a 2 GiB copy;
+        # at these sizes (tens of microseconds) ramp-up and tail cost even a copy a good part of it.
+        src = torch.empty(fwd_b // 2, dtype=torch.uint8, device=dev)
+        dst = torch.empty_like(src)
+        t_c = timed(lambda: dst.copy_(src))
+        del src, dst
         return {"op": name, "fwd_bytes": fwd_b, "bwd_bytes": bwd_b, "fwd_ms": t_f, "bwd_ms": t_b,
                 "fwd_gbs": fwd_b / t_f / 1e6, "bwd_gbs": bwd_b / t_b / 1e6,
-                "fwd_frac": fwd_b / t_f / 1e6 / hbm_peak, "bwd_frac": bwd_b / t_b / 1e6 / hbm_peak}
+                "fwd_frac": fwd_b / t_f / 1e6 / hbm_peak, "bwd_frac": bwd_b / t_b / 1e6 / hbm_peak,
+                "copy_same_bytes_gbs": fwd_b / t_c / 1e6, "copy_same_bytes_frac": fwd_b / t_c / 1e6 / hbm_peak}
 
     rows = []
     # config 1: FusedRMSNorm fp32 [4,256,1024]

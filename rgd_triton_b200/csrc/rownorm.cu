@@ -282,6 +282,212 @@ __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant_
     }
 }
 
+// ---------------------------------------------------------------------------
+// One warp per row, the whole row in registers (VPT 16-byte vectors per lane, lane l
+// owning vectors l, l + 32, ...).  For rows of more than 128 vectors the kernel above
+// has to spread a row over several warps and pays a block-wide barrier per row; here
+// the row sums are five shuffles, nothing goes through shared memory, and all of a
+// lane's loads are issued before the first use.  Same CTA -> (tensor, batch, chunk)
+// mapping, same arithmetic and evaluation order per element as row_kernel.
+// ---------------------------------------------------------------------------
+// Makes the compiler forget what it derived from a 16-byte register vector, so that a later
+// pass converts the raw elements again instead of keeping fp32 copies of the whole row alive
+// (which would double the registers per thread and halve the rows in flight per SM).
+template <typename V>
+__device__ __forceinline__ void forget_derived(V &v) {
+    static_assert(sizeof(V) == 16, "16-byte vectors only");
+    uint4 &u = reinterpret_cast<uint4 &>(v);
+    asm volatile("" : "+r"(u.x), "+r"(u.y), "+r"(u.z), "+r"(u.w));
+}
+
+template <typename T, int VE>
+__device__ __forceinline__ void load_w_vec(const void *w, int64_t idx, int w_dtype, float (&out)[VE]) {
+    if (w_dtype == DTypeCode<T>::value) {
+        const Vec<T, VE> v = load_vec<T, VE>(reinterpret_cast<const T *>(w) + idx);
+#pragma unroll
+        for (int e = 0; e < VE; ++e) out[e] = to_f32<T>(v.v[e]);
+    } else if (w_dtype == RGD_F32) {
+        const float4 *src = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(w) + idx);
+#pragma unroll
+        for (int q = 0; q < VE / 4; ++q) {
+            const float4 f = __ldg(src + q);
+            out[4 * q] = f.x; out[4 * q + 1] = f.y; out[4 * q + 2] = f.z; out[4 * q + 3] = f.w;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) out[e] = load_as_f32(w, idx + e, w_dtype);
+    }
+}
+
+template <typename T, int VPT, int OP>
+__global__ void __launch_bounds__(ROW_THREADS, (OP == L2_FWD || OP == RMS_FWD) ? 3 : (OP == L2_BWD ? 2 : 1)) warp_row_kernel(const __grid_constant__ RowParams p) {
+    constexpr bool BWD = (OP == L2_BWD || OP == RMS_BWD);
+    constexpr bool RMS = (OP == RMS_FWD || OP == RMS_BWD);
+    constexpr int VE = VecElems<T>::value;
+    constexpr int WPC = ROW_THREADS / 32;                 // rows per CTA and iteration
+    using V = Vec<T, VE>;
+    __shared__ float dwred[OP == RMS_BWD ? ROW_THREADS * VE : 1];
+
+    const int sid = (int)blockIdx.x >= p.split ? 1 : 0;
+    const RowStream &s = p.s[sid];
+    const int local = (int)blockIdx.x - (sid ? p.split : 0);
+    const int b = local / s.P;
+    const int chunk = local - b * s.P;
+    const int warp = (int)threadIdx.x >> 5, lane = (int)threadIdx.x & 31;
+    const int C = s.C, nvec = C / VE;
+    const float invC = 1.0f / (float)C;
+    const int64_t wbase = (int64_t)b * s.swb;
+
+    float dwacc[OP == RMS_BWD ? VPT * VE : 1];
+    if (OP == RMS_BWD) {
+#pragma unroll
+        for (int i = 0; i < VPT * VE; ++i) dwacc[i] = 0.f;
+    }
+
+    const T *xb = reinterpret_cast<const T *>(s.x) + (int64_t)b * s.sxb;
+    const T *db = BWD ? reinterpret_cast<const T *>(s.dy) + (int64_t)b * s.sdb : nullptr;
+    T *ob = reinterpret_cast<T *>(s.out) + (int64_t)b * s.sob;
+
+    const int step = s.P * WPC;
+    for (int n = chunk * WPC + warp; n < s.N; n += step) {
+        const T *xr = xb + (int64_t)n * s.sxn;
+        const T *dr = BWD ? db + (int64_t)n * s.sdn : nullptr;
+        T *orow = ob + (int64_t)n * s.son;
+
+        V xq[VPT];
+        V dq[BWD ? VPT : 1];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = lane + 32 * j;
+            if (v < nvec) {
+                xq[j] = load_vec_stream<T, VE>(xr + v * VE);
+                if (BWD) dq[j] = load_vec_stream<T, VE>(dr + v * VE);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    xq[j].v[e] = from_f32<T>(0.f);
+                    if (BWD) dq[j].v[e] = from_f32<T>(0.f);
+                }
+            }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+#pragma unroll
+            for (int e = 0; e < VE; ++e) {
+                const float xf = to_f32<T>(xq[j].v[e]);
+                ss = fmaf(xf, xf, ss);
+            }
+        ss = warp_group_sum(ss, 32);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            forget_derived(xq[j]);
+            if (BWD) forget_derived(dq[j]);
+        }
+
+        // Row scale: rmsnorm_cached.py:75-76, l2normalize_cached.py:72-77.
+        float r;
+        if (RMS) {
+            r = rsqrtf(ss * invC + p.eps);
+        } else {
+            const float len = sqrtf(ss);
+            r = (len < p.eps) ? (1.0f / p.eps) : (1.0f / len);
+        }
+
+        if (!BWD) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int v = lane + 32 * j;
+                if (v < nvec) {
+                    float wv[VE];
+                    if (RMS) load_w_vec<T, VE>(s.w, wbase + v * VE, p.w_dtype, wv);
+                    V yo;
+#pragma unroll
+                    for (int e = 0; e < VE; ++e) {
+                        float y = to_f32<T>(xq[j].v[e]) * r;
+                        if (RMS) y = y * wv[e];
+                        yo.v[e] = from_f32<T>(y);
+                    }
+                    store_vec_stream<T, VE>(orow + v * VE, yo);
+                }
+            }
+        } else {
+            // xhat, then g = sum(xhat * dy * w) [/ C for RMS]: rmsnorm_cached.py:213-231,
+            // l2normalize_cached.py:214-226.
+            float g = 0.f;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int v = lane + 32 * j;
+                float wv[VE];
+                if (RMS && v < nvec) load_w_vec<T, VE>(s.w, wbase + v * VE, p.w_dtype, wv);
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    const float xh = to_f32<T>(xq[j].v[e]) * r;
+                    const float df = to_f32<T>(dq[j].v[e]);
+                    if (RMS) {
+                        if (v < nvec) g += xh * df * wv[e];
+                    } else {
+                        g += xh * df;
+                    }
+                }
+            }
+            g = warp_group_sum(g, 32);
+            if (RMS) g *= invC;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                forget_derived(xq[j]);
+                forget_derived(dq[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int v = lane + 32 * j;
+                if (v < nvec) {
+                    float wv[VE];
+                    if (RMS) load_w_vec<T, VE>(s.w, wbase + v * VE, p.w_dtype, wv);
+                    V yo;
+#pragma unroll
+                    for (int e = 0; e < VE; ++e) {
+                        const float xh = to_f32<T>(xq[j].v[e]) * r;
+                        const float df = to_f32<T>(dq[j].v[e]);
+                        float dxv;
+                        if (RMS) {
+                            dxv = (df * wv[e] - xh * g) * r;
+                            if (OP == RMS_BWD) dwacc[j * VE + e] += xh * df;
+                        } else {
+                            dxv = (df - xh * g) * r;
+                        }
+                        yo.v[e] = from_f32<T>(dxv);
+                    }
+                    store_vec_stream<T, VE>(orow + v * VE, yo);
+                }
+            }
+        }
+    }
+
+    if (OP == RMS_BWD) {
+        // Fold the CTA's warps together, one vector slot at a time, and write this CTA's
+        // partial row.
+        float *prow = s.dw_part + ((int64_t)b * s.P + chunk) * C;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            __syncthreads();
+#pragma unroll
+            for (int e = 0; e < VE; ++e) dwred[threadIdx.x * VE + e] = dwacc[j * VE + e];
+            __syncthreads();
+            const int v = lane + 32 * j;
+            if (warp == 0 && v < nvec) {
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int w2 = 0; w2 < WPC; ++w2) a += dwred[(w2 * 32 + lane) * VE + e];
+                    prow[v * VE + e] = a;
+                }
+            }
+        }
+    }
+}
+
 // Second stage of dweight: dw[b or -, c] = sum over partial rows, fixed order.
 // blockDim = (32 columns, 32 row lanes); grid = (ceil(C/32), B or 1, streams).
 struct DwReduceStream {
@@ -450,6 +656,24 @@ bool view_vec_ok(const rgd_rows &v, int esize) {
     return is_aligned(v.ptr, 16) && v.stride_b % ve == 0 && v.stride_n % ve == 0;
 }
 
+template <typename T, int OP>
+int launch_warp_rows(const RowParams &p, int vpt, int grid, cudaStream_t st) {
+    if (vpt == 8) warp_row_kernel<T, 8, OP><<<grid, ROW_THREADS, 0, st>>>(p);
+    else warp_row_kernel<T, 12, OP><<<grid, ROW_THREADS, 0, st>>>(p);
+    count_launch();
+    return check_launch();
+}
+
+template <int OP>
+int launch_warp_rows_dtype(int dtype, const RowParams &p, int vpt, int grid, cudaStream_t st) {
+    switch (dtype) {
+        case RGD_F32: return launch_warp_rows<float, OP>(p, vpt, grid, st);
+        case RGD_F16: return launch_warp_rows<__half, OP>(p, vpt, grid, st);
+        case RGD_BF16: return launch_warp_rows<__nv_bfloat16, OP>(p, vpt, grid, st);
+    }
+    return RGD_E_DTYPE;
+}
+
 // CTAs per batch for each stream.  `budget` is the total CTA count aimed at.
 void split_ctas(int nstreams, const int64_t *N, int64_t B, int rpc, int budget, int *P) {
     int64_t groups[2] = {0, 0}, total = 0;
@@ -467,6 +691,14 @@ void split_ctas(int nstreams, const int64_t *N, int64_t B, int rpc, int budget, 
             if (ps > groups[s]) ps = groups[s];
         }
         if (ps < 1) ps = 1;
+        // Even out the walk: with k = ceil(groups / ps) iterations per CTA, ceil(groups / k)
+        // CTAs do the same work in the same k iterations and none of them idles through a
+        // mostly empty last iteration (2048 row groups over 444 CTAs: 5 iterations at 92%;
+        // over 410 CTAs: 5 iterations at 99.9%).
+        if (groups[s] > 0) {
+            const int64_t k = ceil_div64(groups[s], ps);
+            ps = ceil_div64(groups[s], k);
+        }
         P[s] = (int)ps;
     }
 }
@@ -523,7 +755,19 @@ int run_rows(const RowCall &c, float *dw_part0, float *dw_part1, int budget, cud
     p.w_dtype = c.w_dtype;
     p.eps = c.eps;
     int P[2] = {0, 0};
-    if (pl.ve > 1 && pl.vpt <= 4) {
+    // Rows of 129..384 vectors: one warp per row (warp_row_kernel) instead of several warps
+    // per row with a block-wide barrier per row.
+    const int nvec = pl.ve > 1 ? (cmax + pl.ve - 1) / pl.ve : 0;
+    // (Measured on B200 at 3072 channels: L2 forward 22.5 -> 20.5 us.  With a weight vector
+    // per row, or with x and dy of a backward row in registers, the registers per thread cut
+    // the rows in flight per SM and the multi-warp kernel stays ahead, so only L2 forward
+    // takes this path.)
+    const bool warp_rows = OP == L2_FWD && pl.ve > 1 && nvec > 128 && nvec <= 384;
+    const int warp_vpt = nvec <= 256 ? 8 : 12;
+    if (warp_rows) {
+        pl.tpr = 32;
+        budget = INT32_MAX;                                  // one row per warp, the hardware balances the CTAs
+    } else if (pl.ve > 1 && pl.vpt <= 4) {
         // Pipelined kernel: launch exactly one resident wave, so every CTA streams
         // several rows and the copy pipeline stays full.
         const int per_sm = rows_occupancy_dtype<OP>(c.x_dtype, pl);
@@ -565,6 +809,9 @@ int run_rows(const RowCall &c, float *dw_part0, float *dw_part1, int budget, cud
     if (P_out) { P_out[0] = P[0]; P_out[1] = P[1]; }
     if (grid == 0) return RGD_OK;
     if (grid > INT32_MAX) return RGD_E_SIZE;
+    if constexpr (OP == L2_FWD) {
+        if (warp_rows) return launch_warp_rows_dtype<OP>(c.x_dtype, p, warp_vpt, (int)grid, st);
+    }
     return launch_rows_dtype<OP>(c.x_dtype, p, pl, (int)grid, st);
 }
 
