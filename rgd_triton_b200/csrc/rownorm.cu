@@ -282,24 +282,7 @@ __global__ void __launch_bounds__(ROW_THREADS) row_kernel(const __grid_constant_
     }
 }
 
-// ---------------------------------------------------------------------------
-// One warp per row, the whole row in registers (VPT 16-byte vectors per lane, lane l
-// owning vectors l, l + 32, ...).  For rows of more than 128 vectors the kernel above
-// has to spread a row over several warps and pays a block-wide barrier per row; here
-// the row sums are five shuffles, nothing goes through shared memory, and all of a
-// lane's loads are issued before the first use.  Same CTA -> (tensor, batch, chunk)
-// mapping, same arithmetic and evaluation order per element as row_kernel.
-// ---------------------------------------------------------------------------
-// Makes the compiler forget what it derived from a 16-byte register vector, so that a later
-// pass converts the raw elements again instead of keeping fp32 copies of the whole row alive
-// (which would double the registers per thread and halve the rows in flight per SM).
-template <typename V>
-__device__ __forceinline__ void forget_derived(V &v) {
-    static_assert(sizeof(V) == 16, "16-byte vectors only");
-    uint4 &u = reinterpret_cast<uint4 &>(v);
-    asm volatile("" : "+r"(u.x), "+r"(u.y), "+r"(u.z), "+r"(u.w));
-}
-
+// A 16-byte vector of the weight as fp32, whatever the weight's dtype.
 template <typename T, int VE>
 __device__ __forceinline__ void load_w_vec(const void *w, int64_t idx, int w_dtype, float (&out)[VE]) {
     if (w_dtype == DTypeCode<T>::value) {
@@ -319,14 +302,38 @@ __device__ __forceinline__ void load_w_vec(const void *w, int64_t idx, int w_dty
     }
 }
 
-template <typename T, int VPT, int OP>
-__global__ void __launch_bounds__(ROW_THREADS, (OP == L2_FWD || OP == RMS_FWD) ? 3 : (OP == L2_BWD ? 2 : 1)) warp_row_kernel(const __grid_constant__ RowParams p) {
+// ---------------------------------------------------------------------------
+// Lean kernel for rows of exactly 128 * VPT vectors (four warps per row, two rows per CTA
+// and iteration).  The pipelined kernel above spends about three quarters of its issue
+// slots on bookkeeping (column and row predicates, 64-bit address arithmetic per vector,
+// copy-pipeline slots), and at these row lengths issue slots are what bounds it.  Here the
+// shape is exact, so there are no predicates; addresses advance by one add per row; the next
+// row's vectors are loaded into registers before the current row is processed; and the two
+// row groups of a CTA synchronise separately (named barriers), so neither waits for the other.
+// Same CTA -> (tensor, batch, chunk) mapping, arithmetic and evaluation order as row_kernel.
+// ---------------------------------------------------------------------------
+constexpr int LEAN_TPR = 128;   // narrow form: 128 threads per row, two rows per CTA
+
+template <int ID, int THREADS>
+__device__ __forceinline__ void named_bar_sync() {
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(THREADS) : "memory");
+}
+
+// TPR threads per row, RPC rows per CTA and iteration (CTA = TPR * RPC threads), VPT vectors per
+// thread.  The RMS backward carries x, dy, the weight and the dweight sums per thread; with
+// three vectors per thread that is 171 registers and one CTA per SM, so it runs in the wide
+// form instead: one vector per thread, the whole CTA on one row.
+template <typename T, int VPT, int OP, int TPR, int RPC>
+__global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_constant__ RowParams p) {
+    constexpr int THREADS = TPR * RPC;
     constexpr bool BWD = (OP == L2_BWD || OP == RMS_BWD);
     constexpr bool RMS = (OP == RMS_FWD || OP == RMS_BWD);
     constexpr int VE = VecElems<T>::value;
-    constexpr int WPC = ROW_THREADS / 32;                 // rows per CTA and iteration
+    constexpr int WPR = TPR / 32;                     // warps per row
+    constexpr int NE = VPT * VE;
     using V = Vec<T, VE>;
-    __shared__ float dwred[OP == RMS_BWD ? ROW_THREADS * VE : 1];
+    __shared__ float red[2][THREADS / 32];
+    __shared__ float dwred[(OP == RMS_BWD && RPC > 1) ? THREADS * VE : 1];
 
     const int sid = (int)blockIdx.x >= p.split ? 1 : 0;
     const RowStream &s = p.s[sid];
@@ -334,56 +341,94 @@ __global__ void __launch_bounds__(ROW_THREADS, (OP == L2_FWD || OP == RMS_FWD) ?
     const int b = local / s.P;
     const int chunk = local - b * s.P;
     const int warp = (int)threadIdx.x >> 5, lane = (int)threadIdx.x & 31;
-    const int C = s.C, nvec = C / VE;
-    const float invC = 1.0f / (float)C;
-    const int64_t wbase = (int64_t)b * s.swb;
+    const int rg = (int)threadIdx.x / TPR;
+    const int t = (int)threadIdx.x - rg * TPR;
+    const float invC = 1.0f / (float)s.C;
+    int phase = 0;
 
-    float dwacc[OP == RMS_BWD ? VPT * VE : 1];
-    if (OP == RMS_BWD) {
+    auto group_sum = [&](float v) -> float {
+        v = warp_group_sum(v, 32);
+        if (lane == 0) red[phase][warp] = v;
+        if (rg == 0) named_bar_sync<1, TPR>();             // literal ids: the compiler reserves only these
+        else named_bar_sync<2, TPR>();
+        float a = 0.f;
 #pragma unroll
-        for (int i = 0; i < VPT * VE; ++i) dwacc[i] = 0.f;
-    }
+        for (int i = 0; i < WPR; ++i) a += red[phase][rg * WPR + i];
+        phase ^= 1;
+        return a;
+    };
 
-    const T *xb = reinterpret_cast<const T *>(s.x) + (int64_t)b * s.sxb;
-    const T *db = BWD ? reinterpret_cast<const T *>(s.dy) + (int64_t)b * s.sdb : nullptr;
-    T *ob = reinterpret_cast<T *>(s.out) + (int64_t)b * s.sob;
-
-    const int step = s.P * WPC;
-    for (int n = chunk * WPC + warp; n < s.N; n += step) {
-        const T *xr = xb + (int64_t)n * s.sxn;
-        const T *dr = BWD ? db + (int64_t)n * s.sdn : nullptr;
-        T *orow = ob + (int64_t)n * s.son;
-
-        V xq[VPT];
-        V dq[BWD ? VPT : 1];
+    float wv[RMS ? NE : 1];
+    float dwacc[OP == RMS_BWD ? NE : 1];
+    if (RMS) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
-            const int v = lane + 32 * j;
-            if (v < nvec) {
-                xq[j] = load_vec_stream<T, VE>(xr + v * VE);
-                if (BWD) dq[j] = load_vec_stream<T, VE>(dr + v * VE);
-            } else {
+            float w8[VE];
+            load_w_vec<T, VE>(s.w, (int64_t)b * s.swb + (t + j * TPR) * VE, p.w_dtype, w8);
 #pragma unroll
-                for (int e = 0; e < VE; ++e) {
-                    xq[j].v[e] = from_f32<T>(0.f);
-                    if (BWD) dq[j].v[e] = from_f32<T>(0.f);
+            for (int e = 0; e < VE; ++e) wv[j * VE + e] = w8[e];
+        }
+    }
+    if (OP == RMS_BWD) {
+#pragma unroll
+        for (int i = 0; i < NE; ++i) dwacc[i] = 0.f;
+    }
+
+    const int step = s.P * RPC;
+    int n = chunk * RPC + rg;
+    const T *xr = reinterpret_cast<const T *>(s.x) + (int64_t)b * s.sxb + (int64_t)n * s.sxn + t * VE;
+    const T *dr = BWD ? reinterpret_cast<const T *>(s.dy) + (int64_t)b * s.sdb + (int64_t)n * s.sdn + t * VE : nullptr;
+    T *orow = reinterpret_cast<T *>(s.out) + (int64_t)b * s.sob + (int64_t)n * s.son + t * VE;
+    const int64_t xstep = (int64_t)step * s.sxn, dstep = BWD ? (int64_t)step * s.sdn : 0, ostep = (int64_t)step * s.son;
+
+    // Rows in flight ahead of the one being processed: one (FAR: two).
+    constexpr bool FAR = false;   // measured on B200: two rows ahead (212 registers) ran the RMS backward at 60 us, one row ahead (171) at 42 us
+    V xq[VPT], xn[VPT], xm[FAR ? VPT : 1];
+    V dq[BWD ? VPT : 1], dn[BWD ? VPT : 1], dm[FAR ? VPT : 1];
+    if (n < s.N) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            xq[j] = load_vec_stream<T, VE>(xr + j * TPR * VE);
+            if (BWD) dq[j] = load_vec_stream<T, VE>(dr + j * TPR * VE);
+        }
+    }
+    if (FAR && n + step < s.N) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            xn[j] = load_vec_stream<T, VE>(xr + xstep + j * TPR * VE);
+            dn[j] = load_vec_stream<T, VE>(dr + dstep + j * TPR * VE);
+        }
+    }
+    for (; n < s.N; n += step) {
+        // the rows ahead of this group: in flight while this one is processed
+        if (!FAR) {
+            if (n + step < s.N) {
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    xn[j] = load_vec_stream<T, VE>(xr + xstep + j * TPR * VE);
+                    if (BWD) dn[j] = load_vec_stream<T, VE>(dr + dstep + j * TPR * VE);
                 }
             }
+        } else if (n + 2 * step < s.N) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                xm[j] = load_vec_stream<T, VE>(xr + 2 * xstep + j * TPR * VE);
+                dm[j] = load_vec_stream<T, VE>(dr + 2 * dstep + j * TPR * VE);
+            }
         }
-        float ss = 0.f;
+        float xf[NE];
+        float df[BWD ? NE : 1];
 #pragma unroll
         for (int j = 0; j < VPT; ++j)
 #pragma unroll
             for (int e = 0; e < VE; ++e) {
-                const float xf = to_f32<T>(xq[j].v[e]);
-                ss = fmaf(xf, xf, ss);
+                xf[j * VE + e] = to_f32<T>(xq[j].v[e]);
+                if (BWD) df[j * VE + e] = to_f32<T>(dq[j].v[e]);
             }
-        ss = warp_group_sum(ss, 32);
+        float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            forget_derived(xq[j]);
-            if (BWD) forget_derived(dq[j]);
-        }
+        for (int i = 0; i < NE; ++i) ss = fmaf(xf[i], xf[i], ss);
+        ss = group_sum(ss);
 
         // Row scale: rmsnorm_cached.py:75-76, l2normalize_cached.py:72-77.
         float r;
@@ -397,95 +442,159 @@ __global__ void __launch_bounds__(ROW_THREADS, (OP == L2_FWD || OP == RMS_FWD) ?
         if (!BWD) {
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
-                const int v = lane + 32 * j;
-                if (v < nvec) {
-                    float wv[VE];
-                    if (RMS) load_w_vec<T, VE>(s.w, wbase + v * VE, p.w_dtype, wv);
-                    V yo;
+                V yo;
 #pragma unroll
-                    for (int e = 0; e < VE; ++e) {
-                        float y = to_f32<T>(xq[j].v[e]) * r;
-                        if (RMS) y = y * wv[e];
-                        yo.v[e] = from_f32<T>(y);
-                    }
-                    store_vec_stream<T, VE>(orow + v * VE, yo);
+                for (int e = 0; e < VE; ++e) {
+                    float y = xf[j * VE + e] * r;
+                    if (RMS) y = y * wv[j * VE + e];
+                    yo.v[e] = from_f32<T>(y);
                 }
+                store_vec_stream<T, VE>(orow + j * TPR * VE, yo);
             }
         } else {
             // xhat, then g = sum(xhat * dy * w) [/ C for RMS]: rmsnorm_cached.py:213-231,
             // l2normalize_cached.py:214-226.
             float g = 0.f;
 #pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                const int v = lane + 32 * j;
-                float wv[VE];
-                if (RMS && v < nvec) load_w_vec<T, VE>(s.w, wbase + v * VE, p.w_dtype, wv);
-#pragma unroll
-                for (int e = 0; e < VE; ++e) {
-                    const float xh = to_f32<T>(xq[j].v[e]) * r;
-                    const float df = to_f32<T>(dq[j].v[e]);
-                    if (RMS) {
-                        if (v < nvec) g += xh * df * wv[e];
-                    } else {
-                        g += xh * df;
-                    }
-                }
+            for (int i = 0; i < NE; ++i) {
+                xf[i] *= r;
+                g += RMS ? xf[i] * df[i] * wv[i] : xf[i] * df[i];
             }
-            g = warp_group_sum(g, 32);
+            g = group_sum(g);
             if (RMS) g *= invC;
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
-                forget_derived(xq[j]);
-                forget_derived(dq[j]);
-            }
+                V yo;
 #pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                const int v = lane + 32 * j;
-                if (v < nvec) {
-                    float wv[VE];
-                    if (RMS) load_w_vec<T, VE>(s.w, wbase + v * VE, p.w_dtype, wv);
-                    V yo;
-#pragma unroll
-                    for (int e = 0; e < VE; ++e) {
-                        const float xh = to_f32<T>(xq[j].v[e]) * r;
-                        const float df = to_f32<T>(dq[j].v[e]);
-                        float dxv;
-                        if (RMS) {
-                            dxv = (df * wv[e] - xh * g) * r;
-                            if (OP == RMS_BWD) dwacc[j * VE + e] += xh * df;
-                        } else {
-                            dxv = (df - xh * g) * r;
-                        }
-                        yo.v[e] = from_f32<T>(dxv);
+                for (int e = 0; e < VE; ++e) {
+                    const int i = j * VE + e;
+                    float dxv;
+                    if (RMS) {
+                        dxv = (df[i] * wv[i] - xf[i] * g) * r;
+                        if (OP == RMS_BWD) dwacc[i] += xf[i] * df[i];
+                    } else {
+                        dxv = (df[i] - xf[i] * g) * r;
                     }
-                    store_vec_stream<T, VE>(orow + v * VE, yo);
+                    yo.v[e] = from_f32<T>(dxv);
                 }
+                store_vec_stream<T, VE>(orow + j * TPR * VE, yo);
+            }
+        }
+        xr += xstep;
+        if (BWD) dr += dstep;
+        orow += ostep;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            xq[j] = xn[j];
+            if (BWD) dq[j] = dn[j];
+            if (FAR) {
+                xn[j] = xm[j];
+                dn[j] = dm[j];
             }
         }
     }
 
     if (OP == RMS_BWD) {
-        // Fold the CTA's warps together, one vector slot at a time, and write this CTA's
+        // Fold the CTA's row groups together, one column slot at a time, and write this CTA's
         // partial row.
-        float *prow = s.dw_part + ((int64_t)b * s.P + chunk) * C;
+        float *prow = s.dw_part + ((int64_t)b * s.P + chunk) * s.C;
+        if (RPC == 1) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j)
+#pragma unroll
+                for (int e = 0; e < VE; ++e) prow[(t + j * TPR) * VE + e] = dwacc[j * VE + e];
+            return;
+        }
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             __syncthreads();
 #pragma unroll
             for (int e = 0; e < VE; ++e) dwred[threadIdx.x * VE + e] = dwacc[j * VE + e];
             __syncthreads();
-            const int v = lane + 32 * j;
-            if (warp == 0 && v < nvec) {
+            if (rg == 0) {
 #pragma unroll
                 for (int e = 0; e < VE; ++e) {
                     float a = 0.f;
 #pragma unroll
-                    for (int w2 = 0; w2 < WPC; ++w2) a += dwred[(w2 * 32 + lane) * VE + e];
-                    prow[v * VE + e] = a;
+                    for (int g2 = 0; g2 < RPC; ++g2) a += dwred[(g2 * TPR + t) * VE + e];
+                    prow[(t + j * TPR) * VE + e] = a;
                 }
             }
         }
     }
+}
+
+// Geometry of the lean kernel for rows of `nvec` vectors: wide (one vector per thread, TPR =
+// nvec in {256, 384, 512}) for the RMS backward, else narrow (128 threads per row, 2..4 vectors).
+struct LeanGeom {
+    bool ok;
+    int tpr, rpc, vpt;
+};
+template <int OP>
+LeanGeom lean_geometry(int nvec) {
+    if (false && OP == RMS_BWD && (nvec == 256 || nvec == 384 || nvec == 512)) return {true, nvec, 1, 1};
+    if (nvec % LEAN_TPR == 0 && nvec / LEAN_TPR >= 2 && nvec / LEAN_TPR <= 4) return {true, LEAN_TPR, 2, nvec / LEAN_TPR};
+    return {false, 0, 0, 0};
+}
+
+// F(kernel, threads) for the instantiation that matches the geometry.
+template <typename T, int OP, typename F>
+int with_lean_kernel(const LeanGeom &g, F f) {
+    if (g.rpc == 1) {
+        if constexpr (OP == RMS_BWD) {
+            if (g.tpr == 256) return f(lean_row_kernel<T, 1, OP, 256, 1>, 256);
+            if (g.tpr == 384) return f(lean_row_kernel<T, 1, OP, 384, 1>, 384);
+            if (g.tpr == 512) return f(lean_row_kernel<T, 1, OP, 512, 1>, 512);
+        }
+        return RGD_E_SIZE;
+    }
+    switch (g.vpt) {
+        case 2: return f(lean_row_kernel<T, 2, OP, LEAN_TPR, 2>, 2 * LEAN_TPR);
+        case 3: return f(lean_row_kernel<T, 3, OP, LEAN_TPR, 2>, 2 * LEAN_TPR);
+        case 4: return f(lean_row_kernel<T, 4, OP, LEAN_TPR, 2>, 2 * LEAN_TPR);
+    }
+    return RGD_E_SIZE;
+}
+
+template <typename T, int OP>
+int launch_lean_rows(const RowParams &p, const LeanGeom &g, int grid, cudaStream_t st) {
+    return with_lean_kernel<T, OP>(g, [&](auto kernel, int threads) {
+        kernel<<<grid, threads, 0, st>>>(p);
+        count_launch();
+        return check_launch();
+    });
+}
+
+template <int OP>
+int launch_lean_rows_dtype(int dtype, const RowParams &p, const LeanGeom &g, int grid, cudaStream_t st) {
+    switch (dtype) {
+        case RGD_F32: return launch_lean_rows<float, OP>(p, g, grid, st);
+        case RGD_F16: return launch_lean_rows<__half, OP>(p, g, grid, st);
+        case RGD_BF16: return launch_lean_rows<__nv_bfloat16, OP>(p, g, grid, st);
+    }
+    return RGD_E_DTYPE;
+}
+
+// CTAs of the lean kernel resident on one SM.
+template <typename T, int OP>
+int lean_rows_occupancy_t(const LeanGeom &g) {
+    int n = 0;
+    const int rc = with_lean_kernel<T, OP>(g, [&](auto kernel, int threads) {
+        return cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) == cudaSuccess ? 0 : 1;
+    });
+    if (rc != 0 || n < 1) {
+        (void)cudaGetLastError();
+        n = 1;
+    }
+    return n;
+}
+template <int OP>
+int lean_rows_occupancy(int dtype, const LeanGeom &g) {
+    switch (dtype) {
+        case RGD_F32: return lean_rows_occupancy_t<float, OP>(g);
+        case RGD_F16: return lean_rows_occupancy_t<__half, OP>(g);
+    }
+    return lean_rows_occupancy_t<__nv_bfloat16, OP>(g);
 }
 
 // Second stage of dweight: dw[b or -, c] = sum over partial rows, fixed order.
@@ -656,24 +765,6 @@ bool view_vec_ok(const rgd_rows &v, int esize) {
     return is_aligned(v.ptr, 16) && v.stride_b % ve == 0 && v.stride_n % ve == 0;
 }
 
-template <typename T, int OP>
-int launch_warp_rows(const RowParams &p, int vpt, int grid, cudaStream_t st) {
-    if (vpt == 8) warp_row_kernel<T, 8, OP><<<grid, ROW_THREADS, 0, st>>>(p);
-    else warp_row_kernel<T, 12, OP><<<grid, ROW_THREADS, 0, st>>>(p);
-    count_launch();
-    return check_launch();
-}
-
-template <int OP>
-int launch_warp_rows_dtype(int dtype, const RowParams &p, int vpt, int grid, cudaStream_t st) {
-    switch (dtype) {
-        case RGD_F32: return launch_warp_rows<float, OP>(p, vpt, grid, st);
-        case RGD_F16: return launch_warp_rows<__half, OP>(p, vpt, grid, st);
-        case RGD_BF16: return launch_warp_rows<__nv_bfloat16, OP>(p, vpt, grid, st);
-    }
-    return RGD_E_DTYPE;
-}
-
 // CTAs per batch for each stream.  `budget` is the total CTA count aimed at.
 void split_ctas(int nstreams, const int64_t *N, int64_t B, int rpc, int budget, int *P) {
     int64_t groups[2] = {0, 0}, total = 0;
@@ -755,18 +846,17 @@ int run_rows(const RowCall &c, float *dw_part0, float *dw_part1, int budget, cud
     p.w_dtype = c.w_dtype;
     p.eps = c.eps;
     int P[2] = {0, 0};
-    // Rows of 129..384 vectors: one warp per row (warp_row_kernel) instead of several warps
-    // per row with a block-wide barrier per row.
     const int nvec = pl.ve > 1 ? (cmax + pl.ve - 1) / pl.ve : 0;
-    // (Measured on B200 at 3072 channels: L2 forward 22.5 -> 20.5 us.  With a weight vector
-    // per row, or with x and dy of a backward row in registers, the registers per thread cut
-    // the rows in flight per SM and the multi-warp kernel stays ahead, so only L2 forward
-    // takes this path.)
-    const bool warp_rows = OP == L2_FWD && pl.ve > 1 && nvec > 128 && nvec <= 384;
-    const int warp_vpt = nvec <= 256 ? 8 : 12;
-    if (warp_rows) {
-        pl.tpr = 32;
-        budget = INT32_MAX;                                  // one row per warp, the hardware balances the CTAs
+    // Rows of exactly 128 * {2, 3, 4} vectors in every tensor: the lean kernel.
+    const LeanGeom lg = lean_geometry<OP>(nvec);
+    bool lean_rows = pl.ve > 1 && lg.ok && cmax % pl.ve == 0;
+    for (int s = 0; s < c.nstreams; ++s) lean_rows = lean_rows && (c.C[s] == cmax || c.N[s] == 0);
+    int rows_per_cta = ROW_THREADS / pl.tpr;
+    if (lean_rows) {
+        pl.tpr = lg.tpr;
+        rows_per_cta = lg.rpc;
+        const int resident = lean_rows_occupancy<OP>(c.x_dtype, lg) * num_sms();
+        if (OP != RMS_BWD || resident < budget) budget = resident;
     } else if (pl.ve > 1 && pl.vpt <= 4) {
         // Pipelined kernel: launch exactly one resident wave, so every CTA streams
         // several rows and the copy pipeline stays full.
@@ -776,7 +866,8 @@ int run_rows(const RowCall &c, float *dw_part0, float *dw_part1, int budget, cud
             if (OP != RMS_BWD || resident < budget) budget = resident;
         }
     }
-    split_ctas(c.nstreams, c.N, c.B, ROW_THREADS / pl.tpr, budget, P);
+    if (!lean_rows) rows_per_cta = ROW_THREADS / pl.tpr;
+    split_ctas(c.nstreams, c.N, c.B, rows_per_cta, budget, P);
     int64_t grid = 0;
     for (int s = 0; s < c.nstreams; ++s) {
         RowStream &rs = p.s[s];
@@ -809,9 +900,7 @@ int run_rows(const RowCall &c, float *dw_part0, float *dw_part1, int budget, cud
     if (P_out) { P_out[0] = P[0]; P_out[1] = P[1]; }
     if (grid == 0) return RGD_OK;
     if (grid > INT32_MAX) return RGD_E_SIZE;
-    if constexpr (OP == L2_FWD) {
-        if (warp_rows) return launch_warp_rows_dtype<OP>(c.x_dtype, p, warp_vpt, (int)grid, st);
-    }
+    if (lean_rows) return launch_lean_rows_dtype<OP>(c.x_dtype, p, lg, (int)grid, st);
     return launch_rows_dtype<OP>(c.x_dtype, p, pl, (int)grid, st);
 }
 
