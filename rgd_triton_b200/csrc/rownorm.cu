@@ -320,9 +320,7 @@ __device__ __forceinline__ void named_bar_sync() {
 }
 
 // TPR threads per row, RPC rows per CTA and iteration (CTA = TPR * RPC threads), VPT vectors per
-// thread.  The RMS backward carries x, dy, the weight and the dweight sums per thread; with
-// three vectors per thread that is 171 registers and one CTA per SM, so it runs in the wide
-// form instead: one vector per thread, the whole CTA on one row.
+// thread.
 template <typename T, int VPT, int OP, int TPR, int RPC>
 __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_constant__ RowParams p) {
     constexpr int THREADS = TPR * RPC;
@@ -381,10 +379,11 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
     T *orow = reinterpret_cast<T *>(s.out) + (int64_t)b * s.sob + (int64_t)n * s.son + t * VE;
     const int64_t xstep = (int64_t)step * s.sxn, dstep = BWD ? (int64_t)step * s.sdn : 0, ostep = (int64_t)step * s.son;
 
-    // Rows in flight ahead of the one being processed: one (FAR: two).
-    constexpr bool FAR = false;   // measured on B200: two rows ahead (212 registers) ran the RMS backward at 60 us, one row ahead (171) at 42 us
-    V xq[VPT], xn[VPT], xm[FAR ? VPT : 1];
-    V dq[BWD ? VPT : 1], dn[BWD ? VPT : 1], dm[FAR ? VPT : 1];
+    // The next row of this group is in flight while the current one is processed.  (Two rows
+    // ahead was measured for the RMS backward, by register copies and by rotating buffers
+    // through an unrolled loop: both slower on B200, 60-73 us against 42 us at configuration 5.)
+    V xq[VPT], xn[VPT];
+    V dq[BWD ? VPT : 1], dn[BWD ? VPT : 1];
     if (n < s.N) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -392,28 +391,12 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
             if (BWD) dq[j] = load_vec_stream<T, VE>(dr + j * TPR * VE);
         }
     }
-    if (FAR && n + step < s.N) {
-#pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            xn[j] = load_vec_stream<T, VE>(xr + xstep + j * TPR * VE);
-            dn[j] = load_vec_stream<T, VE>(dr + dstep + j * TPR * VE);
-        }
-    }
     for (; n < s.N; n += step) {
-        // the rows ahead of this group: in flight while this one is processed
-        if (!FAR) {
-            if (n + step < s.N) {
-#pragma unroll
-                for (int j = 0; j < VPT; ++j) {
-                    xn[j] = load_vec_stream<T, VE>(xr + xstep + j * TPR * VE);
-                    if (BWD) dn[j] = load_vec_stream<T, VE>(dr + dstep + j * TPR * VE);
-                }
-            }
-        } else if (n + 2 * step < s.N) {
+        if (n + step < s.N) {
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
-                xm[j] = load_vec_stream<T, VE>(xr + 2 * xstep + j * TPR * VE);
-                dm[j] = load_vec_stream<T, VE>(dr + 2 * dstep + j * TPR * VE);
+                xn[j] = load_vec_stream<T, VE>(xr + xstep + j * TPR * VE);
+                if (BWD) dn[j] = load_vec_stream<T, VE>(dr + dstep + j * TPR * VE);
             }
         }
         float xf[NE];
@@ -487,10 +470,6 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
         for (int j = 0; j < VPT; ++j) {
             xq[j] = xn[j];
             if (BWD) dq[j] = dn[j];
-            if (FAR) {
-                xn[j] = xm[j];
-                dn[j] = dm[j];
-            }
         }
     }
 
@@ -524,15 +503,16 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
     }
 }
 
-// Geometry of the lean kernel for rows of `nvec` vectors: wide (one vector per thread, TPR =
-// nvec in {256, 384, 512}) for the RMS backward, else narrow (128 threads per row, 2..4 vectors).
+// Geometry of the lean kernel for rows of `nvec` vectors: 128 threads per row, 2..4 vectors per
+// thread, two rows per CTA.  (A wide form, one vector per thread and the whole CTA on one row,
+// was measured for the RMS backward: 65 instead of 171 registers, but the same bytes in flight
+// per SM and the same 42-44 us at configuration 5, so it is not kept.)
 struct LeanGeom {
     bool ok;
     int tpr, rpc, vpt;
 };
 template <int OP>
 LeanGeom lean_geometry(int nvec) {
-    if (false && OP == RMS_BWD && (nvec == 256 || nvec == 384 || nvec == 512)) return {true, nvec, 1, 1};
     if (nvec % LEAN_TPR == 0 && nvec / LEAN_TPR >= 2 && nvec / LEAN_TPR <= 4) return {true, LEAN_TPR, 2, nvec / LEAN_TPR};
     return {false, 0, 0, 0};
 }
@@ -540,14 +520,7 @@ LeanGeom lean_geometry(int nvec) {
 // F(kernel, threads) for the instantiation that matches the geometry.
 template <typename T, int OP, typename F>
 int with_lean_kernel(const LeanGeom &g, F f) {
-    if (g.rpc == 1) {
-        if constexpr (OP == RMS_BWD) {
-            if (g.tpr == 256) return f(lean_row_kernel<T, 1, OP, 256, 1>, 256);
-            if (g.tpr == 384) return f(lean_row_kernel<T, 1, OP, 384, 1>, 384);
-            if (g.tpr == 512) return f(lean_row_kernel<T, 1, OP, 512, 1>, 512);
-        }
-        return RGD_E_SIZE;
-    }
+    if (g.rpc != 2 || g.tpr != LEAN_TPR) return RGD_E_SIZE;
     switch (g.vpt) {
         case 2: return f(lean_row_kernel<T, 2, OP, LEAN_TPR, 2>, 2 * LEAN_TPR);
         case 3: return f(lean_row_kernel<T, 3, OP, LEAN_TPR, 2>, 2 * LEAN_TPR);
