@@ -86,14 +86,6 @@ __device__ __forceinline__ uint32_t pack16b(float a, float b) {
 // BIAS: whether an additive bias exists; the no-bias instantiation carries none of
 // the bias code (and none of its register pressure).
 // (BIAS: 0 none, 1 read from global memory by the compute threads, 2 staged through TMA.)
-#ifdef RGD_ATTN_TIMING
-__device__ long long g_dbg[64];
-#define DBG_T(var) const long long var = clock64()
-#define DBG_ACC(slot, t0, t1) dbg[slot] += (t1) - (t0)
-#else
-#define DBG_T(var)
-#define DBG_ACC(slot, t0, t1)
-#endif
 
 template <int D, bool BF16, bool DKDV, int BIAS>
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_constant__ BwdTmaParams p) {
@@ -124,10 +116,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
     }
     const int nit = max(i_end - i_begin, 0);
     int *status = p.status;
-#ifdef RGD_ATTN_TIMING
-    long long dbg[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long k0 = clock64();
-#endif
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.x_full, 1);
@@ -226,29 +214,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
             for (int it = 0; it < nit && ok; ++it) {
                 const int s = it & 1, sn = s ^ 1;
                 const uint32_t par = (uint32_t)it & 1u;
-                DBG_T(m0);
                 ok = mbar_wait(&sm.p_ready, par, status, 53);
                 if (!ok) break;
-                DBG_T(m1);
-                DBG_ACC(0, m0, m1);
                 tc_fence_after_sync();
                 if (DKDV) issue_acc(ACC1_COL, G1_COL, smem_u32(sm.y2[s]), it == 0);     // dV += P^T dO
                 const bool more = it + 1 < nit;
                 if (more) {
                     ok = mbar_wait(&sm.y_full[sn], (uint32_t)((it + 1) >> 1) & 1u, status, 54);
                     if (!ok) break;
-                    DBG_T(my);
-                    DBG_ACC(4, m1, my);
                     tc_fence_after_sync();
                     issue_g(G1_COL, x1a, smem_u32(sm.y1[sn]));
                     umma_commit(&sm.g1_full);
                 }
-                DBG_T(m2);
-                DBG_ACC(1, m1, m2);
                 ok = mbar_wait(&sm.ds_ready, par, status, 55);
                 if (!ok) break;
-                DBG_T(m3);
-                DBG_ACC(2, m2, m3);
                 tc_fence_after_sync();
                 issue_acc(DKDV ? ACC2_COL : ACC1_COL, G2_COL, smem_u32(sm.y1[s]), it == 0);   // dK += dS^T Q | dQ += dS K
                 umma_commit(&sm.y_empty[s]);
@@ -256,14 +235,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                     issue_g(G2_COL, x2a, smem_u32(sm.y2[sn]));
                     umma_commit(&sm.g2_full);
                 }
-                DBG_T(m4);
-                DBG_ACC(3, m3, m4);
             }
             umma_commit(&sm.acc_full);
-#ifdef RGD_ATTN_TIMING
-            if (!DKDV && blockIdx.x == 0 && blockIdx.y == 0)
-                { for (int i = 0; i < 4; ++i) g_dbg[48 + i] = dbg[i]; g_dbg[57] = dbg[4]; }
-#endif
         }
     } else {
         // ------------------------------ compute warps ------------------------------
@@ -360,12 +333,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                     }
                 }
             }
-
-            DBG_T(c0t);
             ok = mbar_wait(&sm.g1_full, par, status, 61);
             if (!ok) break;
-            DBG_T(c1t);
-            DBG_ACC(0, c0t, c1t);
             tc_fence_after_sync();
             {
                 uint32_t ra[32], rb[32];
@@ -426,13 +395,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                     mbar_arrive(&sm.p_ready);
                 }
             }
-
-            DBG_T(c2t);
-            DBG_ACC(1, c1t, c2t);
             ok = mbar_wait(&sm.g2_full, par, status, 62);
             if (!ok) break;
-            DBG_T(c3t);
-            DBG_ACC(2, c2t, c3t);
             tc_fence_after_sync();
             {
                 uint32_t ga[32], gb[32];
@@ -476,15 +440,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
             }
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_ready);
-            DBG_T(c4t);
-            DBG_ACC(3, c3t, c4t);
         }
-#ifdef RGD_ATTN_TIMING
-        if (!DKDV && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
-            for (int i = 0; i < 4; ++i) g_dbg[52 + i] = dbg[i];
-            g_dbg[56] = clock64() - k0;
-        }
-#endif
 
         // epilogue: accumulators -> global
         if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 63);
@@ -574,9 +530,6 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
     const int nit = max(i_end - i_begin, 0);
     const int nsub = 2 * nit;
     int *status = p.status;
-#ifdef RGD_ATTN_TIMING
-    long long dbg[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.x_full, 1);
@@ -602,9 +555,6 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
     tc_fence_after_sync();
     const uint32_t tbase = sm.tmem_base;
 
-#ifdef RGD_ATTN_TIMING
-    const long long k0 = clock64();
-#endif
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0 && nit > 0) {
@@ -702,34 +652,21 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                     ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 87);
                     if (!ok) break;
                 }
-                DBG_T(b0);
                 ok = mbar_wait(&sm.p_ready[sb], par, status, 83);
                 if (!ok) break;
-                DBG_T(b1);
-                DBG_ACC(0, b0, b1);
                 tc_fence_after_sync();
                 issue_acc(u, ACC1_COL, G1_COL, dy2m[s]);            // dV += P^T dO
                 tc_fence_before_sync();
                 mbar_arrive(&sm.g1_free[sb]);   // issued, not finished: the tensor pipe runs MMAs in issue order
-                DBG_T(b2);
-                DBG_ACC(1, b1, b2);
                 ok = mbar_wait(&sm.ds_ready[sb], par, status, 84);
                 if (!ok) break;
-                DBG_T(b3);
-                DBG_ACC(2, b2, b3);
                 tc_fence_after_sync();
                 issue_acc(u, ACC2_COL, G2_COL, dy1m[s]);            // dK += dS^T Q
                 tc_fence_before_sync();
                 mbar_arrive(&sm.g2_free[sb]);
                 if (sb == 1) umma_commit(&sm.y_empty[s]);            // both sub-blocks of this block consumed
-                DBG_T(b4);
-                DBG_ACC(3, b3, b4);
             }
             umma_commit(&sm.acc_full);
-#ifdef RGD_ATTN_TIMING
-            if (blockIdx.x == 0 && blockIdx.y == 0)
-                for (int i = 0; i < 4; ++i) g_dbg[8 + i] = dbg[i];
-#endif
         }
     } else {
         // ------------------------------ compute warps ------------------------------
@@ -756,15 +693,11 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
             float pv[64];
 
             // row statistics of this block have landed
-            DBG_T(c0t);
             ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
             if (!ok) break;
             ok = mbar_wait(&sm.g1_full[sb], par, status, 91);
             if (!ok) break;
-            DBG_T(c1t);
-            DBG_ACC(0, c0t, c1t);
             tc_fence_after_sync();
-#ifndef RGD_DBG_NOCOMPUTE
             {
                 uint32_t ra[32], rb[32];
                 tmem_ld32(lane_base + G1_COL + col, ra);
@@ -803,18 +736,12 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 tmem_st32(lane_base + G1_COL + col, pk);
                 tmem_wait_st();
             }
-#endif
             tc_fence_before_sync();
             mbar_arrive(&sm.p_ready[sb]);
-            DBG_T(c2t);
-            DBG_ACC(1, c1t, c2t);
 
             ok = mbar_wait(&sm.g2_full[sb], par, status, 92);
             if (!ok) break;
-            DBG_T(c3t);
-            DBG_ACC(2, c2t, c3t);
             tc_fence_after_sync();
-#ifndef RGD_DBG_NOCOMPUTE
             {
                 uint32_t ga[32], gb[32];
                 tmem_ld32(lane_base + G2_COL + col, ga);
@@ -836,16 +763,9 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 tmem_st32(lane_base + G2_COL + col, pk);
                 tmem_wait_st();
             }
-#endif
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_ready[sb]);
-            DBG_T(c4t);
-            DBG_ACC(3, c3t, c4t);
         }
-#ifdef RGD_ATTN_TIMING
-        if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 127) == 0)
-            for (int i = 0; i < 4; ++i) g_dbg[16 + 8 * sb + i] = dbg[i];
-#endif
 
         // epilogue: dV, dK -> global
         if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 93);
@@ -887,9 +807,6 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
 
     tc_fence_before_sync();
     __syncthreads();
-#ifdef RGD_ATTN_TIMING
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_dbg[40] = clock64() - k0;
-#endif
     if (warp == 0) tmem_dealloc(tbase, TMEM_COLS);
 }
 
@@ -939,10 +856,6 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
     const int i_end = ((p.causal ? min(p.Tk, r0 + BT) : p.Tk) + BT - 1) / BT;
     const int nit = max(i_end, 0);
     int *status = p.status;
-#ifdef RGD_ATTN_TIMING
-    long long dbg[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long k0 = clock64();
-#endif
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.x_full, 1);
@@ -1131,15 +1044,12 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
             const bool next = it + 1 < nit;
             const uint32_t dcol = ((it & 1) ? G2B_COL : G2A_COL) + half * 64;
             const bool slow_next = (p.causal && (it + 1) * BT + BT > r0) || (it + 1) * BT + BT > p.Tk;
-            DBG_T(c0t);
             ok = mbar_wait(&sm.g2_full[it & 1], (uint32_t)(it >> 1) & 1u, status, 62);
             if (!ok) break;
             if (next) {
                 ok = mbar_wait(&sm.g1_full, (uint32_t)(it + 1) & 1u, status, 61);
                 if (!ok) break;
             }
-            DBG_T(c1t);
-            DBG_ACC(0, c0t, c1t);
             tc_fence_after_sync();
             const uint32_t scol = G1_COL + half * 64;
 #pragma unroll
@@ -1180,15 +1090,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_ready);
-            DBG_T(c4t);
-            DBG_ACC(3, c1t, c4t);
         }
-#ifdef RGD_ATTN_TIMING
-        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
-            for (int i = 0; i < 4; ++i) g_dbg[52 + i] = dbg[i];
-            g_dbg[56] = clock64() - k0;
-        }
-#endif
 
         // epilogue: dQ -> global
         if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 63);
@@ -1371,8 +1273,3 @@ int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st) {
 }  // namespace attn
 }  // namespace rgd
 
-#ifdef RGD_ATTN_TIMING
-extern "C" int rgd_dbg_fetch(long long *out) {
-    return (int)cudaMemcpyFromSymbol(out, rgd::attn::g_dbg, sizeof(long long) * 64);
-}
-#endif

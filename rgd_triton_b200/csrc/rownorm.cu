@@ -379,9 +379,10 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
     T *orow = reinterpret_cast<T *>(s.out) + (int64_t)b * s.sob + (int64_t)n * s.son + t * VE;
     const int64_t xstep = (int64_t)step * s.sxn, dstep = BWD ? (int64_t)step * s.sdn : 0, ostep = (int64_t)step * s.son;
 
-    // The next row of this group is in flight while the current one is processed.  (Two rows
-    // ahead was measured for the RMS backward, by register copies and by rotating buffers
-    // through an unrolled loop: both slower on B200, 60-73 us against 42 us at configuration 5.)
+    // The next row of this group is in flight while the current one is processed.  (Measured
+    // for the RMS backward on B200 at configuration 5 and not kept: two rows ahead, by register
+    // copies or by rotating buffers through an unrolled loop, 60-73 us against 42 us; weight
+    // row and dweight sums in shared memory, 128 registers and two CTAs per SM, 53 us.)
     V xq[VPT], xn[VPT];
     V dq[BWD ? VPT : 1], dn[BWD ? VPT : 1];
     if (n < s.N) {
