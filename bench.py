@@ -423,9 +423,9 @@ def main():
     achieved = dom[1] / (dom[2] * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": dom[0], "achieved": achieved, "peak": tf_burst, "unit": "TFLOP/s",
                 "frac": achieved / tf_burst, "peak_source": peak_src,
-                # DRAM bytes of the dK/dV + dQ launches: ncu capture of the quarter-size case (16 of the 64
-                # (batch, head) pairs, profiles/attention_tmem_kernels_small_case.md) scaled x4
-                "traffic": 4 * (67.74e6 + 5.86e6 + 67.71e6 + 4.66e6),
+                # DRAM bytes (read + write) of the prep, dK/dV and dQ launches: ncu capture of the quarter-size
+                # case (16 of the 64 (batch, head) pairs, profiles/attention_tmem_kernels_small_case.md) scaled x4
+                "traffic": 4 * (33.82e6 + 67.85e6 + 8.40e6 + 67.70e6 + 4.39e6),
                 "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
                 "fwd_tflops": f_fwd / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": f_bwd / (bwd_ms * 1e-3) / 1e12}
 
