@@ -12,7 +12,7 @@ from tests._util import DTYPES, T, assert_parity, gen, randn
 
 pytestmark = pytest.mark.gpu
 
-DIMS = [32, 63, 97, 122, 257, 384, 510, 740, 1023, 1024, 3072]
+DIMS = [32, 63, 97, 122, 257, 384, 510, 740, 1023, 1024, 2048, 3072, 4096]
 SEQS = [14, 97, 200]
 
 
@@ -114,6 +114,36 @@ def test_l2norm2(dt, n1, n2, c1, c2):
     assert_parity(yb, O.l2norm_fwd(b, 1e-6), "y2")
     assert_parity(da, O.l2norm_bwd(a, g1, 1e-6), "dx1", atol_rel=1e-5)
     assert_parity(db, O.l2norm_bwd(b, g2, 1e-6), "dx2", atol_rel=1e-5)
+
+
+@pytest.mark.parametrize("dt,C", [("bf16", 2048), ("f16", 3072), ("bf16", 4096), ("f32", 1024), ("f32", 1536)])
+def test_exact_row_lengths_strided_views_and_weight_kinds(dt, C):
+    """Rows of exactly 128 * {2, 3, 4} 16-byte vectors take the lean kernel: strided row and
+    batch views (a slice of a wider, longer tensor), rows that do not fill the last CTA
+    iteration, per-batch and fp32 weights, and L2 with a zero row."""
+    dtype = DTYPES[dt]
+    g = gen(C + 3)
+    host = randn(g, 3, 2 * 37, 2 * C, dtype=dtype)
+    view = lambda t: t[:, 1::2, C // 2:C // 2 + C]      # row stride 4C, batch stride 148C, 16-byte aligned offset
+    x = view(host)
+    dy = randn(g, *x.shape, dtype=dtype)
+    for wshape, wdt in (((C,), dtype), ((3, 1, C), torch.float32)):
+        w = (1 + 0.02 * torch.randn(*wshape, generator=g)).to(wdt)
+        xin = view(host.cuda()).detach().requires_grad_(True)
+        assert xin.stride() == x.stride()
+        wd = w.cuda().requires_grad_(True)
+        y = F_.triton_rms_func_fn(xin, wd, 1e-6)
+        dx, dw = torch.autograd.grad(y, (xin, wd), dy.cuda())
+        assert_parity(y.cpu(), O.rmsnorm_fwd(x, w, 1e-6), f"y {wshape}")
+        odx, odw = O.rmsnorm_bwd(x, w, dy, 1e-6)
+        assert_parity(dx.cpu(), odx, f"dx {wshape}", atol_rel=1e-5)
+        assert_parity(dw.cpu(), odw, f"dw {wshape}", atol_rel=1e-5)
+    xz = x.clone()
+    xz[1, 5] = 0                                        # forward only: its gradient is dy / eps, beyond fp16
+    (y,), _ = _run(lambda a: F_.triton_norm_func_fn(a, 1e-6), [xz], [dy])
+    assert_parity(y, O.l2norm_fwd(xz, 1e-6), "l2 y")
+    (_,), (dxl,) = _run(lambda a: F_.triton_norm_func_fn(a, 1e-6), [x.contiguous()], [dy])
+    assert_parity(dxl, O.l2norm_bwd(x, dy, 1e-6), "l2 dx", atol_rel=1e-5)
 
 
 def test_strided_and_noncontiguous_inputs():
