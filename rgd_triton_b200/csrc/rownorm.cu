@@ -314,6 +314,15 @@ __device__ __forceinline__ void load_w_vec(const void *w, int64_t idx, int w_dty
 // ---------------------------------------------------------------------------
 constexpr int LEAN_TPR = 128;   // narrow form: 128 threads per row, two rows per CTA
 
+// Makes the compiler forget what it derived from a 16-byte register vector, so that a later
+// pass converts the raw elements again instead of keeping fp32 copies of the whole row alive.
+template <typename V>
+__device__ __forceinline__ void forget_derived(V &v) {
+    static_assert(sizeof(V) == 16, "16-byte vectors only");
+    uint4 &u = reinterpret_cast<uint4 &>(v);
+    asm volatile("" : "+r"(u.x), "+r"(u.y), "+r"(u.z), "+r"(u.w));
+}
+
 template <int ID, int THREADS>
 __device__ __forceinline__ void named_bar_sync() {
     asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(THREADS) : "memory");
@@ -322,7 +331,7 @@ __device__ __forceinline__ void named_bar_sync() {
 // TPR threads per row, RPC rows per CTA and iteration (CTA = TPR * RPC threads), VPT vectors per
 // thread.
 template <typename T, int VPT, int OP, int TPR, int RPC>
-__global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_constant__ RowParams p) {
+__global__ void __launch_bounds__(TPR * RPC, OP == RMS_BWD ? 2 : 1) lean_row_kernel(const __grid_constant__ RowParams p) {
     constexpr int THREADS = TPR * RPC;
     constexpr bool BWD = (OP == L2_BWD || OP == RMS_BWD);
     constexpr bool RMS = (OP == RMS_FWD || OP == RMS_BWD);
@@ -332,6 +341,9 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
     using V = Vec<T, VE>;
     __shared__ float red[2][THREADS / 32];
     __shared__ float dwred[(OP == RMS_BWD && RPC > 1) ? THREADS * VE : 1];
+    // RMS backward: the fp32 weight row sits in shared memory ([VPT][TPR][VE]) and is read
+    // per use, which with the raw-register passes below keeps the kernel at 2 CTAs per SM.
+    __shared__ __align__(16) float wsm[OP == RMS_BWD ? TPR * NE : 1];
 
     const int sid = (int)blockIdx.x >= p.split ? 1 : 0;
     const RowStream &s = p.s[sid];
@@ -356,7 +368,7 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
         return a;
     };
 
-    float wv[RMS ? NE : 1];
+    float wv[OP == RMS_FWD ? NE : 1];
     float dwacc[OP == RMS_BWD ? NE : 1];
     if (RMS) {
 #pragma unroll
@@ -364,13 +376,25 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
             float w8[VE];
             load_w_vec<T, VE>(s.w, (int64_t)b * s.swb + (t + j * TPR) * VE, p.w_dtype, w8);
 #pragma unroll
-            for (int e = 0; e < VE; ++e) wv[j * VE + e] = w8[e];
+            for (int e = 0; e < VE; ++e) {
+                if (OP == RMS_FWD) wv[j * VE + e] = w8[e];
+                else if (rg == 0) wsm[(j * TPR + t) * VE + e] = w8[e];
+            }
         }
     }
     if (OP == RMS_BWD) {
 #pragma unroll
         for (int i = 0; i < NE; ++i) dwacc[i] = 0.f;
+        __syncthreads();
     }
+    auto w_slot = [&](int j, float (&w8)[VE]) {            // this thread's weights of vector j
+        const float4 *src = reinterpret_cast<const float4 *>(wsm + (j * TPR + t) * VE);
+#pragma unroll
+        for (int q = 0; q < VE / 4; ++q) {
+            const float4 f = src[q];
+            w8[4 * q] = f.x; w8[4 * q + 1] = f.y; w8[4 * q + 2] = f.z; w8[4 * q + 3] = f.w;
+        }
+    };
 
     const int step = s.P * RPC;
     int n = chunk * RPC + rg;
@@ -382,7 +406,8 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
     // The next row of this group is in flight while the current one is processed.  (Measured
     // for the RMS backward on B200 at configuration 5 and not kept: two rows ahead, by register
     // copies or by rotating buffers through an unrolled loop, 60-73 us against 42 us; weight
-    // row and dweight sums in shared memory, 128 registers and two CTAs per SM, 53 us.)
+    // row AND dweight sums in shared memory, 53 us.  Kept: weight row in shared memory plus
+    // raw-register passes, two CTAs per SM, 40 us.)
     V xq[VPT], xn[VPT];
     V dq[BWD ? VPT : 1], dn[BWD ? VPT : 1];
     if (n < s.N) {
@@ -400,68 +425,113 @@ __global__ void __launch_bounds__(TPR * RPC) lean_row_kernel(const __grid_consta
                 if (BWD) dn[j] = load_vec_stream<T, VE>(dr + dstep + j * TPR * VE);
             }
         }
-        float xf[NE];
-        float df[BWD ? NE : 1];
+        if constexpr (OP == RMS_BWD) {
+            // Three passes over the raw 16-bit (or fp32) registers, converting again in each:
+            // fp32 copies of x and dy kept across the two row sums would cost 2 * NE registers
+            // and with them the second CTA per SM.  Same arithmetic and order as below.
+            float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < VPT; ++j)
-#pragma unroll
-            for (int e = 0; e < VE; ++e) {
-                xf[j * VE + e] = to_f32<T>(xq[j].v[e]);
-                if (BWD) df[j * VE + e] = to_f32<T>(dq[j].v[e]);
-            }
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < NE; ++i) ss = fmaf(xf[i], xf[i], ss);
-        ss = group_sum(ss);
-
-        // Row scale: rmsnorm_cached.py:75-76, l2normalize_cached.py:72-77.
-        float r;
-        if (RMS) {
-            r = rsqrtf(ss * invC + p.eps);
-        } else {
-            const float len = sqrtf(ss);
-            r = (len < p.eps) ? (1.0f / p.eps) : (1.0f / len);
-        }
-
-        if (!BWD) {
-#pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                V yo;
+            for (int j = 0; j < VPT; ++j)
 #pragma unroll
                 for (int e = 0; e < VE; ++e) {
-                    float y = xf[j * VE + e] * r;
-                    if (RMS) y = y * wv[j * VE + e];
-                    yo.v[e] = from_f32<T>(y);
+                    const float xf = to_f32<T>(xq[j].v[e]);
+                    ss = fmaf(xf, xf, ss);
                 }
-                store_vec_stream<T, VE>(orow + j * TPR * VE, yo);
-            }
-        } else {
-            // xhat, then g = sum(xhat * dy * w) [/ C for RMS]: rmsnorm_cached.py:213-231,
-            // l2normalize_cached.py:214-226.
+            ss = group_sum(ss);
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) forget_derived(xq[j]);
+            const float r = rsqrtf(ss * invC + p.eps);
             float g = 0.f;
 #pragma unroll
-            for (int i = 0; i < NE; ++i) {
-                xf[i] *= r;
-                g += RMS ? xf[i] * df[i] * wv[i] : xf[i] * df[i];
+            for (int j = 0; j < VPT; ++j) {
+                float w8[VE];
+                w_slot(j, w8);
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    const float xh = to_f32<T>(xq[j].v[e]) * r;
+                    g += xh * to_f32<T>(dq[j].v[e]) * w8[e];
+                }
             }
-            g = group_sum(g);
-            if (RMS) g *= invC;
+            g = group_sum(g) * invC;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                forget_derived(xq[j]);
+                forget_derived(dq[j]);
+            }
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 V yo;
+                float w8[VE];
+                w_slot(j, w8);
 #pragma unroll
                 for (int e = 0; e < VE; ++e) {
                     const int i = j * VE + e;
-                    float dxv;
-                    if (RMS) {
-                        dxv = (df[i] * wv[i] - xf[i] * g) * r;
-                        if (OP == RMS_BWD) dwacc[i] += xf[i] * df[i];
-                    } else {
-                        dxv = (df[i] - xf[i] * g) * r;
-                    }
-                    yo.v[e] = from_f32<T>(dxv);
+                    const float xh = to_f32<T>(xq[j].v[e]) * r;
+                    const float df = to_f32<T>(dq[j].v[e]);
+                    yo.v[e] = from_f32<T>((df * w8[e] - xh * g) * r);
+                    dwacc[i] += xh * df;
                 }
                 store_vec_stream<T, VE>(orow + j * TPR * VE, yo);
+            }
+        } else {
+            float xf[NE];
+            float df[BWD ? NE : 1];
+    #pragma unroll
+            for (int j = 0; j < VPT; ++j)
+    #pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    xf[j * VE + e] = to_f32<T>(xq[j].v[e]);
+                    if (BWD) df[j * VE + e] = to_f32<T>(dq[j].v[e]);
+                }
+            float ss = 0.f;
+    #pragma unroll
+            for (int i = 0; i < NE; ++i) ss = fmaf(xf[i], xf[i], ss);
+            ss = group_sum(ss);
+
+            // Row scale: rmsnorm_cached.py:75-76, l2normalize_cached.py:72-77.
+            float r;
+            if (RMS) {
+                r = rsqrtf(ss * invC + p.eps);
+            } else {
+                const float len = sqrtf(ss);
+                r = (len < p.eps) ? (1.0f / p.eps) : (1.0f / len);
+            }
+
+            if (!BWD) {
+    #pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    V yo;
+    #pragma unroll
+                    for (int e = 0; e < VE; ++e) {
+                        float y = xf[j * VE + e] * r;
+                        if (RMS) y = y * wv[j * VE + e];
+                        yo.v[e] = from_f32<T>(y);
+                    }
+                    store_vec_stream<T, VE>(orow + j * TPR * VE, yo);
+                }
+            } else {
+                // xhat, then g = sum(xhat * dy * w) [/ C for RMS]: rmsnorm_cached.py:213-231,
+                // l2normalize_cached.py:214-226.
+                float g = 0.f;
+    #pragma unroll
+                for (int i = 0; i < NE; ++i) {
+                    xf[i] *= r;
+                    g += xf[i] * df[i];                         // (the RMS backward took the branch above)
+                }
+                g = group_sum(g);
+                if (RMS) g *= invC;
+    #pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    V yo;
+    #pragma unroll
+                    for (int e = 0; e < VE; ++e) {
+                        const int i = j * VE + e;
+                        float dxv;
+                        dxv = (df[i] - xf[i] * g) * r;
+                        yo.v[e] = from_f32<T>(dxv);
+                    }
+                    store_vec_stream<T, VE>(orow + j * TPR * VE, yo);
+                }
             }
         }
         xr += xstep;
