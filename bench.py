@@ -431,18 +431,19 @@ def main():
 
     # ---------------- end to end: host buffers through the module API ----------------
     # Every step copies its inputs from pinned host memory, runs forward + backward through
-    # ops.FlashAttention and copies all four results back.  Steps alternate between two CUDA
+    # ops.FlashAttention and copies all four results back.  Steps rotate over three CUDA
     # streams, each with its own pinned result buffers, so one step's device-to-host copies
     # overlap the next step's host-to-device copies and kernels (PCIe is full duplex and the
     # copy engines are separate); within a stream everything stays in order.
+    n_slots = 3        # measured on B200: 1 stream 12.0 ms per step, 2 streams 6.9, 3 streams 6.3, 4 streams 6.3
     slots = []
-    for _ in range(2):
+    for _ in range(n_slots):
         slots.append({"stream": torch.cuda.Stream(device=dev),
                       "ho": torch.empty_like(hq).pin_memory(),
                       "hgrads": [torch.empty_like(hq).pin_memory() for _ in range(3)]})
 
     def e2e_step(i):
-        sl = slots[i & 1]
+        sl = slots[i % n_slots]
         with torch.cuda.stream(sl["stream"]):
             dq_, dk_, dv_, ddo = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
             o, grads = attn_step(dq_, dk_, dv_, ddo)
@@ -471,7 +472,7 @@ def main():
     nbytes = hq.numel() * hq.element_size()
     e2e = {"value": world * (f_fwd + f_bwd) / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "steps": e2e_steps,
-           "overlap": "steps alternate between 2 CUDA streams: D2H of step i overlaps H2D + kernels of step i+1"}
+           "overlap": "steps rotate over 3 CUDA streams: D2H of step i overlaps H2D + kernels of the next steps"}
     del slots
     del q, k, v, do
     torch.cuda.empty_cache()
