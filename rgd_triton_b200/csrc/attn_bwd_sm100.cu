@@ -61,6 +61,10 @@ struct alignas(1024) BwdTmaSmem {
     unsigned char x1[BT * D * 2], x2[BT * D * 2];            // fixed tiles
     unsigned char y1[2][BT * D * 2], y2[2][BT * D * 2];      // looped tiles, 2 stages
     unsigned char bias[BSTAGES > 0 ? BSTAGES : 1][BSTAGES > 0 ? BT * BT * 2 : 1024];
+    // dK/dV: row statistics of the staged query block (not with head_dim 128 and staged bias
+    // tiles: shared memory is full there and the statistics are read from global memory)
+    static constexpr int NSTAT = (D == 128 && BSTAGES > 0) ? 4 : BT;
+    alignas(16) float lse_s[2][NSTAT], dsc_s[2][NSTAT];
     uint64_t x_full, g1_full, g2_full, p_ready, ds_ready, acc_full;
     uint64_t y_full[2], y_empty[2];
     uint64_t bb_full[2], bb_empty[2];
@@ -90,6 +94,7 @@ __device__ __forceinline__ uint32_t pack16b(float a, float b) {
 template <int D, bool BF16, bool DKDV, int BIAS>
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_constant__ BwdTmaParams p) {
     constexpr int BSTAGES = BIAS == 2 ? (D == 64 ? 2 : 1) : 0;
+    constexpr bool STAGE_STATS = DKDV && !(D == 128 && BSTAGES > 0);
     constexpr uint32_t BIAS_BYTES = BT * BT * 2;
     constexpr int HALVES = D / 64;
     constexpr uint32_t PANEL = 128 * 64 * 2;
@@ -162,11 +167,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                 const uint32_t ph = (uint32_t)(it >> 1) & 1u;
                 ok = mbar_wait(&sm.y_empty[s], ph ^ 1u, status, 41);
                 if (!ok) break;
-                mbar_expect_tx(&sm.y_full[s], 2 * TILE_BYTES);
+                mbar_expect_tx(&sm.y_full[s], 2 * TILE_BYTES + (STAGE_STATS ? 2 * BT * 4 : 0));
                 const int row = (i_begin + it) * BT;
                 for (int hh = 0; hh < HALVES; ++hh) {
                     tma_load_4d(sm.y1[s] + hh * PANEL, my1, &sm.y_full[s], hh * 64, row, h, b);
                     tma_load_4d(sm.y2[s] + hh * PANEL, my2, &sm.y_full[s], hh * 64, row, h, b);
+                }
+                if constexpr (STAGE_STATS) {
+                    // the query block's lse / delta rows, read by every compute thread in both phases
+                    bulk_load_1d(sm.lse_s[s], p.lse2 + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
+                    bulk_load_1d(sm.dsc_s[s], p.delta_s + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
                 }
                 if constexpr (BIAS == 2) {
                     const int sb = it % BSTAGES;
@@ -333,6 +343,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                     }
                 }
             }
+            // row statistics of this query block: staged in shared memory, else straight from global
+            const float *lse_blk = STAGE_STATS ? sm.lse_s[it & 1] : lse2_bh + blk0;
+            const float *dsc_blk = STAGE_STATS ? sm.dsc_s[it & 1] : ds_bh + blk0;
+            if (STAGE_STATS) {
+                ok = mbar_wait(&sm.y_full[it & 1], (uint32_t)(it >> 1) & 1u, status, 60);
+                if (!ok) break;
+            }
             ok = mbar_wait(&sm.g1_full, par, status, 61);
             if (!ok) break;
             tc_fence_after_sync();
@@ -351,7 +368,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                     if (DKDV) {
                         float4 l4[16];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) l4[i] = __ldg(reinterpret_cast<const float4 *>(lse2_bh + c0) + i);
+                        for (int i = 0; i < 16; ++i) l4[i] = reinterpret_cast<const float4 *>(lse_blk + half * 64)[i];
                         tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
@@ -380,7 +397,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                         const int qi = DKDV ? col : row, kj = DKDV ? row : col;
                         float x = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]) * p.scale_log2;
                         const bool masked = kj >= p.Tk || qi >= p.Tq || (p.causal && kj > qi);
-                        const float l2 = DKDV ? __ldg(lse2_bh + qi) : lse_row;     // qi < Tq128 always
+                        const float l2 = DKDV ? lse_blk[half * 64 + i] : lse_row;
                         if constexpr (BIAS != 0) x = fmaf(bv[i], LOG2E, x);
                         pv[i] = masked ? 0.f : ex2b(x - l2);
                     }
@@ -406,7 +423,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                 if (DKDV) {
                     float4 d4[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) d4[i] = __ldg(reinterpret_cast<const float4 *>(ds_bh + c0) + i);
+                    for (int i = 0; i < 16; ++i) d4[i] = reinterpret_cast<const float4 *>(dsc_blk + half * 64)[i];
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
