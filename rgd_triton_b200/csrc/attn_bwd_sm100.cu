@@ -391,15 +391,28 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                     }
                 } else {
                     tmem_wait_ld();
+                    // Interior blocks with a bias need no mask either: rows past the end of Q have
+                    // lse2 = +inf, which makes their P exactly 0 whatever the (clamped) bias holds.
+                    const bool need_mask = diag || cta_key_tail || (!DKDV && blk0 + BT > p.Tk);
+                    if (!need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const int col = c0 + i;
-                        const int qi = DKDV ? col : row, kj = DKDV ? row : col;
-                        float x = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]) * p.scale_log2;
-                        const bool masked = kj >= p.Tk || qi >= p.Tq || (p.causal && kj > qi);
-                        const float l2 = DKDV ? lse_blk[half * 64 + i] : lse_row;
-                        if constexpr (BIAS != 0) x = fmaf(bv[i], LOG2E, x);
-                        pv[i] = masked ? 0.f : ex2b(x - l2);
+                        for (int i = 0; i < 64; ++i) {
+                            float x = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]) * p.scale_log2;
+                            const float l2 = DKDV ? lse_blk[half * 64 + i] : lse_row;
+                            if constexpr (BIAS != 0) x = fmaf(bv[i], LOG2E, x);
+                            pv[i] = ex2b(x - l2);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 64; ++i) {
+                            const int col = c0 + i;
+                            const int qi = DKDV ? col : row, kj = DKDV ? row : col;
+                            float x = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]) * p.scale_log2;
+                            const bool masked = kj >= p.Tk || qi >= p.Tq || (p.causal && kj > qi);
+                            const float l2 = DKDV ? lse_blk[half * 64 + i] : lse_row;
+                            if constexpr (BIAS != 0) x = fmaf(bv[i], LOG2E, x);
+                            pv[i] = masked ? 0.f : ex2b(x - l2);
+                        }
                     }
                 }
                 if (DKDV) {
