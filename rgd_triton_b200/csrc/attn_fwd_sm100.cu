@@ -354,15 +354,23 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                         if constexpr (BIAS == 1) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
                         if constexpr (BIAS == 2) bias_from_smem<BF16>(btile, row_l, c * 64 + hf * 32, bb);
                         if (hf == 0) tmem_wait_ld();
+                        // two copies of the loop, so that blocks without a mask carry no per-element test
+                        if (need_mask) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            float x = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
-                            if constexpr (BIAS != 0) x += bb[i];
-                            if (need_mask) {
+                            for (int i = 0; i < 32; ++i) {
+                                float x = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
+                                if constexpr (BIAS != 0) x += bb[i];
                                 const int col = n0 + c * 64 + hf * 32 + i;
                                 if (col >= p.Tk || (p.causal && col > row)) x = -INFINITY;
+                                mx = fmaxf(mx, x);
                             }
-                            mx = fmaxf(mx, x);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                float x = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
+                                if constexpr (BIAS != 0) x += bb[i];
+                                mx = fmaxf(mx, x);
+                            }
                         }
                     }
                 }
@@ -416,22 +424,35 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                         if constexpr (BIAS == 1) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 64 + hf * 32, bb);
                         if constexpr (BIAS == 2) bias_from_smem<BF16>(btile, row_l, c * 64 + hf * 32, bb);
                         if (hf == 0) tmem_wait_ld();
+                        if (need_mask) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float x0 = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
-                            float x1 = __uint_as_float(hf ? r1[i + 1] : r0[i + 1]) * p.scale_log2;
-                            if constexpr (BIAS != 0) {
-                                x0 += bb[i];
-                                x1 += bb[i + 1];
-                            }
-                            if (need_mask) {
+                            for (int i = 0; i < 32; i += 2) {
+                                float x0 = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
+                                float x1 = __uint_as_float(hf ? r1[i + 1] : r0[i + 1]) * p.scale_log2;
+                                if constexpr (BIAS != 0) {
+                                    x0 += bb[i];
+                                    x1 += bb[i + 1];
+                                }
                                 const int col = n0 + c * 64 + hf * 32 + i;
                                 if (col >= p.Tk || (p.causal && col > row)) x0 = -INFINITY;
                                 if (col + 1 >= p.Tk || (p.causal && col + 1 > row)) x1 = -INFINITY;
+                                const float p0 = ex2(x0 - m_use), p1 = ex2(x1 - m_use);
+                                ls0 += p0 + p1;
+                                pk[hf * 16 + (i >> 1)] = pack16<BF16>(p0, p1);
                             }
-                            const float p0 = ex2(x0 - m_use), p1 = ex2(x1 - m_use);
-                            ls0 += p0 + p1;
-                            pk[hf * 16 + (i >> 1)] = pack16<BF16>(p0, p1);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                float x0 = __uint_as_float(hf ? r1[i] : r0[i]) * p.scale_log2;
+                                float x1 = __uint_as_float(hf ? r1[i + 1] : r0[i + 1]) * p.scale_log2;
+                                if constexpr (BIAS != 0) {
+                                    x0 += bb[i];
+                                    x1 += bb[i + 1];
+                                }
+                                const float p0 = ex2(x0 - m_use), p1 = ex2(x1 - m_use);
+                                ls0 += p0 + p1;
+                                pk[hf * 16 + (i >> 1)] = pack16<BF16>(p0, p1);
+                            }
                         }
                     }
                 }
