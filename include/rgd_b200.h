@@ -13,8 +13,11 @@
  *     1000 + cudaError_t; RGD_E_TIMEOUT a bounded device-side wait that ran out.
  *     Argument errors correspond to the AssertionError / RuntimeError the
  *     reference's host wrappers raise; the Python layer re-raises them as such.
- *   - All entry points are re-entrant; the only process-wide state is the
- *     one-time cudaFuncSetAttribute opt-in for large shared memory.
+ *   - All entry points are re-entrant.  Process-wide state: a memo of the
+ *     per-kernel cudaFuncSetAttribute opt-ins for large shared memory and of
+ *     occupancy queries (each made once per device and kernel), the launch
+ *     counter, the sticky status word of the bounded device-side waits, and the
+ *     fixed scratch of rgd_rmsnorm_bwd_static.
  *
  * Each declaration cites the reference interface (file:line inside the
  * rgd_triton project) whose launch it replaces.
@@ -79,6 +82,33 @@ int64_t     rgd_launch_count(void);
  * cleared by the call).  Synchronises the device; meant for tests, smoke
  * checks and debugging, not for the per-step path. */
 int         rgd_device_status(void);
+
+/* Test hook for the bounded device-side waits (no counterpart in the
+ * reference): launches one thread that waits, for at most `limit_ns`
+ * (1 us .. 100 ms), on a barrier nothing ever arrives at.  The wait gives up,
+ * records itself in the status word and the kernel returns normally, so the
+ * next rgd_device_status() reports RGD_E_TIMEOUT once and RGD_OK afterwards.
+ * Nothing traps, faults or spins without a limit. */
+int         rgd_selftest_bounded_wait(int64_t limit_ns, void *stream);
+
+/* ---- launch-plan cache -------------------------------------------------- */
+/* What `enable_cache` means here.  The reference keeps the compiled Triton
+ * kernel handle of the first launch in the module's cache slot and relaunches
+ * it directly (rgd_triton/ops.py:12-24, e.g.
+ * flash_attn_triton_cached.py:805-836,878-879).  This library has nothing to
+ * compile at run time; what costs host time per attention call is encoding the
+ * TMA tensor-map descriptors.  An rgd_cache holds the descriptors of the calls
+ * it has seen, keyed on base pointer + extents + strides + box + dtype, so a
+ * repeated call copies them instead of re-encoding, and a call whose tensors
+ * moved or changed shape misses and re-encodes (it can never launch with a
+ * stale descriptor, unlike the reference's frozen constexprs).  The handle is
+ * host memory only; pass NULL wherever a cache is accepted to run without. */
+typedef struct rgd_cache rgd_cache;
+rgd_cache  *rgd_cache_create(void);                 /* NULL if out of host memory */
+void        rgd_cache_destroy(rgd_cache *cache);    /* NULL is allowed            */
+/* Counters of the cache (any of the three pointers may be NULL). */
+int         rgd_cache_stats(rgd_cache *cache, int64_t *hits, int64_t *misses,
+                            int64_t *entries);
 
 /* ---- row L2 normalise: y = x / max(||x||, eps) ------------------------- */
 /* Replaces _norm_fwd / _fused_norm_fwd (l2normalize_cached.py:237-318,
@@ -219,10 +249,13 @@ int64_t rgd_attn_lse_rows(int64_t Tq);
 int rgd_attn_fwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v,
                  const rgd_bias *bias, const rgd_heads *o, float *lse,
                  int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d,
-                 float softmax_scale, int causal, int dtype, void *stream);
+                 float softmax_scale, int causal, int dtype, rgd_cache *cache,
+                 void *stream);
 
-/* Scratch bytes for rgd_attn_bwd (delta rows and, on the tensor-memory path,
- * an fp32 dQ accumulator). */
+/* Scratch bytes for rgd_attn_bwd: one fp32 row of delta = rowsum(O * dO) per
+ * (batch, head) on the general path; on the tensor-memory path two fp32 rows
+ * per (batch, head), lse * log2(e) and delta * scale, each Tq rounded up to
+ * 128.  There is no fp32 dQ accumulator on either path. */
 int64_t rgd_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq,
                                      int64_t Tk, int64_t d, int dtype);
 
@@ -235,12 +268,23 @@ int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v,
                  const rgd_heads *dk, const rgd_heads *dv, int64_t B,
                  int64_t H, int64_t Tq, int64_t Tk, int64_t d,
                  float softmax_scale, int causal, int dtype, void *workspace,
-                 int64_t workspace_bytes, void *stream);
+                 int64_t workspace_bytes, rgd_cache *cache, void *stream);
 
-/* Which attention implementation a call with these sizes takes:
- * 1 = tcgen05 / tensor-memory / TMA kernels, 0 = general mma.sync kernels. */
-int rgd_attn_uses_tmem(int64_t Tq, int64_t Tk, int64_t d, int dtype,
-                       int64_t q_stride_n, int64_t k_stride_n);
+/* Which attention implementation rgd_attn_fwd / rgd_attn_bwd take for these
+ * views: 1 = tcgen05 / tensor-memory / TMA kernels, 0 = general mma.sync
+ * kernels.  Evaluates exactly the test the entry points use (head_dim 64 or
+ * 128, every view 16-byte addressable with positive strides on dimensions of
+ * extent > 1, and for the forward softmax_scale > 0). */
+int rgd_attn_fwd_uses_tmem(const rgd_heads *q, const rgd_heads *k,
+                           const rgd_heads *v, const rgd_heads *o, int64_t B,
+                           int64_t H, int64_t Tq, int64_t Tk, int64_t d,
+                           float softmax_scale, int dtype);
+int rgd_attn_bwd_uses_tmem(const rgd_heads *q, const rgd_heads *k,
+                           const rgd_heads *v, const rgd_heads *o,
+                           const rgd_heads *d_o, const rgd_heads *dq,
+                           const rgd_heads *dk, const rgd_heads *dv, int64_t B,
+                           int64_t H, int64_t Tq, int64_t Tk, int64_t d,
+                           int dtype);
 
 #ifdef __cplusplus
 }

@@ -53,6 +53,10 @@ SIGNATURES = {
     "rgd_abi_version": (_i32, []),
     "rgd_launch_count": (_i64, []),
     "rgd_device_status": (_i32, []),
+    "rgd_selftest_bounded_wait": (_i32, [_i64, _vp]),
+    "rgd_cache_create": (_vp, []),
+    "rgd_cache_destroy": (None, [_vp]),
+    "rgd_cache_stats": (_i32, [_vp, _pi64, _pi64, _pi64]),
     "rgd_l2norm_fwd": (_i32, [_i32, _pRows, _pRows, _pi64, _pi64, _i64, _f32, _i32, _vp]),
     "rgd_l2norm_bwd": (_i32, [_i32, _pRows, _pRows, _pRows, _pi64, _pi64, _i64, _f32, _i32, _vp]),
     "rgd_rmsnorm_fwd": (_i32, [_i32, _pRows, _pvp, _pi64, _pRows, _pi64, _pi64, _i64, _f32, _i32, _i32, _vp]),
@@ -69,11 +73,13 @@ SIGNATURES = {
     "rgd_lnrope_bwd": (_i32, [_pHeads, _pHeads, _pHeads, _pHeads, _vp, _i64, _i64, _pHeads, _pHeads] + [_i64] * 9
                        + [_f32, _i32, _i32, _vp]),
     "rgd_attn_lse_rows": (_i64, [_i64]),
-    "rgd_attn_fwd": (_i32, [_pHeads, _pHeads, _pHeads, _pBias, _pHeads, _vp] + [_i64] * 5 + [_f32, _i32, _i32, _vp]),
+    "rgd_attn_fwd": (_i32, [_pHeads, _pHeads, _pHeads, _pBias, _pHeads, _vp] + [_i64] * 5
+                     + [_f32, _i32, _i32, _vp, _vp]),
     "rgd_attn_bwd_workspace_bytes": (_i64, [_i64] * 5 + [_i32]),
     "rgd_attn_bwd": (_i32, [_pHeads, _pHeads, _pHeads, _pBias, _pHeads, _vp, _pHeads, _pHeads, _pHeads, _pHeads]
-                     + [_i64] * 5 + [_f32, _i32, _i32, _vp, _i64, _vp]),
-    "rgd_attn_uses_tmem": (_i32, [_i64, _i64, _i64, _i32, _i64, _i64]),
+                     + [_i64] * 5 + [_f32, _i32, _i32, _vp, _i64, _vp, _vp]),
+    "rgd_attn_fwd_uses_tmem": (_i32, [_pHeads] * 4 + [_i64] * 5 + [_f32, _i32]),
+    "rgd_attn_bwd_uses_tmem": (_i32, [_pHeads] * 8 + [_i64] * 5 + [_i32]),
 }
 
 _lib = None
@@ -135,6 +141,26 @@ def require_device(t: torch.Tensor) -> None:
 
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def device_guard(t: torch.Tensor):
+    """Context that makes t's device current for the launch; free of charge
+    when it already is (the common case), which matters for the small operators
+    whose host path is as long as their kernel."""
+    if t.device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(t.device)
 
 
 def dtype_code(dt: torch.dtype) -> int:

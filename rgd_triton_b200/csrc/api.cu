@@ -1,6 +1,8 @@
 // Library-level entry points of librgd_b200: device check, status strings,
 // launch accounting.
 #include <atomic>
+#include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -25,9 +27,66 @@ int num_sms() {
     return v;
 }
 
+namespace {
+struct LaunchKey {
+    int dev;
+    const void *kernel;
+    uint64_t a, b;
+    bool operator==(const LaunchKey &o) const { return dev == o.dev && kernel == o.kernel && a == o.a && b == o.b; }
+};
+struct LaunchKeyHash {
+    size_t operator()(const LaunchKey &k) const {
+        uint64_t h = reinterpret_cast<uintptr_t>(k.kernel) * 0x9E3779B97F4A7C15ull;
+        h ^= (k.a + 0x632BE59BD9B4E019ull) + (h << 6) + (h >> 2);
+        h ^= (k.b + (uint64_t)k.dev * 0x100000001B3ull) + (h << 6) + (h >> 2);
+        return (size_t)h;
+    }
+};
+std::mutex g_launch_memo_mutex;
+std::unordered_map<LaunchKey, int, LaunchKeyHash> g_smem_memo, g_occ_memo;
+}  // namespace
+
+int ensure_dyn_smem(const void *kernel, size_t bytes) {
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return cuda_status(e);
+    const LaunchKey key{dev, kernel, (uint64_t)bytes, 0};
+    {
+        std::lock_guard<std::mutex> lock(g_launch_memo_mutex);
+        auto it = g_smem_memo.find(key);
+        if (it != g_smem_memo.end()) return it->second;
+    }
+    const int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (rc != RGD_OK) {
+        (void)cudaGetLastError();
+        return rc;                      // not memoised: the next call asks the driver again
+    }
+    std::lock_guard<std::mutex> lock(g_launch_memo_mutex);
+    g_smem_memo[key] = rc;
+    return rc;
+}
+
+int cached_occupancy(const void *kernel, int threads, size_t smem) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+    const LaunchKey key{dev, kernel, (uint64_t)threads, (uint64_t)smem};
+    {
+        std::lock_guard<std::mutex> lock(g_launch_memo_mutex);
+        auto it = g_occ_memo.find(key);
+        if (it != g_occ_memo.end()) return it->second;
+    }
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem) != cudaSuccess || n < 1) {
+        (void)cudaGetLastError();
+        n = 1;
+    }
+    std::lock_guard<std::mutex> lock(g_launch_memo_mutex);
+    g_occ_memo[key] = n;
+    return n;
+}
+
 }  // namespace rgd
 
-extern "C" int rgd_abi_version(void) { return 1; }
+extern "C" int rgd_abi_version(void) { return 2; }
 
 extern "C" int64_t rgd_launch_count(void) { return rgd::g_launches.load(std::memory_order_relaxed); }
 

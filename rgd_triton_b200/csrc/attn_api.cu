@@ -8,10 +8,11 @@ namespace attn {
 int general_fwd(const AttnParams &p, int dtype, cudaStream_t st);
 int general_bwd(const AttnParams &p, int dtype, cudaStream_t st);
 bool tmem_fwd_eligible(const AttnParams &p);
-int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st);
+int tmem_fwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st);
 int tmem_status_fetch();
 bool tmem_bwd_eligible(const AttnParams &p);
-int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st);
+int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st);
+int bounded_wait_selftest(int64_t limit_ns, cudaStream_t st);
 int64_t tmem_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq);
 }  // namespace attn
 }  // namespace rgd
@@ -72,15 +73,33 @@ void fill_common(AttnParams &p, const rgd_heads *q, const rgd_heads *k, const rg
     p.vec_v = dvec && heads_vec16(v);
 }
 
+void fill_fwd(AttnParams &p, const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
+              const rgd_heads *o, int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d, float scale, int causal) {
+    fill_common(p, q, k, v, bias, B, H, Tq, Tk, d, scale, causal);
+    p.out_o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_sn = o->stride_n;
+    p.vec_o = d % 8 == 0 && heads_vec16(o);
+}
+
+void fill_bwd(AttnParams &p, const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
+              const rgd_heads *o, const rgd_heads *d_o, const rgd_heads *dq, const rgd_heads *dk, const rgd_heads *dv,
+              int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d, float scale, int causal) {
+    fill_common(p, q, k, v, bias, B, H, Tq, Tk, d, scale, causal);
+    p.o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_sn = o->stride_n;
+    p.d_o = d_o->ptr; p.do_sb = d_o->stride_b; p.do_sh = d_o->stride_h; p.do_sn = d_o->stride_n;
+    p.dq = dq->ptr; p.dq_sb = dq->stride_b; p.dq_sh = dq->stride_h; p.dq_sn = dq->stride_n;
+    p.dk = dk->ptr; p.dk_sb = dk->stride_b; p.dk_sh = dk->stride_h; p.dk_sn = dk->stride_n;
+    p.dv = dv->ptr; p.dv_sb = dv->stride_b; p.dv_sh = dv->stride_h; p.dv_sn = dv->stride_n;
+    const bool dvec = d % 8 == 0;
+    p.vec_o = dvec && heads_vec16(o);
+    p.vec_do = dvec && heads_vec16(d_o);
+    p.vec_dq = dvec && heads_vec16(dq);
+    p.vec_dk = dvec && heads_vec16(dk);
+    p.vec_dv = dvec && heads_vec16(dv);
+}
+
 }  // namespace
 
 extern "C" int64_t rgd_attn_lse_rows(int64_t Tq) { return Tq < 0 ? RGD_E_INVALID : lse_rows(Tq); }
-
-extern "C" int rgd_attn_uses_tmem(int64_t Tq, int64_t Tk, int64_t d, int dtype, int64_t q_stride_n,
-                                  int64_t k_stride_n) {
-    return (d == 64 || d == 128) && Tq >= 1 && Tk >= 1 && (dtype == RGD_F16 || dtype == RGD_BF16) &&
-           q_stride_n % 8 == 0 && k_stride_n % 8 == 0;
-}
 
 extern "C" int rgd_device_status(void) {
     const int v = attn::tmem_status_fetch();
@@ -90,18 +109,28 @@ extern "C" int rgd_device_status(void) {
 
 extern "C" int rgd_attn_fwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
                             const rgd_heads *o, float *lse, int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d,
-                            float softmax_scale, int causal, int dtype, void *stream) {
+                            float softmax_scale, int causal, int dtype, rgd_cache *cache, void *stream) {
     if (int e = check_common(q, k, v, bias, B, H, Tq, Tk, d, dtype)) return e;
     if (!o) return RGD_E_NULL;
     const bool work = B > 0 && H > 0 && Tq > 0;
     if (work && (!lse || (d > 0 && !o->ptr))) return RGD_E_NULL;
     AttnParams p{};
-    fill_common(p, q, k, v, bias, B, H, Tq, Tk, d, softmax_scale, causal);
-    p.out_o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_sn = o->stride_n;
-    p.vec_o = d % 8 == 0 && heads_vec16(o);
+    fill_fwd(p, q, k, v, bias, o, B, H, Tq, Tk, d, softmax_scale, causal);
     p.lse = lse;
-    if (work && attn::tmem_fwd_eligible(p)) return attn::tmem_fwd(p, dtype, (cudaStream_t)stream);
+    if (work && attn::tmem_fwd_eligible(p)) {
+        const int rc = attn::tmem_fwd(p, dtype, cache, (cudaStream_t)stream);
+        if (rc != attn::TMEM_NOT_TAKEN) return rc;
+    }
     return attn::general_fwd(p, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int rgd_attn_fwd_uses_tmem(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_heads *o,
+                                      int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d, float softmax_scale,
+                                      int dtype) {
+    if (check_common(q, k, v, nullptr, B, H, Tq, Tk, d, dtype) != RGD_OK || !o) return 0;
+    AttnParams p{};
+    fill_fwd(p, q, k, v, nullptr, o, B, H, Tq, Tk, d, softmax_scale, 0);
+    return (B > 0 && H > 0 && Tq > 0 && attn::tmem_fwd_eligible(p)) ? 1 : 0;
 }
 
 extern "C" int64_t rgd_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d, int dtype) {
@@ -117,7 +146,7 @@ extern "C" int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_he
                             const rgd_heads *o, const float *lse, const rgd_heads *d_o, const rgd_heads *dq,
                             const rgd_heads *dk, const rgd_heads *dv, int64_t B, int64_t H, int64_t Tq, int64_t Tk,
                             int64_t d, float softmax_scale, int causal, int dtype, void *workspace,
-                            int64_t workspace_bytes, void *stream) {
+                            int64_t workspace_bytes, rgd_cache *cache, void *stream) {
     if (int e = check_common(q, k, v, bias, B, H, Tq, Tk, d, dtype)) return e;
     if (!o || !d_o || !dq || !dk || !dv) return RGD_E_NULL;
     const bool work = B > 0 && H > 0 && d > 0;
@@ -127,20 +156,27 @@ extern "C" int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_he
     if (need > 0 && (!workspace || workspace_bytes < need)) return RGD_E_WORKSPACE;
     if (need > 0 && !is_aligned(workspace, 16)) return RGD_E_STRIDE;
     AttnParams p{};
-    fill_common(p, q, k, v, bias, B, H, Tq, Tk, d, softmax_scale, causal);
-    p.o = o->ptr; p.o_sb = o->stride_b; p.o_sh = o->stride_h; p.o_sn = o->stride_n;
-    p.d_o = d_o->ptr; p.do_sb = d_o->stride_b; p.do_sh = d_o->stride_h; p.do_sn = d_o->stride_n;
-    p.dq = dq->ptr; p.dq_sb = dq->stride_b; p.dq_sh = dq->stride_h; p.dq_sn = dq->stride_n;
-    p.dk = dk->ptr; p.dk_sb = dk->stride_b; p.dk_sh = dk->stride_h; p.dk_sn = dk->stride_n;
-    p.dv = dv->ptr; p.dv_sb = dv->stride_b; p.dv_sh = dv->stride_h; p.dv_sn = dv->stride_n;
-    const bool dvec = d % 8 == 0;
-    p.vec_o = dvec && heads_vec16(o);
-    p.vec_do = dvec && heads_vec16(d_o);
-    p.vec_dq = dvec && heads_vec16(dq);
-    p.vec_dk = dvec && heads_vec16(dk);
-    p.vec_dv = dvec && heads_vec16(dv);
+    fill_bwd(p, q, k, v, bias, o, d_o, dq, dk, dv, B, H, Tq, Tk, d, softmax_scale, causal);
     p.lse = const_cast<float *>(lse);
     p.delta = reinterpret_cast<float *>(workspace);
-    if (work && attn::tmem_bwd_eligible(p)) return attn::tmem_bwd(p, dtype, (cudaStream_t)stream);
+    if (work && attn::tmem_bwd_eligible(p)) {
+        const int rc = attn::tmem_bwd(p, dtype, cache, (cudaStream_t)stream);
+        if (rc != attn::TMEM_NOT_TAKEN) return rc;
+    }
     return attn::general_bwd(p, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int rgd_attn_bwd_uses_tmem(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_heads *o,
+                                      const rgd_heads *d_o, const rgd_heads *dq, const rgd_heads *dk,
+                                      const rgd_heads *dv, int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d,
+                                      int dtype) {
+    if (check_common(q, k, v, nullptr, B, H, Tq, Tk, d, dtype) != RGD_OK || !o || !d_o || !dq || !dk || !dv) return 0;
+    AttnParams p{};
+    fill_bwd(p, q, k, v, nullptr, o, d_o, dq, dk, dv, B, H, Tq, Tk, d, 1.f, 0);
+    return (B > 0 && H > 0 && d > 0 && attn::tmem_bwd_eligible(p)) ? 1 : 0;
+}
+
+extern "C" int rgd_selftest_bounded_wait(int64_t limit_ns, void *stream) {
+    if (limit_ns < 1000 || limit_ns > 100000000) return RGD_E_INVALID;      // 1 us .. 100 ms
+    return attn::bounded_wait_selftest(limit_ns, (cudaStream_t)stream);
 }

@@ -33,7 +33,7 @@ using namespace rgd::sm100;
 
 int *tmem_status_ptr();   // attn_fwd_sm100.cu
 bool bias_tma_ok(const AttnParams &p);
-int encode_bias_map(CUtensorMap *out, const AttnParams &p, bool bf16);
+int encode_bias_map(rgd_cache *cache, CUtensorMap *out, const AttnParams &p, bool bf16);
 
 constexpr int BWD_THREADS = 320;
 constexpr int DKDV_SUB_THREADS = 384;   // 8 compute warps, TMA producer, three MMA issuers
@@ -1201,16 +1201,17 @@ int64_t tmem_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq) {
 
 bool tmem_bwd_eligible(const AttnParams &p) {
     return (p.d == 64 || p.d == 128) && p.Tq >= 1 && p.Tk >= 1 && p.vec_q && p.vec_k && p.vec_v && p.vec_o && p.vec_do &&
-           p.vec_dq && p.vec_dk && p.vec_dv;
+           p.vec_dq && p.vec_dk && p.vec_dv && heads_map_encodable(p.q, p.B, p.H, p.Tq, p.q_sb, p.q_sh, p.q_sn) &&
+           heads_map_encodable(p.k, p.B, p.H, p.Tk, p.k_sb, p.k_sh, p.k_sn) &&
+           heads_map_encodable(p.v, p.B, p.H, p.Tk, p.v_sb, p.v_sh, p.v_sn) &&
+           heads_map_encodable(p.d_o, p.B, p.H, p.Tq, p.do_sb, p.do_sh, p.do_sn);
 }
 
 template <int D, bool BF16, bool DKDV, int BIAS>
 static int launch_bwd_one(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
     constexpr int BSTAGES = BIAS == 2 ? (D == 64 ? 2 : 1) : 0;
     const size_t smem = sizeof(BwdTmaSmem<D, BSTAGES>) + 1024;
-    if (int e = cuda_status(cudaFuncSetAttribute(attn_bwd_tmem<D, BF16, DKDV, BIAS>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
-        return e;
+    if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_tmem<D, BF16, DKDV, BIAS>), smem)) return e;
     dim3 grid(nblocks, BH);
     attn_bwd_tmem<D, BF16, DKDV, BIAS><<<grid, BWD_THREADS, smem, st>>>(bp);
     count_launch();
@@ -1227,9 +1228,7 @@ static int launch_bwd_tmem(const BwdTmaParams &bp, int nblocks, int BH, cudaStre
 template <int D, bool BF16>
 static int launch_dkdv_sub(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
     const size_t smem = sizeof(DkdvSubSmem<D>) + 1024;
-    if (int e = cuda_status(cudaFuncSetAttribute(attn_bwd_dkdv_sub<D, BF16>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
-        return e;
+    if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dkdv_sub<D, BF16>), smem)) return e;
     dim3 grid(nblocks, BH);
     attn_bwd_dkdv_sub<D, BF16><<<grid, DKDV_SUB_THREADS, smem, st>>>(bp);
     count_launch();
@@ -1250,9 +1249,7 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     bp.out2 = nullptr;
     if (bp.bias_kind == RGD_BIAS_NONE) {
         const size_t smem = sizeof(DqPipeSmem<D>) + 1024;
-        if (int e = cuda_status(cudaFuncSetAttribute(attn_bwd_dq_pipe<D, BF16>,
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
-            return e;
+        if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dq_pipe<D, BF16>), smem)) return e;
         dim3 grid((p.Tq + BT - 1) / BT, BH);
         attn_bwd_dq_pipe<D, BF16><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp);
         count_launch();
@@ -1261,12 +1258,20 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     return launch_bwd_tmem<D, BF16, false>(bp, (p.Tq + BT - 1) / BT, BH, st);
 }
 
-// p.delta points at the caller's workspace (tmem_bwd_workspace_bytes).
-int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st) {
+// p.delta points at the caller's workspace (tmem_bwd_workspace_bytes).  Returns TMEM_NOT_TAKEN
+// (nothing launched) when a descriptor cannot be encoded after all.
+int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st) {
     BwdTmaParams bp{};
     const bool bf16 = dtype == RGD_BF16;
     const int Tq128 = (p.Tq + 127) / 128 * 128;
     float *lse2 = p.delta, *delta_s = p.delta + (int64_t)p.B * p.H * Tq128;
+    if (encode_heads_map_cached(cache, &bp.mq, p.q, p.B, p.H, p.Tq, p.d, p.q_sb, p.q_sh, p.q_sn, 64, BT, bf16) ||
+        encode_heads_map_cached(cache, &bp.mk, p.k, p.B, p.H, p.Tk, p.d, p.k_sb, p.k_sh, p.k_sn, 64, BT, bf16) ||
+        encode_heads_map_cached(cache, &bp.mv, p.v, p.B, p.H, p.Tk, p.d, p.v_sb, p.v_sh, p.v_sn, 64, BT, bf16) ||
+        encode_heads_map_cached(cache, &bp.mdo, p.d_o, p.B, p.H, p.Tq, p.d, p.do_sb, p.do_sh, p.do_sn, 64, BT, bf16))
+        return TMEM_NOT_TAKEN;
+    bp.status = tmem_status_ptr();
+    if (!bp.status) return RGD_E_DEVICE;
     {
         const int rows_per_cta = 256 / (p.d / 8);
         dim3 grid((Tq128 + rows_per_cta - 1) / rows_per_cta, p.B * p.H);
@@ -1275,10 +1280,6 @@ int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st) {
         count_launch();
         if (int e = check_launch()) return e;
     }
-    if (int e = encode_heads_map(&bp.mq, p.q, p.B, p.H, p.Tq, p.d, p.q_sb, p.q_sh, p.q_sn, 64, BT, bf16)) return e;
-    if (int e = encode_heads_map(&bp.mk, p.k, p.B, p.H, p.Tk, p.d, p.k_sb, p.k_sh, p.k_sn, 64, BT, bf16)) return e;
-    if (int e = encode_heads_map(&bp.mv, p.v, p.B, p.H, p.Tk, p.d, p.v_sb, p.v_sh, p.v_sn, 64, BT, bf16)) return e;
-    if (int e = encode_heads_map(&bp.mdo, p.d_o, p.B, p.H, p.Tq, p.d, p.do_sb, p.do_sh, p.do_sn, 64, BT, bf16)) return e;
     bp.bias = p.bias; bp.b_sb = p.b_sb; bp.b_sh = p.b_sh; bp.b_sq = p.b_sq;
     bp.bias_kind = p.bias_kind; bp.bias_f32 = p.bias_f32;
     // bias_vec: 0 scalar loads, 1 rows are 16-byte addressable (vector loads), 2 staged through TMA
@@ -1286,7 +1287,7 @@ int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st) {
     if (p.bias_kind != RGD_BIAS_NONE && !p.bias_f32 && is_aligned(p.bias, 16) && p.b_sb % 8 == 0 && p.b_sh % 8 == 0 &&
         (p.bias_kind != RGD_BIAS_MATRIX || p.b_sq % 8 == 0))
         bp.bias_vec = 1;
-    if (bias_tma_ok(p) && encode_bias_map(&bp.mbias, p, bf16) == RGD_OK) {
+    if (bias_tma_ok(p) && encode_bias_map(cache, &bp.mbias, p, bf16) == RGD_OK) {
         bp.bias_vec = 2;
         bp.bias_h0 = p.b_sh == 0;
         bp.bias_b0 = p.b_sb == 0;
@@ -1294,8 +1295,6 @@ int tmem_bwd(const AttnParams &p, int dtype, cudaStream_t st) {
     bp.lse2 = lse2; bp.delta_s = delta_s;
     bp.H = p.H; bp.Tq = p.Tq; bp.Tk = p.Tk; bp.Tq128 = Tq128; bp.causal = p.causal;
     bp.scale = p.scale; bp.scale_log2 = p.scale * LOG2E;
-    bp.status = tmem_status_ptr();
-    if (!bp.status) return RGD_E_DEVICE;
     if (p.d == 128) return bf16 ? bwd_both<128, true>(bp, p, st) : bwd_both<128, false>(bp, p, st);
     return bf16 ? bwd_both<64, true>(bp, p, st) : bwd_both<64, false>(bp, p, st);
 }

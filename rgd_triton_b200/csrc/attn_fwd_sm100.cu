@@ -26,6 +26,8 @@
 // RGD_E_TIMEOUT.
 #include <math.h>
 
+#include <mutex>
+
 #include "attn_mma.cuh"
 #include "sm100_prims.cuh"
 
@@ -511,9 +513,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
 // Device address of the status word on the current device (the symbol has one
 // instance per device, so the address is looked up per device and cached).
 int *tmem_status_ptr() {
+    static std::mutex mu;
     static int *cache[64] = {nullptr};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
     if (cache[dev] == nullptr) {
         void *ptr = nullptr;
         if (cudaGetSymbolAddress(&ptr, g_tmem_status) != cudaSuccess) {
@@ -525,17 +529,26 @@ int *tmem_status_ptr() {
     return cache[dev];
 }
 
+// Views the TMA descriptors can describe: 16-byte addressable rows, and for every dimension
+// of extent > 1 a positive stride (a tensor expanded over batch or heads has stride 0 there
+// and takes the general kernels).
+static bool tma_view_ok(const void *ptr, int B, int H, int T, int64_t sb, int64_t sh, int64_t sn) {
+    return heads_map_encodable(ptr, B, H, T, sb, sh, sn);
+}
+
 bool tmem_fwd_eligible(const AttnParams &p) {
-    return (p.d == 64 || p.d == 128) && p.Tq >= 1 && p.Tk >= 1 && p.vec_q && p.vec_k && p.vec_v && p.vec_o;
+    // The mask-free fast path takes the block maximum before scaling, which needs scale > 0.
+    return (p.d == 64 || p.d == 128) && p.Tq >= 1 && p.Tk >= 1 && p.scale > 0.f && p.vec_q && p.vec_k && p.vec_v &&
+           p.vec_o && tma_view_ok(p.q, p.B, p.H, p.Tq, p.q_sb, p.q_sh, p.q_sn) &&
+           tma_view_ok(p.k, p.B, p.H, p.Tk, p.k_sb, p.k_sh, p.k_sn) &&
+           tma_view_ok(p.v, p.B, p.H, p.Tk, p.v_sb, p.v_sh, p.v_sn);
 }
 
 template <int D, bool BF16, int BIAS>
 static int launch_fwd_one(const FwdTmaParams &fp, int Tq, int BH, cudaStream_t st) {
     constexpr int NT = (BIAS == 2 && D == 128) ? 1 : 2;
     const size_t smem = sizeof(FwdTmaSmem<D, NT, BIAS == 2>) + 1024;
-    if (int e = cuda_status(cudaFuncSetAttribute(attn_fwd_tmem<D, BF16, BIAS>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
-        return e;
+    if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_fwd_tmem<D, BF16, BIAS>), smem)) return e;
     dim3 grid((Tq + NT * TM - 1) / (NT * TM), BH);
     attn_fwd_tmem<D, BF16, BIAS><<<grid, FWD_THREADS, smem, st>>>(fp);
     count_launch();
@@ -558,17 +571,20 @@ bool bias_tma_ok(const AttnParams &p) {
 }
 
 // (Tk, Tq, H or 1, B or 1) map over the bias; broadcast dims (stride 0) become extent 1.
-int encode_bias_map(CUtensorMap *out, const AttnParams &p, bool bf16) {
+int encode_bias_map(rgd_cache *cache, CUtensorMap *out, const AttnParams &p, bool bf16) {
     const int64_t Hb = p.b_sh == 0 ? 1 : p.H, Bb = p.b_sb == 0 ? 1 : p.B;
-    return encode_heads_map(out, p.bias, Bb, Hb, p.Tq, p.Tk, p.b_sb, p.b_sh, p.b_sq, 64, TM, bf16);
+    return encode_heads_map_cached(cache, out, p.bias, Bb, Hb, p.Tq, p.Tk, p.b_sb, p.b_sh, p.b_sq, 64, TM, bf16);
 }
 
-int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
+// Returns TMEM_NOT_TAKEN (nothing launched) when a descriptor cannot be encoded after all; the
+// caller then runs the general kernels.
+int tmem_fwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st) {
     FwdTmaParams fp{};
     const bool bf16 = dtype == RGD_BF16;
-    if (int e = encode_heads_map(&fp.mq, p.q, p.B, p.H, p.Tq, p.d, p.q_sb, p.q_sh, p.q_sn, 64, TM, bf16)) return e;
-    if (int e = encode_heads_map(&fp.mk, p.k, p.B, p.H, p.Tk, p.d, p.k_sb, p.k_sh, p.k_sn, 64, TN, bf16)) return e;
-    if (int e = encode_heads_map(&fp.mv, p.v, p.B, p.H, p.Tk, p.d, p.v_sb, p.v_sh, p.v_sn, 64, TN, bf16)) return e;
+    if (encode_heads_map_cached(cache, &fp.mq, p.q, p.B, p.H, p.Tq, p.d, p.q_sb, p.q_sh, p.q_sn, 64, TM, bf16) ||
+        encode_heads_map_cached(cache, &fp.mk, p.k, p.B, p.H, p.Tk, p.d, p.k_sb, p.k_sh, p.k_sn, 64, TN, bf16) ||
+        encode_heads_map_cached(cache, &fp.mv, p.v, p.B, p.H, p.Tk, p.d, p.v_sb, p.v_sh, p.v_sn, 64, TN, bf16))
+        return TMEM_NOT_TAKEN;
     fp.o = p.out_o; fp.o_sb = p.o_sb; fp.o_sh = p.o_sh; fp.o_sn = p.o_sn;
     fp.bias = p.bias; fp.b_sb = p.b_sb; fp.b_sh = p.b_sh; fp.b_sq = p.b_sq;
     fp.bias_kind = p.bias_kind; fp.bias_f32 = p.bias_f32;
@@ -576,7 +592,7 @@ int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
     fp.bias_vec = p.bias_kind != RGD_BIAS_NONE && is_aligned(p.bias, 16) && p.b_sb % bel == 0 && p.b_sh % bel == 0 &&
                   (p.bias_kind != RGD_BIAS_MATRIX || p.b_sq % bel == 0);
     int bias_mode = p.bias_kind == RGD_BIAS_NONE ? 0 : 1;
-    if (bias_mode == 1 && bias_tma_ok(p) && encode_bias_map(&fp.mbias, p, bf16) == RGD_OK) {
+    if (bias_mode == 1 && bias_tma_ok(p) && encode_bias_map(cache, &fp.mbias, p, bf16) == RGD_OK) {
         bias_mode = 2;
         fp.bias_h0 = p.b_sh == 0;
         fp.bias_b0 = p.b_sb == 0;
@@ -590,6 +606,27 @@ int tmem_fwd(const AttnParams &p, int dtype, cudaStream_t st) {
     if (p.d == 128)
         return bf16 ? launch_fwd_tmem<128, true>(fp, bias_mode, p.Tq, BH, st) : launch_fwd_tmem<128, false>(fp, bias_mode, p.Tq, BH, st);
     return bf16 ? launch_fwd_tmem<64, true>(fp, bias_mode, p.Tq, BH, st) : launch_fwd_tmem<64, false>(fp, bias_mode, p.Tq, BH, st);
+}
+
+// Exercises the give-up path of the bounded waits without any broken pipeline: one thread waits,
+// with a short limit, on an mbarrier that nothing ever arrives at.  The wait runs out, records
+// its site code in the status word and the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(int *status, unsigned long long limit_ns, int *gave_up) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+        const bool completed = mbar_wait(&bar, 0, status, 99, limit_ns);
+        if (gave_up) *gave_up = completed ? 0 : 1;
+    }
+}
+
+int bounded_wait_selftest(int64_t limit_ns, cudaStream_t st) {
+    int *status = tmem_status_ptr();
+    if (!status) return RGD_E_DEVICE;
+    bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(status, (unsigned long long)limit_ns, nullptr);
+    count_launch();
+    return check_launch();
 }
 
 // Read and clear the sticky device status word of the tensor-memory kernels

@@ -343,7 +343,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_q_general(const __grid_cons
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
     if (bytes > 48 * 1024)
-        return cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        return ensure_dyn_smem(reinterpret_cast<const void *>(kernel), bytes);
     return RGD_OK;
 }
 

@@ -14,6 +14,8 @@ constexpr int BN = 64;          // key rows per tile
 constexpr int NTHREADS = 128;   // 4 warps, 16 tile rows each
 constexpr int PAD = 8;          // 16-byte row padding: conflict-free ldmatrix
 constexpr float LOG2E = 1.4426950408889634f;
+// Internal answer of the tensor-memory entry points: nothing was launched, run the general kernels.
+constexpr int TMEM_NOT_TAKEN = -1000;
 
 struct AttnParams {
     const void *q, *k, *v, *o, *d_o;   // (B,H,T,d) views; o / d_o read in the backward

@@ -16,6 +16,12 @@ namespace rgd {
 void count_launch();                    // defined in api.cu
 int  check_launch();                    // cudaGetLastError -> status code
 int  num_sms();                         // SM count of the current device (cached)
+// Opt a kernel in to `bytes` of dynamic shared memory.  The driver call is made once per
+// (device, kernel, size); later launches only look the answer up.
+int  ensure_dyn_smem(const void *kernel, size_t bytes);
+// cudaOccupancyMaxActiveBlocksPerMultiprocessor, memoised per (device, kernel, threads,
+// shared memory).  Never returns less than 1.
+int  cached_occupancy(const void *kernel, int threads, size_t smem);
 
 static inline int cuda_status(cudaError_t e) {
     return e == cudaSuccess ? RGD_OK : RGD_E_CUDA_BASE + (int)e;

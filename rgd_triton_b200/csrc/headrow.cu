@@ -716,15 +716,10 @@ int launch_pipelined(const HeadParams &p, int64_t tiles, cudaStream_t st) {
     const size_t smem = (size_t)PIPE_STAGES * SLOTS * HEAD_THREADS * 16;
     auto kernel = head_kernel_pipelined<T, TP, VPT, OP>;
     if (smem > 32 * 1024)   // static shared memory counts towards the 48 KB default limit too
-        if (int e = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
-            return e;
+        if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(kernel), smem)) return e;
     // Persistent grid, never more CTAs than tiles:
     // one resident wave of persistent CTAs
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, HEAD_THREADS, smem) != cudaSuccess || per_sm < 1) {
-        (void)cudaGetLastError();
-        per_sm = 1;
-    }
+    const int per_sm = cached_occupancy(reinterpret_cast<const void *>(kernel), HEAD_THREADS, smem);
     int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > tiles) grid = tiles;
     kernel<<<(unsigned)grid, HEAD_THREADS, smem, st>>>(p);
@@ -740,14 +735,9 @@ int launch_flat(const HeadParams &p, int64_t tiles, cudaStream_t st) {
     const size_t smem = (size_t)PIPE_STAGES * SLOTS * HEAD_THREADS * 16;
     auto kernel = head_kernel_flat<T, TP, VPT, RPT, OP, D>;
     if (smem > 32 * 1024)
-        if (int e = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
-            return e;
+        if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(kernel), smem)) return e;
     // one resident wave of persistent CTAs
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, HEAD_THREADS, smem) != cudaSuccess || per_sm < 1) {
-        (void)cudaGetLastError();
-        per_sm = 1;
-    }
+    const int per_sm = cached_occupancy(reinterpret_cast<const void *>(kernel), HEAD_THREADS, smem);
     int64_t grid = (int64_t)num_sms() * per_sm;
     if (grid > tiles) grid = tiles;
     kernel<<<(unsigned)grid, HEAD_THREADS, smem, st>>>(p);

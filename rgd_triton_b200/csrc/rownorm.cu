@@ -624,12 +624,10 @@ template <typename T, int OP>
 int lean_rows_occupancy_t(const LeanGeom &g) {
     int n = 0;
     const int rc = with_lean_kernel<T, OP>(g, [&](auto kernel, int threads) {
-        return cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) == cudaSuccess ? 0 : 1;
+        n = cached_occupancy(reinterpret_cast<const void *>(kernel), threads, 0);
+        return 0;
     });
-    if (rc != 0 || n < 1) {
-        (void)cudaGetLastError();
-        n = 1;
-    }
+    if (rc != 0 || n < 1) n = 1;
     return n;
 }
 template <int OP>
@@ -724,8 +722,7 @@ int launch_row_kernel(const RowParams &p, int grid, cudaStream_t st) {
     auto kernel = row_kernel<T, VE, VPT, OP, PIPE>;
     const size_t smem = PIPE ? row_pipe_smem<OP>(VPT) : 0;
     if (smem > 32 * 1024)   // static shared memory counts towards the 48 KB default limit too
-        if (int e = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
-            return e;
+        if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(kernel), smem)) return e;
     kernel<<<grid, ROW_THREADS, smem, st>>>(p);
     count_launch();
     return check_launch();
@@ -737,13 +734,8 @@ int row_kernel_occupancy() {
     auto kernel = row_kernel<T, VE, VPT, OP, PIPE>;
     const size_t smem = PIPE ? row_pipe_smem<OP>(VPT) : 0;
     if (smem > 32 * 1024)
-        (void)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, ROW_THREADS, smem) != cudaSuccess || n < 1) {
-        (void)cudaGetLastError();
-        n = 1;
-    }
-    return n;
+        (void)ensure_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
+    return cached_occupancy(reinterpret_cast<const void *>(kernel), ROW_THREADS, smem);
 }
 
 template <typename T, int OP>
@@ -895,6 +887,13 @@ int run_rows(const RowCall &c, float *dw_part0, float *dw_part1, int budget, cud
     const LeanGeom lg = lean_geometry<OP>(nvec);
     bool lean_rows = pl.ve > 1 && lg.ok && cmax % pl.ve == 0;
     for (int s = 0; s < c.nstreams; ++s) lean_rows = lean_rows && (c.C[s] == cmax || c.N[s] == 0);
+    // The lean kernel reads the weight with 16-byte loads: its address and batch stride
+    // must allow that; any other weight view takes the pipelined kernel (scalar weight loads).
+    if (c.w) {
+        const int wvec = 16 / dtype_size(c.w_dtype);
+        for (int s = 0; s < c.nstreams; ++s)
+            lean_rows = lean_rows && (c.N[s] == 0 || (is_aligned(c.w[s], 16) && c.wsb[s] % wvec == 0));
+    }
     int rows_per_cta = ROW_THREADS / pl.tpr;
     if (lean_rows) {
         pl.tpr = lg.tpr;
@@ -1098,9 +1097,13 @@ extern "C" int rgd_rmsnorm_bwd_static(int nstreams, const rgd_rows *x, const voi
                                       void *const *dw, const int *dw_per_batch, const int64_t *N,
                                       const int64_t *C, int64_t B, float eps, int x_dtype, int w_dtype,
                                       void *stream) {
-    if (nstreams < 1 || nstreams > 2 || !N || !C || B < 0) return RGD_E_INVALID;
+    // Same argument checks, in the same order, as the workspace form: a bad size or a null
+    // pointer is reported as such before anything is sized or looked up.
+    RowCall c{nstreams, x, dy, dx, w, w_stride_b, N, C, B, eps, x_dtype, w_dtype};
+    if (int e = validate_rows(c, true, true)) return e;
+    if (!dw || !dw_per_batch) return RGD_E_NULL;
     const int64_t need = rgd_rmsnorm_bwd_workspace_bytes(nstreams, N, C, B);
-    if (need < 0) return (int)need;
+    if (need < 0) return RGD_E_INVALID;
     // Sizes whose partial rows do not fit the fixed array are refused, not truncated.
     if (need > (int64_t)RGD_RMSNORM_BWD_STATIC_SCRATCH_BYTES) return RGD_E_WORKSPACE;
     void *scratch = nullptr;

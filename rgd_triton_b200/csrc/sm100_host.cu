@@ -2,8 +2,29 @@
 // the driver entry point (no link-time dependency on libcuda) and the sticky
 // device status word.
 #include <mutex>
+#include <new>
+#include <string.h>
+#include <vector>
 
 #include "sm100_prims.cuh"
+
+// A launch-plan cache: the tensor-map descriptors of the attention calls it has seen, keyed on
+// everything that goes into a descriptor (base pointer, extents, strides, box, element type).
+// A call whose tensors moved or changed shape simply misses and encodes afresh, so a stale
+// entry can never be launched with.  Entries are few (a training step reuses the same handful
+// of buffers), so a small array with round-robin replacement is enough.
+struct rgd_cache {
+    struct Entry {
+        const void *base;
+        int64_t v[10];           // B, H, T, d, stride_b, stride_h, stride_n, box_d, box_t, bf16
+        CUtensorMap map;
+    };
+    static constexpr size_t CAPACITY = 64;
+    std::mutex mu;
+    std::vector<Entry> entries;
+    size_t next = 0;
+    int64_t hits = 0, misses = 0;
+};
 
 namespace rgd {
 namespace sm100 {
@@ -25,6 +46,43 @@ static EncodeTiledFn encoder() {
             (void)cudaGetLastError();
     });
     return fn;
+}
+
+bool heads_map_encodable(const void *base, int64_t B, int64_t H, int64_t T, int64_t stride_b, int64_t stride_h,
+                         int64_t stride_n) {
+    if (!is_aligned(base, 16)) return false;
+    const int64_t limit = (1ll << 40) / 2;      // descriptor strides are below 2^40 bytes
+    auto ok = [&](int64_t extent, int64_t stride) {
+        return extent <= 1 || (stride > 0 && stride % 8 == 0 && stride < limit);
+    };
+    return ok(T, stride_n) && ok(H, stride_h) && ok(B, stride_b);
+}
+
+int encode_heads_map_cached(rgd_cache *cache, CUtensorMap *out, const void *base, int64_t B, int64_t H, int64_t T,
+                            int64_t d, int64_t stride_b, int64_t stride_h, int64_t stride_n, int box_d, int box_t,
+                            bool bf16) {
+    if (!cache) return encode_heads_map(out, base, B, H, T, d, stride_b, stride_h, stride_n, box_d, box_t, bf16);
+    const int64_t v[10] = {B, H, T, d, stride_b, stride_h, stride_n, box_d, box_t, bf16 ? 1 : 0};
+    std::lock_guard<std::mutex> lock(cache->mu);
+    for (const rgd_cache::Entry &e : cache->entries)
+        if (e.base == base && memcmp(e.v, v, sizeof(v)) == 0) {
+            *out = e.map;
+            ++cache->hits;
+            return RGD_OK;
+        }
+    ++cache->misses;
+    if (int rc = encode_heads_map(out, base, B, H, T, d, stride_b, stride_h, stride_n, box_d, box_t, bf16)) return rc;
+    rgd_cache::Entry e;
+    e.base = base;
+    memcpy(e.v, v, sizeof(v));
+    e.map = *out;
+    if (cache->entries.size() < rgd_cache::CAPACITY) {
+        cache->entries.push_back(e);
+    } else {
+        cache->entries[cache->next] = e;
+        cache->next = (cache->next + 1) % rgd_cache::CAPACITY;
+    }
+    return RGD_OK;
 }
 
 int encode_heads_map(CUtensorMap *out, const void *base, int64_t B, int64_t H, int64_t T, int64_t d,
@@ -51,3 +109,16 @@ int encode_heads_map(CUtensorMap *out, const void *base, int64_t B, int64_t H, i
 
 }  // namespace sm100
 }  // namespace rgd
+
+extern "C" rgd_cache *rgd_cache_create(void) { return new (std::nothrow) rgd_cache(); }
+
+extern "C" void rgd_cache_destroy(rgd_cache *cache) { delete cache; }
+
+extern "C" int rgd_cache_stats(rgd_cache *cache, int64_t *hits, int64_t *misses, int64_t *entries) {
+    if (!cache) return RGD_E_NULL;
+    std::lock_guard<std::mutex> lock(cache->mu);
+    if (hits) *hits = cache->hits;
+    if (misses) *misses = cache->misses;
+    if (entries) *entries = (int64_t)cache->entries.size();
+    return RGD_OK;
+}

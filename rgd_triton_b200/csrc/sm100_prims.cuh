@@ -55,14 +55,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Wait for the phase with the given parity to complete.  Returns false when
 // the wait was abandoned (time limit, or another thread already flagged an
 // error in *status); `code` identifies the waiting site.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 0u) {
             if (*reinterpret_cast<volatile int *>(status) != 0) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 atomicCAS(status, 0, code);
                 return false;
             }
@@ -225,6 +226,15 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
 // [box_d, box_t, 1, 1].  Returns RGD_OK or a status code.
 int encode_heads_map(CUtensorMap *out, const void *base, int64_t B, int64_t H, int64_t T, int64_t d,
                      int64_t stride_b, int64_t stride_h, int64_t stride_n, int box_d, int box_t, bool bf16);
+// Whether encode_heads_map accepts this view: 16-byte aligned base, and for every dimension of
+// extent > 1 a positive stride that is a multiple of 16 bytes and below the descriptor's limit.
+bool heads_map_encodable(const void *base, int64_t B, int64_t H, int64_t T, int64_t stride_b, int64_t stride_h,
+                         int64_t stride_n);
+// The same through a launch-plan cache (rgd_cache, may be null): a descriptor already encoded
+// for exactly these arguments is copied out of the cache instead of being re-encoded.
+int encode_heads_map_cached(rgd_cache *cache, CUtensorMap *out, const void *base, int64_t B, int64_t H, int64_t T,
+                            int64_t d, int64_t stride_b, int64_t stride_h, int64_t stride_n, int box_d, int box_t,
+                            bool bf16);
 
 }  // namespace sm100
 }  // namespace rgd

@@ -80,6 +80,12 @@ def _cache_put(cache, slot: str, key) -> None:
         setattr(cache, slot, key)
 
 
+def _native_cache(cache):
+    """The library's launch-plan cache behind a module cache (None without one)."""
+    native = getattr(cache, "native", None)
+    return native() if native is not None else None
+
+
 # --------------------------------------------------------------------------
 # Row L2 normalise
 # --------------------------------------------------------------------------
@@ -103,7 +109,7 @@ def _l2_launch(xs, dys, outs, eps: float, bwd: bool) -> None:
     Cc = _i64(*[t.shape[2] for t in xs])
     B = xs[0].shape[0]
     dt = _lib.dtype_code(xs[0].dtype)
-    with torch.cuda.device(xs[0].device):
+    with _lib.device_guard(xs[0]):
         if bwd:
             da = (Rows * n)(*[_lib.rows(t) for t in dys])
             code = lib.rgd_l2norm_bwd(n, xa, da, oa, N, Cc, B, float(eps), dt, _lib.stream_ptr())
@@ -217,7 +223,7 @@ def _rms_fwd(xs, ws, eps):
     wsb = _i64(*[p[1] for p in preps])
     N = _i64(*[t.shape[1] for t in xs])
     Cc = _i64(*[t.shape[2] for t in xs])
-    with torch.cuda.device(xs[0].device):
+    with _lib.device_guard(xs[0]):
         code = lib.rgd_rmsnorm_fwd(n, xa, wp, wsb, ya, N, Cc, xs[0].shape[0], float(eps),
                                    _lib.dtype_code(xs[0].dtype), _lib.dtype_code(preps[0][0].dtype),
                                    _lib.stream_ptr())
@@ -237,7 +243,7 @@ def _rms_bwd(xs, ws, dys, eps):
         dws.append(torch.empty(shape, dtype=w.dtype, device=w.device))
     N = _i64(*[t.shape[1] for t in xs])
     Cc = _i64(*[t.shape[2] for t in xs])
-    with torch.cuda.device(xs[0].device):
+    with _lib.device_guard(xs[0]):
         nbytes = lib.rgd_rmsnorm_bwd_workspace_bytes(n, N, Cc, B)
         _require(nbytes >= 0, "rmsnorm_bwd: bad sizes")
         work = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=xs[0].device)
@@ -377,7 +383,7 @@ def _ln_launch(q, k, dqo, dko, qo, ko, heads_second, eps, bwd):
     B, H, nq, nk, d = _head_dims(q, k, heads_second)
     hv = lambda t: C.byref(_lib.heads(t, heads_second))
     dt = _lib.dtype_code(q.dtype)
-    with torch.cuda.device(q.device):
+    with _lib.device_guard(q):
         if bwd:
             code = lib.rgd_headln_bwd(hv(q), hv(k), hv(dqo), hv(dko), hv(qo), hv(ko), B, H, nq, nk, d, float(eps), dt,
                                       _lib.stream_ptr())
@@ -427,7 +433,7 @@ def _rope_launch(q, k, pos, qo, ko, cuts, heads_second, transposed):
     lib = _lib.load()
     B, H, nq, nk, d = _head_dims(q, k, heads_second)
     hv = lambda t: C.byref(_lib.heads(t, heads_second))
-    with torch.cuda.device(q.device):
+    with _lib.device_guard(q):
         code = lib.rgd_rope(hv(q), hv(k), pos.data_ptr(), pos.stride(0), pos.stride(1), hv(qo), hv(ko),
                             B, H, nq, nk, d, pos.shape[1], pos.shape[2], cuts[0], cuts[1],
                             1 if transposed else 0, _lib.dtype_code(q.dtype), _lib.dtype_code(pos.dtype),
@@ -488,7 +494,7 @@ def _lnrope_launch(q, k, dqo, dko, pos, qo, ko, cuts, heads_second, eps, bwd):
     hv = lambda t: C.byref(_lib.heads(t, heads_second))
     tail = (B, H, nq, nk, d, pos.shape[1], pos.shape[2], cuts[0], cuts[1], float(eps),
             _lib.dtype_code(q.dtype), _lib.dtype_code(pos.dtype), _lib.stream_ptr())
-    with torch.cuda.device(q.device):
+    with _lib.device_guard(q):
         if bwd:
             code = lib.rgd_lnrope_bwd(hv(q), hv(k), hv(dqo), hv(dko), pos.data_ptr(), pos.stride(0), pos.stride(1),
                                       hv(qo), hv(ko), *tail)
@@ -598,11 +604,12 @@ class FlashAttnFunc(torch.autograd.Function):
         bias_t, bias_s = _prep_bias(bias, q, seqlen_q, seqlen_k)
         o = torch.empty_like(q)
         lse = torch.empty((batch, nheads, lib.rgd_attn_lse_rows(seqlen_q)), device=q.device, dtype=torch.float32)
-        with torch.cuda.device(q.device):
+        with _lib.device_guard(q):
             code = lib.rgd_attn_fwd(C.byref(_attn_heads(q)), C.byref(_attn_heads(k)), C.byref(_attn_heads(v)),
                                     C.byref(bias_s), C.byref(_attn_heads(o)), lse.data_ptr(),
                                     batch, nheads, seqlen_q, seqlen_k, d, float(softmax_scale),
-                                    1 if causal else 0, _lib.dtype_code(q.dtype), _lib.stream_ptr())
+                                    1 if causal else 0, _lib.dtype_code(q.dtype), _native_cache(kernel_cache),
+                                    _lib.stream_ptr())
         _lib.check(code, "attn_fwd")
         ctx.save_for_backward(q, k, v, o, lse, bias_t)
         ctx.causal, ctx.softmax_scale, ctx.kernel_cache = causal, softmax_scale, kernel_cache
@@ -625,7 +632,7 @@ class FlashAttnFunc(torch.autograd.Function):
         _, bias_s = _prep_bias(bias, q, seqlen_q, seqlen_k)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dt = _lib.dtype_code(q.dtype)
-        with torch.cuda.device(q.device):
+        with _lib.device_guard(q):
             nbytes = lib.rgd_attn_bwd_workspace_bytes(batch, nheads, seqlen_q, seqlen_k, d, dt)
             _require(nbytes >= 0, "attn_bwd: bad sizes")
             work = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=q.device)
@@ -633,7 +640,8 @@ class FlashAttnFunc(torch.autograd.Function):
             code = lib.rgd_attn_bwd(hv(q), hv(k), hv(v), C.byref(bias_s), hv(o), lse.data_ptr(), hv(do),
                                     hv(dq), hv(dk), hv(dv), batch, nheads, seqlen_q, seqlen_k, d,
                                     float(ctx.softmax_scale), 1 if ctx.causal else 0, dt,
-                                    work.data_ptr(), work.numel(), _lib.stream_ptr())
+                                    work.data_ptr(), work.numel(), _native_cache(ctx.kernel_cache),
+                                    _lib.stream_ptr())
         _lib.check(code, "attn_bwd")
         return dq, dk, dv, None, None, None, None
 

@@ -16,19 +16,60 @@ from . import functional as F_
 
 
 class _LaunchCache:
-    """Named slots, one per kernel of an operator (``fwd``, ``bwd``, ...).
+    """Named slots, one per kernel of an operator (``fwd``, ``bwd``, ...), plus
+    the native launch-plan cache of the C library.
 
     A slot holds the launch key (shapes, strides, dtypes, device) that was last
     validated for that kernel; a call with the same key skips host-side
     validation, a call with a different key re-validates and replaces it.
+    ``native()`` is the ``rgd_cache`` handle (created on first use) in which the
+    library keeps the encoded TMA descriptors of the calls this module made.
     """
 
     def __init__(self, fields):
         for name in fields:
             setattr(self, name, None)
+        self._native = None
+
+    def native(self):
+        if self._native is None:
+            from . import _lib
+            self._native = _lib.load().rgd_cache_create()
+        return self._native
+
+    def stats(self):
+        """(hits, misses, entries) of the native descriptor cache."""
+        import ctypes as C
+        from . import _lib
+        h, m, e = C.c_int64(0), C.c_int64(0), C.c_int64(0)
+        if self._native is not None:
+            _lib.load().rgd_cache_stats(self._native, C.byref(h), C.byref(m), C.byref(e))
+        return h.value, m.value, e.value
+
+    def __del__(self):
+        native, self._native = getattr(self, "_native", None), None
+        if native is not None:
+            try:
+                from . import _lib
+                _lib.load().rgd_cache_destroy(native)
+            except Exception:       # interpreter shutdown
+                pass
+
+    # the native handle belongs to this process and this object only
+    def __getstate__(self):
+        state = dict(vars(self))
+        state["_native"] = None
+        return state
+
+    def __deepcopy__(self, memo):
+        new = _LaunchCache(())
+        for k, v in vars(self).items():
+            setattr(new, k, None if k == "_native" else v)
+        return new
 
     def __repr__(self):
-        return "LaunchCache(" + ", ".join(f"{k}={'set' if v is not None else None}" for k, v in vars(self).items()) + ")"
+        slots = {k: v for k, v in vars(self).items() if k != "_native"}
+        return "LaunchCache(" + ", ".join(f"{k}={'set' if v is not None else None}" for k, v in slots.items()) + ")"
 
 
 class CachableModule(nn.Module):
