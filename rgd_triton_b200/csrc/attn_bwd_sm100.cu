@@ -310,7 +310,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
                         for (int e = 0; e < 8; ++e) bv[8 * c + e] = to_f32<T>(cv.v[e]);
                     }
                 }
-                mbar_arrive(&sm.bb_empty[sb]);      // values are in registers: the stage can be refilled
+                // (the stage is handed back at the end of the iteration, once instructions that
+                // consume these values have been issued: an arrive right here could be performed
+                // while the loads above are still in flight, and with a single stage the refill
+                // by the copy engine follows at once)
             }
             if constexpr (BIAS == 1) {
                 if (DKDV) {
@@ -470,6 +473,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
             }
             tc_fence_before_sync();
             mbar_arrive(&sm.ds_ready);
+            // dS, which depends on every bias value read above, has been stored: the bias stage is free
+            if constexpr (BIAS == 2) mbar_arrive(&sm.bb_empty[it % BSTAGES]);
         }
 
         // epilogue: accumulators -> global

@@ -67,7 +67,7 @@ struct alignas(1024) FwdTmaSmem {
     unsigned char v[2][TN * D * 2];
     unsigned char bias[BTMA ? NT * 2 : 1][BTMA ? TM * TN * 2 : 1024];
     uint64_t q_full, o_full;
-    uint64_t s_full[2], p_full[2];
+    uint64_t s_full[2], p_half[2][2];           // p_half[tile][h]: P of keys [64h, 64h+64) is in tensor memory
     uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
     uint64_t b_full[2][2], b_empty[2][2];      // [tile][stage]
     uint32_t tmem_base;
@@ -140,6 +140,42 @@ __device__ __forceinline__ void load_bias32(const FwdTmaParams &p, const char *b
     }
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// Maximum of 32 score values (three-input max: 16 instructions instead of 32).
+__device__ __forceinline__ float max32(const uint32_t (&r)[32]) {
+    float a = fmaxf(__uint_as_float(r[0]), __uint_as_float(r[1]));
+    float b = fmaxf(__uint_as_float(r[2]), __uint_as_float(r[3]));
+#pragma unroll
+    for (int i = 4; i < 32; i += 4) {
+        a = fmax3(a, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+        b = fmax3(b, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+    }
+    return fmaxf(a, b);
+}
+
+// P = 2^(s * scale_log2 - m) for 32 scores, packed to 16-bit pairs; the row sum goes to two
+// accumulators so that neither addition chain is longer than 16.
+template <bool BF16>
+__device__ __forceinline__ void exp32(const uint32_t (&r)[32], float scale_log2, float m, uint32_t (&pk)[16], float &s0,
+                                      float &s1) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        const float p0 = ex2(fmaf(__uint_as_float(r[i]), scale_log2, -m));
+        const float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2, -m));
+        const float p2 = ex2(fmaf(__uint_as_float(r[i + 2]), scale_log2, -m));
+        const float p3 = ex2(fmaf(__uint_as_float(r[i + 3]), scale_log2, -m));
+        s0 += p0 + p1;
+        s1 += p2 + p3;
+        pk[i >> 1] = pack16<BF16>(p0, p1);
+        pk[(i >> 1) + 1] = pack16<BF16>(p2, p3);
+    }
+}
+
 // BIAS: 0 none, 1 read straight from global memory by the softmax threads (vector
 // bias, fp32 bias, unaligned views), 2 matrix bias staged tile by tile through TMA.
 template <int D, bool BF16, int BIAS>
@@ -179,7 +215,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
         mbar_init(&sm.o_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&sm.s_full[s], 1);
-            mbar_init(&sm.p_full[s], 128);
+            mbar_init(&sm.p_half[s][0], 128);
+            mbar_init(&sm.p_half[s][1], 128);
             mbar_init(&sm.k_full[s], 1);
             mbar_init(&sm.k_empty[s], 1);
             mbar_init(&sm.v_full[s], 1);
@@ -257,10 +294,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 }
                 umma_commit(&sm.s_full[t]);
             };
-            auto issue_pv = [&](int t, int s, bool first) {
+            // O_t += P_t[:, 64h .. 64h+64) V[64h .. 64h+64, :]: the first half can run while the
+            // softmax threads still form the second half of P
+            auto issue_pv = [&](int t, int s, int h, bool first) {
                 const uint32_t v_addr = smem_u32(sm.v[s]);
 #pragma unroll
-                for (int kk = 0; kk < TN / 16; ++kk)
+                for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
                     umma_ts(tbase + 256 + t * 128, tbase + t * 128 + kk * 8, make_sdesc(v_addr + kk * 2048, PANEL, 1024),
                             idesc_pv, !first || kk > 0);
             };
@@ -279,10 +318,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 ok = mbar_wait(&sm.v_full[s], ph, status, 23);
                 if (!ok) break;
                 if (j < nb[0]) {
-                    ok = mbar_wait(&sm.p_full[0], par, status, 24);
+                    ok = mbar_wait(&sm.p_half[0][0], par, status, 24);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_pv(0, s, j == 0);
+                    issue_pv(0, s, 0, j == 0);
+                    ok = mbar_wait(&sm.p_half[0][1], par, status, 27);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(0, s, 1, false);
                 }
                 if (more) {
                     ok = mbar_wait(&sm.k_full[s ^ 1], (uint32_t)((j + 1) >> 1) & 1u, status, 25);
@@ -291,10 +334,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                     if (j + 1 < nb[0]) issue_s(0, s ^ 1);
                 }
                 if (j < nb[1]) {
-                    ok = mbar_wait(&sm.p_full[1], par, status, 26);
+                    ok = mbar_wait(&sm.p_half[1][0], par, status, 26);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_pv(1, s, j == 0);
+                    issue_pv(1, s, 0, j == 0);
+                    ok = mbar_wait(&sm.p_half[1][1], par, status, 28);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(1, s, 1, false);
                 }
                 umma_commit(&sm.v_empty[s]);
                 if (more) {
@@ -332,6 +379,72 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
             }
             const int n0 = j * TN;
             const bool need_mask = (n0 + TN > p.Tk) || (p.causal && n0 + TN > m0 + t * TM);
+
+            const uint32_t s_addr = lane_base + s_col;
+            if (BIAS == 0 && !need_mask) {
+                // ---- interior block, no bias: the loads of tensor memory run one 32-column chunk
+                // ahead of the arithmetic in both passes, so their latency is paid once per block
+                // and not once per chunk; P leaves in two halves, so the first P V product
+                // starts while the second half's exponentials are still being taken ----
+                uint32_t ra[32], rb[32];
+                tmem_ld32(s_addr, ra);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 32, rb);
+                float m0 = max32(ra);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 64, ra);
+                float m1 = max32(rb);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 96, rb);
+                m0 = fmaxf(m0, max32(ra));
+                tmem_wait_ld();
+                tmem_ld32(s_addr, ra);                       // chunk 0 again, for the second pass
+                m1 = fmaxf(m1, max32(rb));
+                const float mx = fmaxf(m0, m1) * p.scale_log2;          // scale > 0: max commutes with it
+                const bool want = (mx > m_ref + RESCALE_THRESHOLD) || (m_ref == -INFINITY && mx > -INFINITY);
+                if (__any_sync(0xffffffffu, want)) {
+                    const float alpha = !want ? 1.f : (m_ref == -INFINITY ? 0.f : ex2(m_ref - mx));
+                    l_sum *= alpha;
+                    if (want) m_ref = mx;
+                    if (j > 0) {
+#pragma unroll 1
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t r[32];
+                            tmem_ld32(lane_base + o_col + c * 32, r);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                            tmem_st32(lane_base + o_col + c * 32, r);
+                        }
+                    }
+                }
+                const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+                float ls0 = 0.f, ls1 = 0.f;
+                uint32_t pk[16];
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 32, rb);
+                exp32<BF16>(ra, p.scale_log2, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr, pk);                       // packed P over columns already read
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 64, ra);
+                exp32<BF16>(rb, p.scale_log2, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr + 16, pk);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 96, rb);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.p_half[t][0]);               // keys 0..63 of P are in place
+                exp32<BF16>(ra, p.scale_log2, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr + 32, pk);
+                tmem_wait_ld();
+                exp32<BF16>(rb, p.scale_log2, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr + 48, pk);
+                l_sum += ls0 + ls1;
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.p_half[t][1]);
+                continue;
+            }
 
             // pass 1: block maximum of x = s * scale * log2e + bias * log2e, 64 columns per round
             float mx = -INFINITY;
@@ -463,7 +576,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
             }
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&sm.p_full[t]);
+            mbar_arrive(&sm.p_half[t][0]);
+            mbar_arrive(&sm.p_half[t][1]);
             if constexpr (BIAS == 2) mbar_arrive(&sm.b_empty[t][j & 1]);   // bias tile read twice, now free
         }
 

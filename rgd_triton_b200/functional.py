@@ -70,20 +70,84 @@ def _key(*tensors, extra=()) -> tuple:
     return tuple((tuple(t.shape), t.stride(), t.dtype, t.device.index) for t in tensors if t is not None) + tuple(extra)
 
 
-def _cache_hit(cache, slot: str, key) -> bool:
-    """True when `slot` of the module cache already holds this validated key."""
-    return cache is not None and getattr(cache, slot, None) == key
+def _plan(cache, slot: str, key, validate):
+    """Launch plan of `slot` for this key.
 
-
-def _cache_put(cache, slot: str, key) -> None:
-    if cache is not None:
-        setattr(cache, slot, key)
+    With a module cache: when the slot already holds `key` (same shapes,
+    strides, dtypes, device as the last validated call) the stored plan is
+    returned and host-side validation is skipped; otherwise `validate()` runs,
+    the slot takes the new key and a fresh, empty plan.  The plan is a dict in
+    which the launch helpers keep their marshalled ctypes arguments, so a
+    repeated call only refreshes the data pointers.  Without a cache every call
+    validates and marshals from scratch (returns None)."""
+    if cache is None:
+        validate()
+        return None
+    store = cache.__dict__
+    ent = store.get("_plan_" + slot)
+    if ent is not None and ent[0] == key:
+        return ent[1]
+    validate()
+    setattr(cache, slot, key)
+    plan = {}
+    store["_plan_" + slot] = (key, plan)
+    return plan
 
 
 def _native_cache(cache):
     """The library's launch-plan cache behind a module cache (None without one)."""
     native = getattr(cache, "native", None)
     return native() if native is not None else None
+
+
+def _needs_grad(*tensors) -> bool:
+    """Whether autograd has to record this call.  When it does not, the entry
+    points run the forward directly instead of through autograd.Function, whose
+    bookkeeping costs more host time than a small operator's whole launch."""
+    if not torch.is_grad_enabled():
+        return False
+    for t in tensors:
+        if t is not None and t.requires_grad:
+            return True
+    return False
+
+
+def _rows_arr(plan, tag: str, tensors):
+    """ctypes array of rgd_rows for `tensors`; kept in the plan, pointers refreshed."""
+    arr = plan.get(tag) if plan is not None else None
+    if arr is None:
+        arr = (Rows * len(tensors))(*[_lib.rows(t) for t in tensors])
+        if plan is not None:
+            plan[tag] = arr
+    else:
+        for a, t in zip(arr, tensors):
+            a.ptr = t.data_ptr()
+    return arr
+
+
+def _heads_refs(plan, tag: str, tensors, layout):
+    """byref()s of rgd_heads structs for `tensors` (None stays None); `layout` maps a tensor
+    to its struct.  The structs are kept in the plan, pointers refreshed."""
+    hs = plan.get(tag) if plan is not None else None
+    if hs is None:
+        hs = [None if t is None else layout(t) for t in tensors]
+        if plan is not None:
+            plan[tag] = hs
+    else:
+        for h, t in zip(hs, tensors):
+            if h is not None:
+                h.ptr = t.data_ptr()
+    return [None if h is None else C.byref(h) for h in hs]
+
+
+def _const(plan, tag: str, make):
+    """A value that depends only on the launch key (sizes, dtype codes), made once per plan."""
+    if plan is None:
+        return make()
+    v = plan.get(tag)
+    if v is None:
+        v = plan[tag] = make()
+    return v
 
 
 # --------------------------------------------------------------------------
@@ -100,22 +164,43 @@ def _check_rows(xs, what: str) -> None:
     _require(all(x.shape[0] == xs[0].shape[0] for x in xs), f"{what}: batch sizes differ")
 
 
-def _l2_launch(xs, dys, outs, eps: float, bwd: bool) -> None:
+def _row_sizes(plan, xs):
+    return _const(plan, "sizes", lambda: (_i64(*[t.shape[1] for t in xs]), _i64(*[t.shape[2] for t in xs]),
+                                          xs[0].shape[0], _lib.dtype_code(xs[0].dtype)))
+
+
+def _l2_launch(plan, xs, dys, outs, eps: float, bwd: bool) -> None:
     lib = _lib.load()
     n = len(xs)
-    xa = (Rows * n)(*[_lib.rows(t) for t in xs])
-    oa = (Rows * n)(*[_lib.rows(t) for t in outs])
-    N = _i64(*[t.shape[1] for t in xs])
-    Cc = _i64(*[t.shape[2] for t in xs])
-    B = xs[0].shape[0]
-    dt = _lib.dtype_code(xs[0].dtype)
+    N, Cc, B, dt = _row_sizes(plan, xs)
+    xa, oa = _rows_arr(plan, "x", xs), _rows_arr(plan, "out", outs)
     with _lib.device_guard(xs[0]):
         if bwd:
-            da = (Rows * n)(*[_lib.rows(t) for t in dys])
-            code = lib.rgd_l2norm_bwd(n, xa, da, oa, N, Cc, B, float(eps), dt, _lib.stream_ptr())
+            code = lib.rgd_l2norm_bwd(n, xa, _rows_arr(plan, "dy", dys), oa, N, Cc, B, float(eps), dt, _lib.stream_ptr())
         else:
             code = lib.rgd_l2norm_fwd(n, xa, oa, N, Cc, B, float(eps), dt, _lib.stream_ptr())
-    _lib.check(code, "l2norm_bwd" if bwd else "l2norm_fwd")
+    if code:
+        _lib.check(code, "l2norm_bwd" if bwd else "l2norm_fwd")
+
+
+def _l2_forward(xs, eps, cache, tag):
+    xs = [_last_contig(x) for x in xs]
+    plan = _plan(cache, "fwd", _key(*xs, extra=("l2", tag)), lambda: _check_rows(xs, tag))
+    ys = [torch.empty_like(x) for x in xs]
+    _l2_launch(plan, xs, None, ys, eps, bwd=False)
+    return xs, ys
+
+
+def _l2_backward(xs, dys, eps, cache, tag):
+    dys = [_last_contig(d) for d in dys]
+
+    def validate():
+        _check_rows([*xs, *dys], tag + " backward")
+        _require(all(d.shape == x.shape for d, x in zip(dys, xs)), "gradient shape mismatch")
+    plan = _plan(cache, "bwd", _key(*xs, *dys, extra=("l2", tag)), validate)
+    dxs = [torch.empty_like(x) for x in xs]
+    _l2_launch(plan, xs, dys, dxs, eps, bwd=True)
+    return dxs
 
 
 class Norm_Func(torch.autograd.Function):
@@ -123,13 +208,7 @@ class Norm_Func(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, norm_eps=1e-6, use_ptx=False, kernel_cache=None):
-        x = _last_contig(x)
-        key = _key(x, extra=("l2", 1))
-        if not _cache_hit(kernel_cache, "fwd", key):
-            _check_rows([x], "L2Normalize")
-            _cache_put(kernel_cache, "fwd", key)
-        y = torch.empty_like(x)
-        _l2_launch([x], None, [y], norm_eps, bwd=False)
+        (x,), (y,) = _l2_forward([x], norm_eps, kernel_cache, "L2Normalize")
         ctx.save_for_backward(x)
         ctx.norm_eps = norm_eps
         ctx.kernel_cache = kernel_cache
@@ -137,20 +216,14 @@ class Norm_Func(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        (x,) = ctx.saved_tensors
-        dy = _last_contig(dy)
-        key = _key(x, dy, extra=("l2", 1))
-        if not _cache_hit(ctx.kernel_cache, "bwd", key):
-            _check_rows([x, dy], "L2Normalize backward")
-            _require(dy.shape == x.shape, "gradient shape mismatch")
-            _cache_put(ctx.kernel_cache, "bwd", key)
-        dx = torch.empty_like(x)
-        _l2_launch([x], [dy], [dx], ctx.norm_eps, bwd=True)
+        (dx,) = _l2_backward(list(ctx.saved_tensors), [dy], ctx.norm_eps, ctx.kernel_cache, "L2Normalize")
         return dx, None, None, None
 
 
 def triton_norm_func_fn(x, norm_eps=1e-6, use_ptx=False, kernel_cache=None):
     """L2-normalise the rows of x.  ``use_ptx`` is accepted and ignored."""
+    if not _needs_grad(x):
+        return _l2_forward([x], norm_eps, kernel_cache, "L2Normalize")[1][0]
     return Norm_Func.apply(x, norm_eps, use_ptx, kernel_cache)
 
 
@@ -159,32 +232,23 @@ class Fused_Norm_Func(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x1, x2, norm_eps=1e-6, kernel_cache=None):
-        x1, x2 = _last_contig(x1), _last_contig(x2)
-        key = _key(x1, x2, extra=("l2", 2))
-        if not _cache_hit(kernel_cache, "fwd", key):
-            _check_rows([x1, x2], "FusedL2Normalize2")
-            _cache_put(kernel_cache, "fwd", key)
-        y1, y2 = torch.empty_like(x1), torch.empty_like(x2)
-        _l2_launch([x1, x2], None, [y1, y2], norm_eps, bwd=False)
-        ctx.save_for_backward(x1, x2)
+        xs, ys = _l2_forward([x1, x2], norm_eps, kernel_cache, "FusedL2Normalize2")
+        ctx.save_for_backward(*xs)
         ctx.norm_eps = norm_eps
         ctx.kernel_cache = kernel_cache
-        return y1, y2
+        return ys[0], ys[1]
 
     @staticmethod
     def backward(ctx, dy1, dy2):
-        x1, x2 = ctx.saved_tensors
-        dy1, dy2 = _last_contig(dy1), _last_contig(dy2)
-        key = _key(x1, x2, dy1, dy2, extra=("l2", 2))
-        if not _cache_hit(ctx.kernel_cache, "bwd", key):
-            _check_rows([x1, x2, dy1, dy2], "FusedL2Normalize2 backward")
-            _cache_put(ctx.kernel_cache, "bwd", key)
-        dx1, dx2 = torch.empty_like(x1), torch.empty_like(x2)
-        _l2_launch([x1, x2], [dy1, dy2], [dx1, dx2], ctx.norm_eps, bwd=True)
+        dx1, dx2 = _l2_backward(list(ctx.saved_tensors), [dy1, dy2], ctx.norm_eps, ctx.kernel_cache,
+                                "FusedL2Normalize2")
         return dx1, dx2, None, None
 
 
 def triton_fused_norm_func_fn(x1, x2, norm_eps=1e-6, kernel_cache=None):
+    if not _needs_grad(x1, x2):
+        ys = _l2_forward([x1, x2], norm_eps, kernel_cache, "FusedL2Normalize2")[1]
+        return ys[0], ys[1]
     return Fused_Norm_Func.apply(x1, x2, norm_eps, kernel_cache)
 
 
@@ -208,56 +272,76 @@ def _prep_weight(w: torch.Tensor, x: torch.Tensor):
     return w, w.stride(0), True
 
 
-def _rms_fwd(xs, ws, eps):
-    lib = _lib.load()
-    n = len(xs)
-    preps = [_prep_weight(w, x) for w, x in zip(ws, xs)]
+def _check_weights(preps, xs) -> None:
     _require(all(p[0].dtype == preps[0][0].dtype for p in preps), "weights must share one dtype")
     for p in preps:
         _require(p[0].dtype in _FLOATS, "Only support fp16, bf16, and fp32")
         _require(p[0].device == xs[0].device, "weight and input are on different devices")
-    ys = [torch.empty_like(x) for x in xs]
-    xa = (Rows * n)(*[_lib.rows(t) for t in xs])
-    ya = (Rows * n)(*[_lib.rows(t) for t in ys])
-    wp = (C.c_void_p * n)(*[p[0].data_ptr() for p in preps])
-    wsb = _i64(*[p[1] for p in preps])
-    N = _i64(*[t.shape[1] for t in xs])
-    Cc = _i64(*[t.shape[2] for t in xs])
-    with _lib.device_guard(xs[0]):
-        code = lib.rgd_rmsnorm_fwd(n, xa, wp, wsb, ya, N, Cc, xs[0].shape[0], float(eps),
-                                   _lib.dtype_code(xs[0].dtype), _lib.dtype_code(preps[0][0].dtype),
-                                   _lib.stream_ptr())
-    _lib.check(code, "rmsnorm_fwd")
-    return ys, [p[0] for p in preps]
 
 
-def _rms_bwd(xs, ws, dys, eps):
+def _weight_ptrs(plan, ws):
+    wp = plan.get("w") if plan is not None else None
+    if wp is None:
+        wp = (C.c_void_p * len(ws))(*[w.data_ptr() for w in ws])
+        if plan is not None:
+            plan["w"] = wp
+    else:
+        for i, w in enumerate(ws):
+            wp[i] = w.data_ptr()
+    return wp
+
+
+def _rms_forward(xs, ws, eps, cache, tag):
+    xs = [_last_contig(x) for x in xs]
+    preps = None
+
+    def validate():
+        _check_rows(xs, tag)
+        _check_weights([_prep_weight(w, x) for w, x in zip(ws, xs)], xs)
+    plan = _plan(cache, "fwd", _key(*xs, *ws, extra=("rms", tag)), validate)
+    meta = _const(plan, "wmeta", lambda: [_prep_weight(w, x)[1:] for w, x in zip(ws, xs)])   # (batch stride, per batch)
+    wk = [_last_contig(w) for w in ws]
     lib = _lib.load()
     n = len(xs)
-    preps = [_prep_weight(w, x) for w, x in zip(ws, xs)]
-    B = xs[0].shape[0]
-    dxs = [torch.empty_like(x) for x in xs]
-    dws = []
-    for (w, _, per_batch), x in zip(preps, xs):
-        shape = (B, x.shape[2]) if per_batch else (x.shape[2],)
-        dws.append(torch.empty(shape, dtype=w.dtype, device=w.device))
-    N = _i64(*[t.shape[1] for t in xs])
-    Cc = _i64(*[t.shape[2] for t in xs])
+    N, Cc, B, dt = _row_sizes(plan, xs)
+    wsb, wdt = _const(plan, "wconst", lambda: (_i64(*[m[0] for m in meta]), _lib.dtype_code(wk[0].dtype)))
+    ys = [torch.empty_like(x) for x in xs]
     with _lib.device_guard(xs[0]):
-        nbytes = lib.rgd_rmsnorm_bwd_workspace_bytes(n, N, Cc, B)
-        _require(nbytes >= 0, "rmsnorm_bwd: bad sizes")
-        work = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=xs[0].device)
-        xa = (Rows * n)(*[_lib.rows(t) for t in xs])
-        da = (Rows * n)(*[_lib.rows(t) for t in dys])
-        oa = (Rows * n)(*[_lib.rows(t) for t in dxs])
-        wp = (C.c_void_p * n)(*[p[0].data_ptr() for p in preps])
-        wsb = _i64(*[p[1] for p in preps])
-        dwp = (C.c_void_p * n)(*[t.data_ptr() for t in dws])
-        per = (C.c_int * n)(*[1 if p[2] else 0 for p in preps])
-        code = lib.rgd_rmsnorm_bwd(n, xa, wp, wsb, da, oa, dwp, per, N, Cc, B, float(eps),
-                                   _lib.dtype_code(xs[0].dtype), _lib.dtype_code(preps[0][0].dtype),
+        code = lib.rgd_rmsnorm_fwd(n, _rows_arr(plan, "x", xs), _weight_ptrs(plan, wk), wsb, _rows_arr(plan, "out", ys),
+                                   N, Cc, B, float(eps), dt, wdt, _lib.stream_ptr())
+    if code:
+        _lib.check(code, "rmsnorm_fwd")
+    return xs, wk, ys
+
+
+def _rms_backward(xs, ws, dys, eps, cache, tag):
+    dys = [_last_contig(d) for d in dys]
+
+    def validate():
+        _check_rows([*xs, *dys], tag + " backward")
+        _check_weights([_prep_weight(w, x) for w, x in zip(ws, xs)], xs)
+    plan = _plan(cache, "bwd", _key(*xs, *ws, *dys, extra=("rms", tag)), validate)
+    if cache is not None:
+        cache.bwd_dw = cache.bwd
+    meta = _const(plan, "wmeta", lambda: [_prep_weight(w, x)[1:] for w, x in zip(ws, xs)])
+    lib = _lib.load()
+    n = len(xs)
+    N, Cc, B, dt = _row_sizes(plan, xs)
+    wsb, wdt, per, nbytes = _const(plan, "wconst", lambda: (
+        _i64(*[m[0] for m in meta]), _lib.dtype_code(ws[0].dtype), (C.c_int * n)(*[1 if m[1] else 0 for m in meta]),
+        int(lib.rgd_rmsnorm_bwd_workspace_bytes(n, N, Cc, B))))
+    _require(nbytes >= 0, "rmsnorm_bwd: bad sizes")
+    dxs = [torch.empty_like(x) for x in xs]
+    dws = [torch.empty((B, x.shape[2]) if m[1] else (x.shape[2],), dtype=w.dtype, device=w.device)
+           for m, x, w in zip(meta, xs, ws)]
+    work = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=xs[0].device)
+    dwp = (C.c_void_p * n)(*[t.data_ptr() for t in dws])
+    with _lib.device_guard(xs[0]):
+        code = lib.rgd_rmsnorm_bwd(n, _rows_arr(plan, "x", xs), _weight_ptrs(plan, ws), wsb, _rows_arr(plan, "dy", dys),
+                                   _rows_arr(plan, "out", dxs), dwp, per, N, Cc, B, float(eps), dt, wdt,
                                    work.data_ptr(), work.numel(), _lib.stream_ptr())
-    _lib.check(code, "rmsnorm_bwd")
+    if code:
+        _lib.check(code, "rmsnorm_bwd")
     return dxs, dws
 
 
@@ -266,12 +350,7 @@ class RMS_Func(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, norm_eps=1e-6, kernel_cache=None):
-        x = _last_contig(x)
-        key = _key(x, w, extra=("rms", 1))
-        if not _cache_hit(kernel_cache, "fwd", key):
-            _check_rows([x], "FusedRMSNorm")
-            _cache_put(kernel_cache, "fwd", key)
-        (y,), (wk,) = _rms_fwd([x], [w], norm_eps)
+        (x,), (wk,), (y,) = _rms_forward([x], [w], norm_eps, kernel_cache, "FusedRMSNorm")
         ctx.save_for_backward(x, wk)
         ctx.wshape = w.shape
         ctx.norm_eps = norm_eps
@@ -281,17 +360,13 @@ class RMS_Func(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        dy = _last_contig(dy)
-        key = _key(x, w, dy, extra=("rms", 1))
-        if not _cache_hit(ctx.kernel_cache, "bwd", key):
-            _check_rows([x, dy], "FusedRMSNorm backward")
-            _cache_put(ctx.kernel_cache, "bwd", key)
-            _cache_put(ctx.kernel_cache, "bwd_dw", key)
-        (dx,), (dw,) = _rms_bwd([x], [w], [dy], ctx.norm_eps)
+        (dx,), (dw,) = _rms_backward([x], [w], [dy], ctx.norm_eps, ctx.kernel_cache, "FusedRMSNorm")
         return dx, dw.view(ctx.wshape), None, None
 
 
 def triton_rms_func_fn(x, w, norm_eps=1e-6, kernel_cache=None):
+    if not _needs_grad(x, w):
+        return _rms_forward([x], [w], norm_eps, kernel_cache, "FusedRMSNorm")[2][0]
     return RMS_Func.apply(x, w, norm_eps, kernel_cache)
 
 
@@ -300,32 +375,25 @@ class Fused_RMS_Func(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x1, x2, w1, w2, norm_eps=1e-6, kernel_cache=None):
-        x1, x2 = _last_contig(x1), _last_contig(x2)
-        key = _key(x1, x2, w1, w2, extra=("rms", 2))
-        if not _cache_hit(kernel_cache, "fwd", key):
-            _check_rows([x1, x2], "FusedRMSNorm2")
-            _cache_put(kernel_cache, "fwd", key)
-        (y1, y2), (wk1, wk2) = _rms_fwd([x1, x2], [w1, w2], norm_eps)
-        ctx.save_for_backward(x1, x2, wk1, wk2)
+        xs, wk, ys = _rms_forward([x1, x2], [w1, w2], norm_eps, kernel_cache, "FusedRMSNorm2")
+        ctx.save_for_backward(*xs, *wk)
         ctx.w1shape, ctx.w2shape = w1.shape, w2.shape
         ctx.norm_eps = norm_eps
         ctx.kernel_cache = kernel_cache
-        return y1, y2
+        return ys[0], ys[1]
 
     @staticmethod
     def backward(ctx, dy1, dy2):
         x1, x2, w1, w2 = ctx.saved_tensors
-        dy1, dy2 = _last_contig(dy1), _last_contig(dy2)
-        key = _key(x1, x2, w1, w2, dy1, dy2, extra=("rms", 2))
-        if not _cache_hit(ctx.kernel_cache, "bwd", key):
-            _check_rows([x1, x2, dy1, dy2], "FusedRMSNorm2 backward")
-            _cache_put(ctx.kernel_cache, "bwd", key)
-            _cache_put(ctx.kernel_cache, "bwd_dw", key)
-        (dx1, dx2), (dw1, dw2) = _rms_bwd([x1, x2], [w1, w2], [dy1, dy2], ctx.norm_eps)
+        (dx1, dx2), (dw1, dw2) = _rms_backward([x1, x2], [w1, w2], [dy1, dy2], ctx.norm_eps, ctx.kernel_cache,
+                                               "FusedRMSNorm2")
         return dx1, dx2, dw1.view(ctx.w1shape), dw2.view(ctx.w2shape), None, None
 
 
 def triton_fused_rms_func_fn(x1, x2, w1, w2, norm_eps=1e-6, kernel_cache=None):
+    if not _needs_grad(x1, x2, w1, w2):
+        ys = _rms_forward([x1, x2], [w1, w2], norm_eps, kernel_cache, "FusedRMSNorm2")[2]
+        return ys[0], ys[1]
     return Fused_RMS_Func.apply(x1, x2, w1, w2, norm_eps, kernel_cache)
 
 
@@ -378,19 +446,32 @@ def _prep_pos(pos_emb: torch.Tensor, x: torch.Tensor, nq: int, nk: int) -> torch
     return pos_emb
 
 
-def _ln_launch(q, k, dqo, dko, qo, ko, heads_second, eps, bwd):
+def _ln_launch(plan, q, k, dqo, dko, qo, ko, heads_second, eps, bwd):
     lib = _lib.load()
-    B, H, nq, nk, d = _head_dims(q, k, heads_second)
-    hv = lambda t: C.byref(_lib.heads(t, heads_second))
-    dt = _lib.dtype_code(q.dtype)
+    dims = _const(plan, "dims", lambda: (*_head_dims(q, k, heads_second), _lib.dtype_code(q.dtype)))
+    B, H, nq, nk, d, dt = dims
+    lay = lambda t: _lib.heads(t, heads_second)
     with _lib.device_guard(q):
         if bwd:
-            code = lib.rgd_headln_bwd(hv(q), hv(k), hv(dqo), hv(dko), hv(qo), hv(ko), B, H, nq, nk, d, float(eps), dt,
-                                      _lib.stream_ptr())
+            h = _heads_refs(plan, "h", (q, k, dqo, dko, qo, ko), lay)
+            code = lib.rgd_headln_bwd(*h, B, H, nq, nk, d, float(eps), dt, _lib.stream_ptr())
         else:
-            code = lib.rgd_headln_fwd(hv(q), hv(k), hv(qo), hv(ko), B, H, nq, nk, d, float(eps), dt,
-                                      _lib.stream_ptr())
-    _lib.check(code, "headln_bwd" if bwd else "headln_fwd")
+            h = _heads_refs(plan, "h", (q, k, qo, ko), lay)
+            code = lib.rgd_headln_fwd(*h, B, H, nq, nk, d, float(eps), dt, _lib.stream_ptr())
+    if code:
+        _lib.check(code, "headln_bwd" if bwd else "headln_fwd")
+
+
+def _ln_forward(q, k, heads_second, eps, cache):
+    q, k = _last_contig(q), _last_contig(k)
+
+    def validate():
+        _check_heads([q, k], "FusedHeadLayerNorm", 256)
+        _head_dims(q, k, heads_second)
+    plan = _plan(cache, "fwd", _key(q, k, extra=("ln", bool(heads_second))), validate)
+    qo, ko = torch.empty_like(q), torch.empty_like(k)
+    _ln_launch(plan, q, k, None, None, qo, ko, heads_second, eps, bwd=False)
+    return q, k, qo, ko
 
 
 class Fused_LNQK_Func(torch.autograd.Function):
@@ -399,14 +480,7 @@ class Fused_LNQK_Func(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, heads_second=True, norm_eps=1e-6, kernel_cache=None):
-        q, k = _last_contig(q), _last_contig(k)
-        key = _key(q, k, extra=("ln", bool(heads_second)))
-        if not _cache_hit(kernel_cache, "fwd", key):
-            _check_heads([q, k], "FusedHeadLayerNorm", 256)
-            _head_dims(q, k, heads_second)
-            _cache_put(kernel_cache, "fwd", key)
-        qo, ko = torch.empty_like(q), torch.empty_like(k)
-        _ln_launch(q, k, None, None, qo, ko, heads_second, norm_eps, bwd=False)
+        q, k, qo, ko = _ln_forward(q, k, heads_second, norm_eps, kernel_cache)
         ctx.save_for_backward(q, k)
         ctx.heads_second, ctx.norm_eps, ctx.kernel_cache = heads_second, norm_eps, kernel_cache
         return qo, ko
@@ -415,30 +489,61 @@ class Fused_LNQK_Func(torch.autograd.Function):
     def backward(ctx, dqo, dko):
         q, k = ctx.saved_tensors
         dqo, dko = _last_contig(dqo), _last_contig(dko)
-        key = _key(q, k, dqo, dko, extra=("ln", bool(ctx.heads_second)))
-        if not _cache_hit(ctx.kernel_cache, "bwd", key):
+
+        def validate():
             _check_heads([q, k, dqo, dko], "FusedHeadLayerNorm backward", 256)
             _require(dqo.shape == q.shape and dko.shape == k.shape, "gradient shape mismatch")
-            _cache_put(ctx.kernel_cache, "bwd", key)
+        plan = _plan(ctx.kernel_cache, "bwd", _key(q, k, dqo, dko, extra=("ln", bool(ctx.heads_second))), validate)
         dq, dk = torch.empty_like(dqo), torch.empty_like(dko)
-        _ln_launch(q, k, dqo, dko, dq, dk, ctx.heads_second, ctx.norm_eps, bwd=True)
+        _ln_launch(plan, q, k, dqo, dko, dq, dk, ctx.heads_second, ctx.norm_eps, bwd=True)
         return dq, dk, None, None, None
 
 
 def triton_fused_ln_func_fn(query, key, heads_second=True, norm_eps=1e-6, kernel_cache=None):
+    if not _needs_grad(query, key):
+        return _ln_forward(query, key, heads_second, norm_eps, kernel_cache)[2:]
     return Fused_LNQK_Func.apply(query, key, heads_second, norm_eps, kernel_cache)
 
 
-def _rope_launch(q, k, pos, qo, ko, cuts, heads_second, transposed):
+def _rope_consts(plan, q, k, pos, cuts, heads_second):
+    return _const(plan, "dims", lambda: (*_head_dims(q, k, heads_second), pos.shape[1], pos.shape[2], cuts[0], cuts[1],
+                                         _lib.dtype_code(q.dtype), _lib.dtype_code(pos.dtype), pos.stride(0),
+                                         pos.stride(1)))
+
+
+def _rope_launch(plan, q, k, pos, qo, ko, cuts, heads_second, transposed):
     lib = _lib.load()
-    B, H, nq, nk, d = _head_dims(q, k, heads_second)
-    hv = lambda t: C.byref(_lib.heads(t, heads_second))
+    B, H, nq, nk, d, P, R, cq, ck, dt, pdt, ps0, ps1 = _rope_consts(plan, q, k, pos, cuts, heads_second)
+    qh, kh, qoh, koh = _heads_refs(plan, "h", (q, k, qo, ko), lambda t: _lib.heads(t, heads_second))
     with _lib.device_guard(q):
-        code = lib.rgd_rope(hv(q), hv(k), pos.data_ptr(), pos.stride(0), pos.stride(1), hv(qo), hv(ko),
-                            B, H, nq, nk, d, pos.shape[1], pos.shape[2], cuts[0], cuts[1],
-                            1 if transposed else 0, _lib.dtype_code(q.dtype), _lib.dtype_code(pos.dtype),
-                            _lib.stream_ptr())
-    _lib.check(code, "rope")
+        code = lib.rgd_rope(qh, kh, pos.data_ptr(), ps0, ps1, qoh, koh, B, H, nq, nk, d, P, R, cq, ck,
+                            1 if transposed else 0, dt, pdt, _lib.stream_ptr())
+    if code:
+        _lib.check(code, "rope")
+
+
+def _rope_forward(q, k, pos_emb, seq_cutoff, heads_second, in_place, cache):
+    q, k = _last_contig(q), _last_contig(k)
+    plan = _plan(cache, "fwd", _key(q, k, pos_emb, extra=("rope", bool(heads_second), _cut_key(seq_cutoff))),
+                 lambda: _check_heads([q, k], "RoPE", 128))
+    if plan is not None and "pos_ok" in plan and pos_emb.dtype in (q.dtype, torch.float32) and pos_emb.stride(-1) == 1:
+        pos, cuts = pos_emb, plan["cuts"]          # validated for this key before; no conversion needed
+    else:
+        B, H, nq, nk, d = _head_dims(q, k, heads_second)
+        pos = _prep_pos(pos_emb, q, nq, nk)
+        cuts = _cutoffs(seq_cutoff, nq, nk)
+        if plan is not None:
+            plan["pos_ok"], plan["cuts"] = True, cuts
+    if in_place:
+        qo, ko = q, k
+    else:
+        qo, ko = torch.empty_like(q), torch.empty_like(k)
+    _rope_launch(plan, q, k, pos, qo, ko, cuts, heads_second, transposed=False)
+    return q, k, pos, cuts, qo, ko
+
+
+def _cut_key(seq_cutoff):
+    return tuple(seq_cutoff) if isinstance(seq_cutoff, (tuple, list)) else seq_cutoff
 
 
 class CombinedRoPEFunc(torch.autograd.Function):
@@ -449,20 +554,9 @@ class CombinedRoPEFunc(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, pos_emb, seq_cutoff=None, heads_second=True, in_place=False, kernel_cache=None):
-        q, k = _last_contig(q), _last_contig(k)
-        key = _key(q, k, pos_emb, extra=("rope", bool(heads_second)))
-        if not _cache_hit(kernel_cache, "fwd", key):
-            _check_heads([q, k], "RoPE", 128)
-            _cache_put(kernel_cache, "fwd", key)
-        B, H, nq, nk, d = _head_dims(q, k, heads_second)
-        pos = _prep_pos(pos_emb, q, nq, nk)
-        cuts = _cutoffs(seq_cutoff, nq, nk)
+        q, k, pos, cuts, qo, ko = _rope_forward(q, k, pos_emb, seq_cutoff, heads_second, in_place, kernel_cache)
         if in_place:
-            qo, ko = q, k
             ctx.mark_dirty(q, k)
-        else:
-            qo, ko = torch.empty_like(q), torch.empty_like(k)
-        _rope_launch(q, k, pos, qo, ko, cuts, heads_second, transposed=False)
         ctx.save_for_backward(pos)
         ctx.cuts, ctx.heads_second, ctx.kernel_cache = cuts, heads_second, kernel_cache
         return qo, ko
@@ -472,12 +566,10 @@ class CombinedRoPEFunc(torch.autograd.Function):
         (pos,) = ctx.saved_tensors
         _require(not ctx.needs_input_grad[2], "CombinedRoPE does not support gradients in position embeddings")
         dqo, dko = _last_contig(dqo), _last_contig(dko)
-        key = _key(dqo, dko, pos, extra=("rope", bool(ctx.heads_second)))
-        if not _cache_hit(ctx.kernel_cache, "bwd", key):
-            _check_heads([dqo, dko], "RoPE backward", 128)
-            _cache_put(ctx.kernel_cache, "bwd", key)
+        plan = _plan(ctx.kernel_cache, "bwd", _key(dqo, dko, pos, extra=("rope", bool(ctx.heads_second), ctx.cuts)),
+                     lambda: _check_heads([dqo, dko], "RoPE backward", 128))
         dq, dk = torch.empty_like(dqo), torch.empty_like(dko)
-        _rope_launch(dqo, dko, pos, dq, dk, ctx.cuts, ctx.heads_second, transposed=True)
+        _rope_launch(plan, dqo, dko, pos, dq, dk, ctx.cuts, ctx.heads_second, transposed=True)
         return dq, dk, None, None, None, None, None
 
 
@@ -485,23 +577,42 @@ def triton_rope_fn(query, key, pos_emb, seq_cutoff=None, heads_second=True, fuse
                    in_place=False):
     """Rotary embedding on (query, key).  ``fused_ln`` is accepted for
     signature parity and ignored, as in the reference."""
+    if not _needs_grad(query, key, pos_emb):
+        return _rope_forward(query, key, pos_emb, seq_cutoff, heads_second, in_place, kernel_cache)[4:]
     return CombinedRoPEFunc.apply(query, key, pos_emb, seq_cutoff, heads_second, in_place, kernel_cache)
 
 
-def _lnrope_launch(q, k, dqo, dko, pos, qo, ko, cuts, heads_second, eps, bwd):
+def _lnrope_launch(plan, q, k, dqo, dko, pos, qo, ko, cuts, heads_second, eps, bwd):
     lib = _lib.load()
-    B, H, nq, nk, d = _head_dims(q, k, heads_second)
-    hv = lambda t: C.byref(_lib.heads(t, heads_second))
-    tail = (B, H, nq, nk, d, pos.shape[1], pos.shape[2], cuts[0], cuts[1], float(eps),
-            _lib.dtype_code(q.dtype), _lib.dtype_code(pos.dtype), _lib.stream_ptr())
+    B, H, nq, nk, d, P, R, cq, ck, dt, pdt, ps0, ps1 = _rope_consts(plan, q, k, pos, cuts, heads_second)
+    lay = lambda t: _lib.heads(t, heads_second)
+    tail = (B, H, nq, nk, d, P, R, cq, ck, float(eps), dt, pdt, _lib.stream_ptr())
     with _lib.device_guard(q):
         if bwd:
-            code = lib.rgd_lnrope_bwd(hv(q), hv(k), hv(dqo), hv(dko), pos.data_ptr(), pos.stride(0), pos.stride(1),
-                                      hv(qo), hv(ko), *tail)
+            qh, kh, dqh, dkh, qoh, koh = _heads_refs(plan, "h", (q, k, dqo, dko, qo, ko), lay)
+            code = lib.rgd_lnrope_bwd(qh, kh, dqh, dkh, pos.data_ptr(), ps0, ps1, qoh, koh, *tail)
         else:
-            code = lib.rgd_lnrope_fwd(hv(q), hv(k), pos.data_ptr(), pos.stride(0), pos.stride(1), hv(qo), hv(ko),
-                                      *tail)
-    _lib.check(code, "lnrope_bwd" if bwd else "lnrope_fwd")
+            qh, kh, qoh, koh = _heads_refs(plan, "h", (q, k, qo, ko), lay)
+            code = lib.rgd_lnrope_fwd(qh, kh, pos.data_ptr(), ps0, ps1, qoh, koh, *tail)
+    if code:
+        _lib.check(code, "lnrope_bwd" if bwd else "lnrope_fwd")
+
+
+def _lnrope_forward(q, k, pos_emb, seq_cutoff, heads_second, eps, cache):
+    q, k = _last_contig(q), _last_contig(k)
+    plan = _plan(cache, "fwd", _key(q, k, pos_emb, extra=("lnrope", bool(heads_second), _cut_key(seq_cutoff))),
+                 lambda: _check_heads([q, k], "FusedLNRoPE", 128))
+    if plan is not None and "pos_ok" in plan and pos_emb.dtype in (q.dtype, torch.float32) and pos_emb.stride(-1) == 1:
+        pos, cuts = pos_emb, plan["cuts"]
+    else:
+        B, H, nq, nk, d = _head_dims(q, k, heads_second)
+        pos = _prep_pos(pos_emb, q, nq, nk)
+        cuts = _cutoffs(seq_cutoff, nq, nk)
+        if plan is not None:
+            plan["pos_ok"], plan["cuts"] = True, cuts
+    qo, ko = torch.empty_like(q), torch.empty_like(k)
+    _lnrope_launch(plan, q, k, None, None, pos, qo, ko, cuts, heads_second, eps, bwd=False)
+    return q, k, pos, cuts, qo, ko
 
 
 class FusedRoPEFunc(torch.autograd.Function):
@@ -510,16 +621,7 @@ class FusedRoPEFunc(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, pos_emb, seq_cutoff=None, heads_second=True, norm_eps=1e-6, kernel_cache=None):
-        q, k = _last_contig(q), _last_contig(k)
-        key = _key(q, k, pos_emb, extra=("lnrope", bool(heads_second)))
-        if not _cache_hit(kernel_cache, "fwd", key):
-            _check_heads([q, k], "FusedLNRoPE", 128)
-            _cache_put(kernel_cache, "fwd", key)
-        B, H, nq, nk, d = _head_dims(q, k, heads_second)
-        pos = _prep_pos(pos_emb, q, nq, nk)
-        cuts = _cutoffs(seq_cutoff, nq, nk)
-        qo, ko = torch.empty_like(q), torch.empty_like(k)
-        _lnrope_launch(q, k, None, None, pos, qo, ko, cuts, heads_second, norm_eps, bwd=False)
+        q, k, pos, cuts, qo, ko = _lnrope_forward(q, k, pos_emb, seq_cutoff, heads_second, norm_eps, kernel_cache)
         ctx.save_for_backward(q, k, pos)
         ctx.cuts, ctx.heads_second, ctx.norm_eps, ctx.kernel_cache = cuts, heads_second, norm_eps, kernel_cache
         return qo, ko
@@ -529,17 +631,18 @@ class FusedRoPEFunc(torch.autograd.Function):
         q, k, pos = ctx.saved_tensors
         _require(not ctx.needs_input_grad[2], "CombinedRoPE does not support gradients in position embeddings")
         dqo, dko = _last_contig(dqo), _last_contig(dko)
-        key = _key(q, k, dqo, dko, pos, extra=("lnrope", bool(ctx.heads_second)))
-        if not _cache_hit(ctx.kernel_cache, "bwd", key):
-            _check_heads([q, k, dqo, dko], "FusedLNRoPE backward", 128)
-            _cache_put(ctx.kernel_cache, "bwd", key)
+        plan = _plan(ctx.kernel_cache, "bwd",
+                     _key(q, k, dqo, dko, pos, extra=("lnrope", bool(ctx.heads_second), ctx.cuts)),
+                     lambda: _check_heads([q, k, dqo, dko], "FusedLNRoPE backward", 128))
         dq, dk = torch.empty_like(dqo), torch.empty_like(dko)
-        _lnrope_launch(q, k, dqo, dko, pos, dq, dk, ctx.cuts, ctx.heads_second, ctx.norm_eps, bwd=True)
+        _lnrope_launch(plan, q, k, dqo, dko, pos, dq, dk, ctx.cuts, ctx.heads_second, ctx.norm_eps, bwd=True)
         return dq, dk, None, None, None, None, None
 
 
 def triton_fused_ln_rope_fn(query, key, pos_emb, seq_cutoff=None, heads_second=True, norm_eps=1e-6,
                             kernel_cache=None):
+    if not _needs_grad(query, key, pos_emb):
+        return _lnrope_forward(query, key, pos_emb, seq_cutoff, heads_second, norm_eps, kernel_cache)[4:]
     return FusedRoPEFunc.apply(query, key, pos_emb, seq_cutoff, heads_second, norm_eps, kernel_cache)
 
 
@@ -586,31 +689,33 @@ def _check_attn(q, k, v) -> None:
         _lib.require_device(t)
 
 
+def _attn_forward(q, k, v, bias, causal, softmax_scale, cache):
+    q, k, v = _last_contig(q), _last_contig(k), _last_contig(v)
+    plan = _plan(cache, "fwd", _key(q, k, v, bias, extra=("attn", bool(causal))), lambda: _check_attn(q, k, v))
+    lib = _lib.load()
+    batch, seqlen_q, nheads, d = q.shape
+    seqlen_k = k.shape[1]
+    softmax_scale = softmax_scale or 1.0 / math.sqrt(d)
+    bias_t, bias_s = _prep_bias(bias, q, seqlen_q, seqlen_k)
+    o = torch.empty_like(q)
+    lse_rows, dt = _const(plan, "c", lambda: (int(lib.rgd_attn_lse_rows(seqlen_q)), _lib.dtype_code(q.dtype)))
+    lse = torch.empty((batch, nheads, lse_rows), device=q.device, dtype=torch.float32)
+    qh, kh, vh, oh = _heads_refs(plan, "h", (q, k, v, o), _attn_heads)
+    with _lib.device_guard(q):
+        code = lib.rgd_attn_fwd(qh, kh, vh, C.byref(bias_s), oh, lse.data_ptr(), batch, nheads, seqlen_q, seqlen_k, d,
+                                float(softmax_scale), 1 if causal else 0, dt, _native_cache(cache), _lib.stream_ptr())
+    if code:
+        _lib.check(code, "attn_fwd")
+    return q, k, v, o, lse, bias_t, softmax_scale
+
+
 class FlashAttnFunc(torch.autograd.Function):
     """softmax(Q K^T * scale + bias) V with O(T) memory
     (flash_attn_triton_cached.py:1079-1129).  Returns (o, lse)."""
 
     @staticmethod
     def forward(ctx, q, k, v, bias=None, causal=False, softmax_scale=None, kernel_cache=None):
-        q, k, v = _last_contig(q), _last_contig(k), _last_contig(v)
-        key = _key(q, k, v, bias, extra=("attn", bool(causal)))
-        if not _cache_hit(kernel_cache, "fwd", key):
-            _check_attn(q, k, v)
-            _cache_put(kernel_cache, "fwd", key)
-        lib = _lib.load()
-        batch, seqlen_q, nheads, d = q.shape
-        seqlen_k = k.shape[1]
-        softmax_scale = softmax_scale or 1.0 / math.sqrt(d)
-        bias_t, bias_s = _prep_bias(bias, q, seqlen_q, seqlen_k)
-        o = torch.empty_like(q)
-        lse = torch.empty((batch, nheads, lib.rgd_attn_lse_rows(seqlen_q)), device=q.device, dtype=torch.float32)
-        with _lib.device_guard(q):
-            code = lib.rgd_attn_fwd(C.byref(_attn_heads(q)), C.byref(_attn_heads(k)), C.byref(_attn_heads(v)),
-                                    C.byref(bias_s), C.byref(_attn_heads(o)), lse.data_ptr(),
-                                    batch, nheads, seqlen_q, seqlen_k, d, float(softmax_scale),
-                                    1 if causal else 0, _lib.dtype_code(q.dtype), _native_cache(kernel_cache),
-                                    _lib.stream_ptr())
-        _lib.check(code, "attn_fwd")
+        q, k, v, o, lse, bias_t, softmax_scale = _attn_forward(q, k, v, bias, causal, softmax_scale, kernel_cache)
         ctx.save_for_backward(q, k, v, o, lse, bias_t)
         ctx.causal, ctx.softmax_scale, ctx.kernel_cache = causal, softmax_scale, kernel_cache
         ctx.mark_non_differentiable(lse)
@@ -621,34 +726,41 @@ class FlashAttnFunc(torch.autograd.Function):
         q, k, v, o, lse, bias = ctx.saved_tensors
         _require(not ctx.needs_input_grad[3], "FlashAttention does not support bias gradient yet")
         do = _last_contig(do)
-        key = _key(q, k, v, do, bias, extra=("attn", bool(ctx.causal)))
-        if not _cache_hit(ctx.kernel_cache, "bwd", key):
-            _require(do.shape == q.shape and do.dtype == q.dtype, "dO must match q")
-            _cache_put(ctx.kernel_cache, "bwd_odot", key)
-            _cache_put(ctx.kernel_cache, "bwd", key)
+        cache = ctx.kernel_cache
+        plan = _plan(cache, "bwd", _key(q, k, v, do, bias, extra=("attn", bool(ctx.causal))),
+                     lambda: _require(do.shape == q.shape and do.dtype == q.dtype, "dO must match q"))
+        if cache is not None:
+            cache.bwd_odot = cache.bwd
         lib = _lib.load()
         batch, seqlen_q, nheads, d = q.shape
         seqlen_k = k.shape[1]
         _, bias_s = _prep_bias(bias, q, seqlen_q, seqlen_k)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        dt = _lib.dtype_code(q.dtype)
+        dt, nbytes = _const(plan, "c", lambda: (_lib.dtype_code(q.dtype), int(lib.rgd_attn_bwd_workspace_bytes(
+            batch, nheads, seqlen_q, seqlen_k, d, _lib.dtype_code(q.dtype)))))
+        _require(nbytes >= 0, "attn_bwd: bad sizes")
+        work = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+        qh, kh, vh, oh, doh, dqh, dkh, dvh = _heads_refs(plan, "h", (q, k, v, o, do, dq, dk, dv), _attn_heads)
         with _lib.device_guard(q):
-            nbytes = lib.rgd_attn_bwd_workspace_bytes(batch, nheads, seqlen_q, seqlen_k, d, dt)
-            _require(nbytes >= 0, "attn_bwd: bad sizes")
-            work = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=q.device)
-            hv = lambda t: C.byref(_attn_heads(t))
-            code = lib.rgd_attn_bwd(hv(q), hv(k), hv(v), C.byref(bias_s), hv(o), lse.data_ptr(), hv(do),
-                                    hv(dq), hv(dk), hv(dv), batch, nheads, seqlen_q, seqlen_k, d,
-                                    float(ctx.softmax_scale), 1 if ctx.causal else 0, dt,
-                                    work.data_ptr(), work.numel(), _native_cache(ctx.kernel_cache),
-                                    _lib.stream_ptr())
-        _lib.check(code, "attn_bwd")
+            code = lib.rgd_attn_bwd(qh, kh, vh, C.byref(bias_s), oh, lse.data_ptr(), doh, dqh, dkh, dvh, batch, nheads,
+                                    seqlen_q, seqlen_k, d, float(ctx.softmax_scale), 1 if ctx.causal else 0, dt,
+                                    work.data_ptr(), work.numel(), _native_cache(cache), _lib.stream_ptr())
+        if code:
+            _lib.check(code, "attn_bwd")
         return dq, dk, dv, None, None, None, None
 
 
 def flash_attn_func(q, k, v, bias=None, causal=False, softmax_scale=None, return_lse=False, kernel_cache=None):
     """q: (batch, seqlen_q, nheads, headdim); k, v: (batch, seqlen_k, nheads,
     headdim); bias: optional, 4-D, last two dims (1, seqlen_k) or (seqlen_q,
-    seqlen_k), leading dims broadcastable to (batch, nheads)."""
-    o, lse = FlashAttnFunc.apply(q, k, v, bias, causal, softmax_scale, kernel_cache)
+    seqlen_k), leading dims broadcastable to (batch, nheads).
+
+    The tensor-memory kernels bound every device-side wait; should one ever run
+    out, the call still returns and the results of that launch are invalid.
+    ``rgd_triton_b200._lib.load().rgd_device_status()`` reports (and clears) that
+    condition; poll it at a point where a device synchronisation is acceptable."""
+    if not _needs_grad(q, k, v, bias):
+        _, _, _, o, lse, _, _ = _attn_forward(q, k, v, bias, causal, softmax_scale, kernel_cache)
+    else:
+        o, lse = FlashAttnFunc.apply(q, k, v, bias, causal, softmax_scale, kernel_cache)
     return (o, lse) if return_lse else o

@@ -56,19 +56,21 @@ class _LaunchCache:
                 pass
 
     # the native handle belongs to this process and this object only
+    # (the marshalled arguments kept under "_plan_*" hold raw pointers: they stay behind too)
     def __getstate__(self):
-        state = dict(vars(self))
+        state = {k: v for k, v in vars(self).items() if not k.startswith("_plan_")}
         state["_native"] = None
         return state
 
     def __deepcopy__(self, memo):
         new = _LaunchCache(())
         for k, v in vars(self).items():
-            setattr(new, k, None if k == "_native" else v)
+            if not k.startswith("_plan_"):
+                setattr(new, k, None if k == "_native" else v)
         return new
 
     def __repr__(self):
-        slots = {k: v for k, v in vars(self).items() if k != "_native"}
+        slots = {k: v for k, v in vars(self).items() if not k.startswith("_")}
         return "LaunchCache(" + ", ".join(f"{k}={'set' if v is not None else None}" for k, v in slots.items()) + ")"
 
 

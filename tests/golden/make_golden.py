@@ -4,7 +4,9 @@ The reference's Triton kernels run on the CPU under Triton's interpreter, so
 this script needs no GPU — but it needs the reference checkout, which exists
 only in the build container:
 
-    TRITON_INTERPRET=1 python -O tests/golden/make_golden.py [/path/to/reference]
+    TRITON_INTERPRET=1 python -O tests/golden/make_golden.py /path/to/reference
+
+(the checkout's path is the one argument, or the RGD_REFERENCE environment variable).
 
 ``-O`` is required because the reference's host wrappers ``assert x.is_cuda``.
 The env var must be set before Triton is imported (this script checks).  Each
@@ -21,7 +23,9 @@ if os.environ.get("TRITON_INTERPRET") != "1":
 if __debug__:
     sys.exit("run with python -O (the reference asserts .is_cuda)")
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2 and not os.environ.get("RGD_REFERENCE"):
+    sys.exit("give the path of the reference checkout as the argument (or in RGD_REFERENCE)")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["RGD_REFERENCE"])
 sys.path.insert(0, str(REF))
 OUT = Path(__file__).resolve().parent
 

@@ -38,19 +38,24 @@ def run_attn(q, k, v, do, bias=None, causal=False, scale=None):
     return o.detach().cpu(), lse.cpu(), dq.cpu(), dk.cpu(), dv.cpu()
 
 
-def check(q, k, v, do, bias=None, causal=False, what=""):
-    o, lse, dq, dk, dv = run_attn(q, k, v, do, bias, causal)
-    eo, elsed = O.attn_fwd(q.float(), k.float(), v.float(), None if bias is None else bias.float(), causal)
-    edq, edk, edv = O.attn_bwd(q.float(), k.float(), v.float(), do.float(), None if bias is None else bias.float(),
-                               causal)
-    lo, ldq, ldk, ldv = O.attn_lowp(q, k, v, do, bias, causal)
+# Additive slack on top of "2x the low-precision eager error": half a unit in the last place of
+# a bf16 value of magnitude ~0.1, so the eager error is what decides, not the slack.
+GRAD_FLOOR = 5e-4
+
+
+def check(q, k, v, do, bias=None, causal=False, what="", scale=None):
+    o, lse, dq, dk, dv = run_attn(q, k, v, do, bias, causal, scale)
+    fb = None if bias is None else bias.float()
+    eo, elsed = O.attn_fwd(q.float(), k.float(), v.float(), fb, causal, scale)
+    edq, edk, edv = O.attn_bwd(q.float(), k.float(), v.float(), do.float(), fb, causal, scale)
+    lo, ldq, ldk, ldv = O.attn_lowp(q, k, v, do, bias, causal, scale)
     tq = q.shape[1]
     torch.testing.assert_close(lse[:, :, :tq], elsed, rtol=1e-3, atol=2e-3, msg=lambda m: f"{what} lse: {m}")
     assert_attn(o, eo, lo, f"{what} o")
-    # gradients: the reference's tests allow up to 5x here for the hardest shapes
-    assert_attn(dq, edq, ldq, f"{what} dq", factor=2.0, floor=2e-3)
-    assert_attn(dk, edk, ldk, f"{what} dk", factor=2.0, floor=2e-3)
-    assert_attn(dv, edv, ldv, f"{what} dv", factor=2.0, floor=2e-3)
+    # the reference's own tests allow 2x (out) and up to 5x (gradients); 2x is asked of all four here
+    assert_attn(dq, edq, ldq, f"{what} dq", factor=2.0, floor=GRAD_FLOOR)
+    assert_attn(dk, edk, ldk, f"{what} dk", factor=2.0, floor=GRAD_FLOOR)
+    assert_attn(dv, edv, ldv, f"{what} dv", factor=2.0, floor=GRAD_FLOOR)
 
 
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
@@ -65,20 +70,111 @@ def test_no_bias(dt, d, causal):
         check(q, k, v, do, None, causal, f"d={d} ({tq},{tk}) causal={causal}")
 
 
+BIAS_KINDS = ["vector", "matrix", "matrix_bcast_b", "matrix_bcast_h", "vector_bcast", "matrix_f32"]
+
+
+def make_bias(g, kind, B, H, tq, tk, dtype):
+    shape = {"vector": (B, H, 1, tk), "matrix": (B, H, tq, tk), "matrix_bcast_b": (1, H, tq, tk),
+             "matrix_bcast_h": (B, 1, tq, tk), "vector_bcast": (1, 1, 1, tk), "matrix_f32": (B, H, tq, tk)}[kind]
+    return randn(g, *shape, dtype=torch.float32 if kind == "matrix_f32" else dtype)
+
+
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
-@pytest.mark.parametrize("d", [64, 128])
-@pytest.mark.parametrize("kind", ["vector", "matrix", "matrix_bcast_b", "matrix_bcast_h", "vector_bcast", "matrix_f32"])
+@pytest.mark.parametrize("d", [64, 128, 32, 40, 96])
+@pytest.mark.parametrize("kind", BIAS_KINDS)
 def test_bias(dt, d, kind):
+    """Every bias kind on the tensor-memory kernels (d = 64, 128) and on the general
+    kernels (d = 32, 40, 96; the reference's own grid is bias kind x d in {32, 64},
+    tests/test_flash_attn.py:70-73)."""
     dtype = DTYPES[dt]
     g = gen(d + len(kind))
     B, H = 2, 3
     for tq, tk in [(113, 203), (128, 217), (256, 512), (3, 1023)]:
         q, k, v = randn(g, B, tq, H, d, dtype=dtype), randn(g, B, tk, H, d, dtype=dtype), randn(g, B, tk, H, d, dtype=dtype)
         do = randn(g, B, tq, H, d, dtype=dtype)
-        shape = {"vector": (B, H, 1, tk), "matrix": (B, H, tq, tk), "matrix_bcast_b": (1, H, tq, tk),
-                 "matrix_bcast_h": (B, 1, tq, tk), "vector_bcast": (1, 1, 1, tk), "matrix_f32": (B, H, tq, tk)}[kind]
-        bias = randn(g, *shape, dtype=torch.float32 if kind == "matrix_f32" else dtype)
+        bias = make_bias(g, kind, B, H, tq, tk, dtype)
         check(q, k, v, do, bias, False, f"{kind} d={d} ({tq},{tk})")
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("d", [64, 128, 32, 96])
+@pytest.mark.parametrize("kind", ["vector", "matrix", "matrix_bcast_b", "matrix_f32"])
+def test_causal_with_bias(dt, d, kind):
+    """The causal mask together with a bias, on both kernel families."""
+    dtype = DTYPES[dt]
+    g = gen(3 * d + len(kind))
+    B, H = 2, 2
+    for tq, tk in [(113, 203), (256, 256), (200, 136), (384, 640)]:
+        q, k, v = randn(g, B, tq, H, d, dtype=dtype), randn(g, B, tk, H, d, dtype=dtype), randn(g, B, tk, H, d, dtype=dtype)
+        do = randn(g, B, tq, H, d, dtype=dtype)
+        bias = make_bias(g, kind, B, H, tq, tk, dtype)
+        check(q, k, v, do, bias, True, f"causal {kind} d={d} ({tq},{tk})")
+
+
+def _uses_tmem_fwd(q, k, v):
+    import ctypes as C
+    from rgd_triton_b200 import _lib
+    hv = lambda t: C.byref(F_._attn_heads(t))
+    o = torch.empty_like(q)
+    return _lib.load().rgd_attn_fwd_uses_tmem(hv(q), hv(k), hv(v), hv(o), q.shape[0], q.shape[2], q.shape[1],
+                                              k.shape[1], q.shape[3], 1.0, _lib.dtype_code(q.dtype))
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("kind", [None, "matrix", "vector"])
+def test_misaligned_views_take_the_general_kernels(d, kind):
+    """q, k, v as channel slices [3 : 3 + d] of wider tensors: rows are not 16-byte
+    addressable, so the call must leave the tensor-memory kernels and still be right."""
+    g = gen(70 + d)
+    B, H, tq, tk = 2, 2, 150, 217
+    wide = [randn(g, B, n, H, d + 8, dtype=torch.bfloat16) for n in (tq, tk, tk)]
+    q, k, v = (w[..., 3:3 + d] for w in wide)
+    do = randn(g, B, tq, H, d, dtype=torch.bfloat16)
+    bias = None if kind is None else make_bias(g, kind, B, H, tq, tk, torch.bfloat16)
+    qd, kd, vd = (w.cuda()[..., 3:3 + d] for w in wide)
+    assert _uses_tmem_fwd(qd, kd, vd) == 0
+    assert _uses_tmem_fwd(qd.contiguous(), kd.contiguous(), vd.contiguous()) == 1
+    qd, kd, vd = (t.requires_grad_(True) for t in (qd, kd, vd))
+    o = F_.flash_attn_func(qd, kd, vd, None if bias is None else bias.cuda())
+    dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), do.cuda())
+    fb = None if bias is None else bias.float()
+    eo, _ = O.attn_fwd(q.float(), k.float(), v.float(), fb)
+    edq, edk, edv = O.attn_bwd(q.float(), k.float(), v.float(), do.float(), fb)
+    lo, ldq, ldk, ldv = O.attn_lowp(q, k, v, do, bias)
+    assert_attn(o, eo, lo, "o")
+    assert_attn(dq, edq, ldq, "dq", floor=GRAD_FLOOR)
+    assert_attn(dk, edk, ldk, "dk", floor=GRAD_FLOOR)
+    assert_attn(dv, edv, ldv, "dv", floor=GRAD_FLOOR)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_batch_expanded_keys_and_values(d):
+    """k and v expanded over the batch (stride 0): no tensor map describes that, the call
+    runs on the general kernels instead of failing."""
+    g = gen(90 + d)
+    B, H, tq, tk = 3, 2, 140, 200
+    q, do = randn(g, B, tq, H, d, dtype=torch.float16), randn(g, B, tq, H, d, dtype=torch.float16)
+    k1, v1 = randn(g, 1, tk, H, d, dtype=torch.float16), randn(g, 1, tk, H, d, dtype=torch.float16)
+    k, v = k1.expand(B, -1, -1, -1), v1.expand(B, -1, -1, -1)
+    qd = q.cuda().requires_grad_(True)
+    kd, vd = k1.cuda().expand(B, -1, -1, -1), v1.cuda().expand(B, -1, -1, -1)
+    assert _uses_tmem_fwd(qd, kd, vd) == 0
+    o = F_.flash_attn_func(qd, kd, vd)
+    (dq,) = torch.autograd.grad(o, (qd,), do.cuda())
+    eo, _ = O.attn_fwd(q.float(), k.float(), v.float())
+    edq, _, _ = O.attn_bwd(q.float(), k.float(), v.float(), do.float())
+    lo, ldq, _, _ = O.attn_lowp(q, k, v, do)
+    assert_attn(o, eo, lo, "o")
+    assert_attn(dq, edq, ldq, "dq", floor=GRAD_FLOOR)
+
+
+@pytest.mark.parametrize("d", [64, 32])
+def test_negative_softmax_scale(d):
+    """The reference accepts any scale; a negative one must not reach the forward fast
+    path that takes the block maximum before scaling."""
+    g = gen(5 + d)
+    q, k, v, do = (randn(g, 2, 160, 2, d, dtype=torch.bfloat16) for _ in range(4))
+    check(q, k, v, do, None, False, f"negative scale d={d}", scale=-0.2)
 
 
 def test_block_mask_bias_like_config4():
@@ -137,9 +233,9 @@ def test_noncontiguous_inputs_and_grad():
     edq, edk, edv = O.attn_bwd(q.float(), k.float(), v.float(), do.float())
     lo, ldq, ldk, ldv = O.attn_lowp(q, k, v, do)
     assert_attn(o, eo, lo, "o")
-    assert_attn(dq, edq, ldq, "dq", floor=2e-3)
-    assert_attn(dk, edk, ldk, "dk", floor=2e-3)
-    assert_attn(dv, edv, ldv, "dv", floor=2e-3)
+    assert_attn(dq, edq, ldq, "dq", floor=GRAD_FLOOR)
+    assert_attn(dk, edk, ldk, "dk", floor=GRAD_FLOOR)
+    assert_attn(dv, edv, ldv, "dv", floor=GRAD_FLOOR)
 
 
 def test_backward_overflow_small_seqlens():
@@ -196,43 +292,71 @@ def test_long_sequences_steady_state_pipeline(d, causal):
             assert all(torch.equal(a, b) for a, b in zip(first, cur))
 
 
-def _one_head_check(q, k, v, do, bias, b, h, what):
-    """Exact fp32 oracle on one (batch, head) of a large problem."""
-    sl = lambda t: t[b:b + 1, :, h:h + 1]
-    bsl = None if bias is None else bias[(b if bias.shape[0] > 1 else 0):(b if bias.shape[0] > 1 else 0) + 1,
-                                         (h if bias.shape[1] > 1 else 0):(h if bias.shape[1] > 1 else 0) + 1]
-    return sl(q), sl(k), sl(v), sl(do), bsl
-
-
-@pytest.mark.parametrize("cfg", ["config3", "config4"])
-def test_benchmark_configurations_full_size(cfg):
-    """Third / fourth benchmark configurations at full size; the exact oracle
-    is evaluated for two (batch, head) pairs, and linearity in dO is checked
-    on the whole tensor."""
-    g = gen(0)
-    if cfg == "config3":
-        B, Tn, H, d, dtype = 4, 4096, 16, 128, torch.bfloat16
-        bias = None
-    else:
-        B, Tn, H, d, dtype = 2, 4096, 24, 64, torch.float16
-        bias = randn(g, 1, H, Tn, Tn)
-        blk = (torch.rand(1, H, 64, 64, generator=g) < 0.1) & ~torch.eye(64, dtype=torch.bool)
-        bias = (bias - 1e4 * blk.repeat_interleave(64, 2).repeat_interleave(64, 3)).to(dtype)
-    q, k, v, do = (randn(g, B, Tn, H, d, dtype=dtype) for _ in range(4))
-    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
-    bd = None if bias is None else bias.cuda()
-    o = F_.flash_attn_func(qd, kd, vd, bd)
-    dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), do.cuda(), retain_graph=True)
-    for b, h in ((0, 0), (B - 1, H - 1)):
-        sq, sk, sv, sdo, sb = _one_head_check(q, k, v, do, bias, b, h, cfg)
-        eo, _ = O.attn_fwd(sq.float(), sk.float(), sv.float(), None if sb is None else sb.float())
-        edq, edk, edv = O.attn_bwd(sq.float(), sk.float(), sv.float(), sdo.float(), None if sb is None else sb.float())
+def _check_sampled_heads(cfg, q, k, v, do, bias_dev, o, grads, pairs):
+    """Exact fp32 oracle on a few (batch, head) pairs of a full-size problem; the bias slice
+    of each pair is brought back from the device, so oracle and kernel see the same bits."""
+    dq, dk, dv = grads
+    for b, h in pairs:
+        sq, sk, sv, sdo = (t[b:b + 1, :, h:h + 1] for t in (q, k, v, do))
+        sb = None
+        if bias_dev is not None:
+            bb = b if bias_dev.shape[0] > 1 else 0
+            hh = h if bias_dev.shape[1] > 1 else 0
+            sb = bias_dev[bb:bb + 1, hh:hh + 1].cpu()
+        fb = None if sb is None else sb.float()
+        eo, _ = O.attn_fwd(sq.float(), sk.float(), sv.float(), fb)
+        edq, edk, edv = O.attn_bwd(sq.float(), sk.float(), sv.float(), sdo.float(), fb)
         lo, ldq, ldk, ldv = O.attn_lowp(sq, sk, sv, sdo, sb)
         sl = lambda t: t.detach().cpu()[b:b + 1, :, h:h + 1]
         assert_attn(sl(o), eo, lo, f"{cfg} o[{b},{h}]")
-        assert_attn(sl(dq), edq, ldq, f"{cfg} dq[{b},{h}]", floor=2e-3)
-        assert_attn(sl(dk), edk, ldk, f"{cfg} dk[{b},{h}]", floor=2e-3)
-        assert_attn(sl(dv), edv, ldv, f"{cfg} dv[{b},{h}]", floor=2e-3)
+        assert_attn(sl(dq), edq, ldq, f"{cfg} dq[{b},{h}]", floor=GRAD_FLOOR)
+        assert_attn(sl(dk), edk, ldk, f"{cfg} dk[{b},{h}]", floor=GRAD_FLOOR)
+        assert_attn(sl(dv), edv, ldv, f"{cfg} dv[{b},{h}]", floor=GRAD_FLOOR)
+
+
+def _block_mask_bias(Bb, H, Tn, dtype, seed):
+    """N(0,1) plus -1e4 on 64x64 blocks chosen Bernoulli(0.1), diagonal blocks kept: the bias
+    of the fourth benchmark configuration, generated on the device (1.6 GB at full size)."""
+    gd = torch.Generator(device="cuda").manual_seed(seed)
+    bias = torch.randn(Bb, H, Tn, Tn, device="cuda", generator=gd, dtype=torch.float32).to(dtype)
+    nb = Tn // 64
+    blk = (torch.rand(Bb, H, nb, nb, device="cuda", generator=gd) < 0.1) & ~torch.eye(nb, dtype=torch.bool, device="cuda")
+    bias.view(Bb, H, nb, 64, nb, 64).masked_fill_(blk[:, :, :, None, :, None], -1e4)
+    return bias
+
+
+@pytest.mark.parametrize("cfg", ["config3", "config4_full_bias", "config4_broadcast_bias", "config5_attention"])
+def test_benchmark_configurations_full_size(cfg):
+    """Third, fourth and fifth benchmark configurations' attention at full (per-GPU) size.
+    The exact oracle is evaluated for sampled (batch, head) pairs, and linearity in dO is
+    checked on the whole tensors."""
+    g = gen(0)
+    pairs = None
+    if cfg == "config3":
+        B, Tn, H, d, dtype = 4, 4096, 16, 128, torch.bfloat16
+        bias = None
+    elif cfg.startswith("config4"):
+        B, Tn, H, d, dtype = 2, 4096, 24, 64, torch.float16
+        bias = _block_mask_bias(2 if cfg == "config4_full_bias" else 1, H, Tn, dtype, 4)
+    else:
+        # MMDiT joint attention, one GPU's share of the batch: 4096 image tokens then 512 text
+        # tokens, keys of padded text positions masked by -1e4 in a dense (B, h, T, T) bias
+        B, Tn, H, d, dtype = 2, 4608, 24, 128, torch.bfloat16
+        text_len = [64, 389]                         # the shortest allowed length and a typical one
+        bias = torch.zeros(B, H, Tn, Tn, device="cuda", dtype=dtype)
+        for b, L in enumerate(text_len):
+            bias[b, :, :, 4096 + L:] = -1e4
+        pairs = ((0, 0), (1, H - 1), (0, 11))
+    pairs = pairs or ((0, 0), (B - 1, H - 1))
+    q, k, v, do = (randn(g, B, Tn, H, d, dtype=dtype) for _ in range(4))
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o = F_.flash_attn_func(qd, kd, vd, bias)
+    dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), do.cuda(), retain_graph=True)
+    _check_sampled_heads(cfg, q, k, v, do, bias, o, (dq, dk, dv), pairs)
+    if cfg == "config5_attention":
+        # masked keys get no gradient and contribute nothing
+        for b, L in enumerate(text_len):
+            assert torch.count_nonzero(dk[b, 4096 + L:]) == 0 and torch.count_nonzero(dv[b, 4096 + L:]) == 0
     # linearity of the backward in dO: scaling dO by a power of two scales every
     # gradient by it — exactly in bf16; in fp16 up to subnormal rounding of dS
     dq2, dk2, dv2 = torch.autograd.grad(o, (qd, kd, vd), 2 * do.cuda())
@@ -241,3 +365,20 @@ def test_benchmark_configurations_full_size(cfg):
             assert torch.equal((2 * a.float()).to(a.dtype), b2)
         else:
             torch.testing.assert_close(2 * a.float(), b2.float(), rtol=2e-3, atol=2e-4)
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A device-side wait that nothing ever satisfies ends after its time limit, the kernel
+    returns normally, and the status word reports the time-out exactly once."""
+    from rgd_triton_b200 import _lib
+    lib = _lib.load()
+    assert lib.rgd_device_status() == 0
+    assert lib.rgd_selftest_bounded_wait(0, None) == _lib.RGD_E_INVALID          # limit outside 1 us .. 100 ms
+    assert lib.rgd_selftest_bounded_wait(1_000_000, torch.cuda.current_stream().cuda_stream) == 0   # 1 ms
+    torch.cuda.synchronize()
+    assert lib.rgd_device_status() == _lib.RGD_E_TIMEOUT
+    assert lib.rgd_device_status() == 0
+    # the context is intact: an attention call right after works and leaves the status clear
+    g = gen(12)
+    q, k, v, do = (randn(g, 1, 256, 2, 64, dtype=torch.bfloat16) for _ in range(4))
+    check(q, k, v, do, None, False, "after time-out")

@@ -57,6 +57,34 @@ def test_rmsnorm_per_batch_and_mixed_weight_dtype(dt, wdt):
         assert_parity(dw, odw, f"dw {wshape}", atol_rel=1e-5)
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("per_batch", [False, True])
+def test_weight_views_that_are_not_16_byte_addressable(dt, per_batch):
+    """Rows of 3072 (16-bit) / 1024 (fp32) channels normally run on the kernel that reads the
+    weight with 16-byte loads.  A weight that starts one element into a larger buffer, or
+    per-batch weights whose batch stride is odd, must take the other kernel and still match."""
+    dtype = DTYPES[dt]
+    C = 3072 if dt == "bf16" else 1024
+    g = gen(C + int(per_batch))
+    B, N = 2, 70
+    x, dy = randn(g, B, N, C, dtype=dtype), randn(g, B, N, C, dtype=dtype)
+    if per_batch:
+        wbuf = (1 + 0.02 * torch.randn(B, 1, C + 3, generator=g)).to(dtype)        # batch stride C + 3
+        w = wbuf[:, :, 1:C + 1]
+    else:
+        wbuf = (1 + 0.02 * torch.randn(C + 8, generator=g)).to(dtype)
+        w = wbuf[1:C + 1]
+    xd = x.cuda().requires_grad_(True)
+    wd = (wbuf.cuda()[:, :, 1:C + 1] if per_batch else wbuf.cuda()[1:C + 1]).requires_grad_(True)
+    assert wd.data_ptr() % 16 != 0
+    y = F_.triton_rms_func_fn(xd, wd, 1e-6)
+    dx, dw = torch.autograd.grad(y, (xd, wd), dy.cuda())
+    assert_parity(y.detach().cpu(), O.rmsnorm_fwd(x, w, 1e-6), "y")
+    odx, odw = O.rmsnorm_bwd(x, w, dy, 1e-6)
+    assert_parity(dx.cpu(), odx, "dx", atol_rel=1e-5)
+    assert_parity(dw.cpu(), odw.reshape(dw.shape), "dw", atol_rel=2e-5)
+
+
 @pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("n1,n2,c1,c2", [(97, 97, 128, 128), (1023, 1024, 257, 514), (108, 256, 740, 370),
                                           (512, 4096, 3072, 3072), (14, 31, 63, 32)])
