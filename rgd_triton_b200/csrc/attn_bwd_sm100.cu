@@ -33,7 +33,7 @@ using namespace rgd::sm100;
 
 int *tmem_status_ptr();   // attn_fwd_sm100.cu
 bool bias_tma_ok(const AttnParams &p);
-int encode_bias_map(rgd_cache *cache, CUtensorMap *out, const AttnParams &p, bool bf16);
+int encode_bias_map(rgd_cache *cache, CUtensorMap *out, const AttnParams &p, bool bf16, int box_q);
 
 constexpr int BWD_THREADS = 320;
 constexpr int DKDV_SUB_THREADS = 384;   // 8 compute warps, TMA producer, three MMA issuers
@@ -47,6 +47,7 @@ struct BwdTmaParams {
     int64_t b_sb, b_sh, b_sq;
     int bias_kind, bias_f32, bias_vec;
     CUtensorMap mbias;                  // BIAS == 2: (Tk, Tq, H or 1, B or 1) map over the bias, box 64 x 128
+    CUtensorMap mbias64;                // the same tensor with box 64 keys x 64 queries (dK/dV sub-blocks)
     int bias_h0, bias_b0;               // bias broadcast over heads / batch: coordinate 0
     const float *lse2, *delta_s;        // [B, H, Tq128]: lse * log2(e) (+inf past Tq), delta * scale (0 past Tq)
     int H, Tq, Tk, Tq128, causal;
@@ -531,20 +532,31 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_tmem(const __grid_con
 // GEMMs of sub-block u-1 and the score GEMMs of sub-block u+1, so the exponentials
 // leave the critical path (at the price of N = 64 score GEMMs).
 // ---------------------------------------------------------------------------
-template <int D>
+// BIAS: a matrix bias in the tensor dtype, staged by TMA as one 64-query x 128-key sub-tile per
+// sub-block (two 64-key panels, 128-byte swizzle); stage b belongs to the compute group that
+// owns sub-blocks of parity b, which frees it for the next block as soon as its P is formed.
+// With head_dim 128 and a bias the row statistics are not staged (shared memory is full):
+// they are read from global memory, where every warp reads the same cached words.
+template <int D, bool BIAS>
 struct alignas(1024) DkdvSubSmem {
+    static constexpr bool STAGE_STATS = !(BIAS && D == 128);
     unsigned char x1[BT * D * 2], x2[BT * D * 2];            // K, V
     unsigned char y1[2][BT * D * 2], y2[2][BT * D * 2];      // Q, dO, 2 stages
-    alignas(16) float lse_s[2][BT], dsc_s[2][BT];            // row statistics of the staged query block
+    unsigned char bias[BIAS ? 2 : 1][BIAS ? 64 * BT * 2 : 1024];
+    alignas(16) float lse_s[2][STAGE_STATS ? BT : 4], dsc_s[2][STAGE_STATS ? BT : 4];   // row statistics of the staged query block
     uint64_t x_full, acc_full;
     uint64_t y_full[2], y_empty[2];
     uint64_t g1_full[2], g2_full[2], p_ready[2], ds_ready[2];   // per sub-block parity
     uint64_t g1_free[2], g2_free[2];                            // accumulation GEMM has read P / dS
+    uint64_t bb_full[2], bb_empty[2];                           // bias sub-tile of parity b
     uint32_t tmem_base;
 };
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const __grid_constant__ BwdTmaParams p) {
+    using Smem = DkdvSubSmem<D, BIAS>;
+    constexpr bool STAGE_STATS = Smem::STAGE_STATS;
+    constexpr uint32_t BIAS_BYTES = 64 * BT * 2;
     constexpr int HALVES = D / 64;
     constexpr uint32_t PANEL = 128 * 64 * 2;
     constexpr uint32_t TILE_BYTES = BT * D * 2;
@@ -554,7 +566,7 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
 
     extern __shared__ unsigned char smem_raw[];
-    DkdvSubSmem<D> &sm = *reinterpret_cast<DkdvSubSmem<D> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int blk = blockIdx.x, bh = blockIdx.y;
@@ -578,6 +590,8 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
             mbar_init(&sm.g2_free[s], 1);
             mbar_init(&sm.p_ready[s], 128);
             mbar_init(&sm.ds_ready[s], 128);
+            mbar_init(&sm.bb_full[s], 1);
+            mbar_init(&sm.bb_empty[s], 128);
         }
         fence_mbar_init();
     }
@@ -597,6 +611,7 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
             tma_prefetch_desc(&p.mv);
             tma_prefetch_desc(&p.mq);
             tma_prefetch_desc(&p.mdo);
+            if constexpr (BIAS) tma_prefetch_desc(&p.mbias64);
             mbar_expect_tx(&sm.x_full, 2 * TILE_BYTES);
             for (int hh = 0; hh < HALVES; ++hh) {
                 tma_load_4d(sm.x1 + hh * PANEL, &p.mk, &sm.x_full, hh * 64, r0, h, b);
@@ -608,13 +623,27 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 const uint32_t ph = (uint32_t)(it >> 1) & 1u;
                 ok = mbar_wait(&sm.y_empty[s], ph ^ 1u, status, 71);
                 if (!ok) break;
-                mbar_expect_tx(&sm.y_full[s], 2 * TILE_BYTES + 2 * BT * 4);
+                mbar_expect_tx(&sm.y_full[s], 2 * TILE_BYTES + (STAGE_STATS ? 2 * BT * 4 : 0));
                 const int row = (i_begin + it) * BT;
-                bulk_load_1d(sm.lse_s[s], p.lse2 + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
-                bulk_load_1d(sm.dsc_s[s], p.delta_s + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
+                if constexpr (STAGE_STATS) {
+                    bulk_load_1d(sm.lse_s[s], p.lse2 + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
+                    bulk_load_1d(sm.dsc_s[s], p.delta_s + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
+                }
                 for (int hh = 0; hh < HALVES; ++hh) {
                     tma_load_4d(sm.y1[s] + hh * PANEL, &p.mq, &sm.y_full[s], hh * 64, row, h, b);
                     tma_load_4d(sm.y2[s] + hh * PANEL, &p.mdo, &sm.y_full[s], hh * 64, row, h, b);
+                }
+                if constexpr (BIAS) {
+                    // sub-tile of sub-block parity sb: queries row + 64 sb .. + 63, keys r0 .. r0 + 127
+                    for (int sb = 0; sb < 2 && ok; ++sb) {
+                        ok = mbar_wait(&sm.bb_empty[sb], ((uint32_t)it & 1u) ^ 1u, status, 72);
+                        if (!ok) break;
+                        mbar_expect_tx(&sm.bb_full[sb], BIAS_BYTES);
+                        for (int pn = 0; pn < 2; ++pn)
+                            tma_load_4d(sm.bias[sb] + pn * (64 * 128), &p.mbias64, &sm.bb_full[sb], r0 + pn * 64,
+                                        row + sb * 64, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                    }
+                    if (!ok) break;
                 }
             }
             if (!ok)
@@ -723,13 +752,38 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
             const int c0 = blk0 + sb * 64;                 // first query of the sub-block
             const bool slow = cta_key_tail || (p.causal && blk0 == r0);
             const int s = it & 1;
-            const float4 *lse4 = reinterpret_cast<const float4 *>(&sm.lse_s[s][sb * 64]);
-            const float4 *dsc4 = reinterpret_cast<const float4 *>(&sm.dsc_s[s][sb * 64]);
+            // row statistics of this sub-block's 64 queries: staged in shared memory, else from global
+            const float *lse_f = STAGE_STATS ? &sm.lse_s[s][sb * 64] : p.lse2 + (int64_t)bh * p.Tq128 + c0;
+            const float *dsc_f = STAGE_STATS ? &sm.dsc_s[s][sb * 64] : p.delta_s + (int64_t)bh * p.Tq128 + c0;
+            const float4 *lse4 = reinterpret_cast<const float4 *>(lse_f);
+            const float4 *dsc4 = reinterpret_cast<const float4 *>(dsc_f);
             float pv[64];
 
             // row statistics of this block have landed
             ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
             if (!ok) break;
+            // x0[i] = bias * log2(e) - lse * log2(e) of query i (only -lse without a bias), formed
+            // before the scores are waited for
+            float x0[BIAS ? 64 : 1];
+            if constexpr (BIAS) {
+                ok = mbar_wait(&sm.bb_full[sb], (uint32_t)it & 1u, status, 94);
+                if (!ok) break;
+                // this thread's key column of the sub-tile: panel = key / 64, 16-byte chunk index
+                // XOR (query mod 8) inside the 128-byte row of query i
+                const unsigned char *colp = sm.bias[sb] + (row_l >> 6) * (64 * 128) + (row_l & 7) * 2;
+                const int kc = (row_l & 63) >> 3;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float4 l = lse4[i];
+                    const float lv[4] = {l.x, l.y, l.z, l.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int qi = 4 * i + e;
+                        const float bvl = to_f32<T>(*reinterpret_cast<const T *>(colp + qi * 128 + ((kc ^ (qi & 7)) << 4)));
+                        x0[qi] = fmaf(bvl, LOG2E, -lv[e]);
+                    }
+                }
+            }
             ok = mbar_wait(&sm.g1_full[sb], par, status, 91);
             if (!ok) break;
             tc_fence_after_sync();
@@ -739,30 +793,38 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 tmem_ld32(lane_base + G1_COL + col + 32, rb);
                 tmem_wait_ld();
                 if (!slow) {
+                    if constexpr (BIAS) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 l = lse4[i];
-                        pv[4 * i + 0] = ex2b(fmaf(__uint_as_float(ra[4 * i + 0]), p.scale_log2, -l.x));
-                        pv[4 * i + 1] = ex2b(fmaf(__uint_as_float(ra[4 * i + 1]), p.scale_log2, -l.y));
-                        pv[4 * i + 2] = ex2b(fmaf(__uint_as_float(ra[4 * i + 2]), p.scale_log2, -l.z));
-                        pv[4 * i + 3] = ex2b(fmaf(__uint_as_float(ra[4 * i + 3]), p.scale_log2, -l.w));
-                    }
+                        for (int i = 0; i < 32; ++i) {
+                            pv[i] = ex2b(fmaf(__uint_as_float(ra[i]), p.scale_log2, x0[i]));
+                            pv[32 + i] = ex2b(fmaf(__uint_as_float(rb[i]), p.scale_log2, x0[32 + i]));
+                        }
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 l = lse4[8 + i];
-                        pv[32 + 4 * i + 0] = ex2b(fmaf(__uint_as_float(rb[4 * i + 0]), p.scale_log2, -l.x));
-                        pv[32 + 4 * i + 1] = ex2b(fmaf(__uint_as_float(rb[4 * i + 1]), p.scale_log2, -l.y));
-                        pv[32 + 4 * i + 2] = ex2b(fmaf(__uint_as_float(rb[4 * i + 2]), p.scale_log2, -l.z));
-                        pv[32 + 4 * i + 3] = ex2b(fmaf(__uint_as_float(rb[4 * i + 3]), p.scale_log2, -l.w));
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 l = lse4[i];
+                            pv[4 * i + 0] = ex2b(fmaf(__uint_as_float(ra[4 * i + 0]), p.scale_log2, -l.x));
+                            pv[4 * i + 1] = ex2b(fmaf(__uint_as_float(ra[4 * i + 1]), p.scale_log2, -l.y));
+                            pv[4 * i + 2] = ex2b(fmaf(__uint_as_float(ra[4 * i + 2]), p.scale_log2, -l.z));
+                            pv[4 * i + 3] = ex2b(fmaf(__uint_as_float(ra[4 * i + 3]), p.scale_log2, -l.w));
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 l = lse4[8 + i];
+                            pv[32 + 4 * i + 0] = ex2b(fmaf(__uint_as_float(rb[4 * i + 0]), p.scale_log2, -l.x));
+                            pv[32 + 4 * i + 1] = ex2b(fmaf(__uint_as_float(rb[4 * i + 1]), p.scale_log2, -l.y));
+                            pv[32 + 4 * i + 2] = ex2b(fmaf(__uint_as_float(rb[4 * i + 2]), p.scale_log2, -l.z));
+                            pv[32 + 4 * i + 3] = ex2b(fmaf(__uint_as_float(rb[4 * i + 3]), p.scale_log2, -l.w));
+                        }
                     }
                 } else {
-                    const float *lf = &sm.lse_s[s][sb * 64];
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
                         const int qi = c0 + i;
                         const bool masked = row >= p.Tk || qi >= p.Tq || (p.causal && row > qi);
                         const float sv = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]);
-                        pv[i] = masked ? 0.f : ex2b(fmaf(sv, p.scale_log2, -lf[i]));
+                        const float off = BIAS ? x0[BIAS ? i : 0] : -lse_f[i];
+                        pv[i] = masked ? 0.f : ex2b(fmaf(sv, p.scale_log2, off));
                     }
                 }
                 uint32_t pk[32];
@@ -771,6 +833,8 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 tmem_st32(lane_base + G1_COL + col, pk);
                 tmem_wait_st();
             }
+            // P, which depends on every bias value read above, is stored: the bias stage is free
+            if constexpr (BIAS) mbar_arrive(&sm.bb_empty[sb]);
             tc_fence_before_sync();
             mbar_arrive(&sm.p_ready[sb]);
 
@@ -1164,6 +1228,343 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
 }
 
 // ---------------------------------------------------------------------------
+// dQ with a matrix bias staged by TMA.  One CTA per 128-query tile, looping over key blocks:
+//   S = Q K^T, dP = dO V^T, P = exp2(S * scale * log2e + bias * log2e - lse2) in registers,
+//   dS = P * (dP * scale - delta_s) packed into the dP columns, dQ += dS K.
+// All three GEMMs take their A operand from TENSOR MEMORY: Q and dO, which are the same for
+// every key block, are written there once (packed 16-bit pairs) by the compute threads, straight
+// from global memory, so the Q / dO tiles need no shared memory and two 128 x 128 bias tiles
+// fit beside the K and V rings.
+// Tensor memory (512 columns): S at 0, dP / dS at 128, dQ accumulator at 256, Q at 384, dO at 448.
+// S and dP are single-buffered; the loop keeps the tensor pipe fed like this:
+//   compute, block it:  dS(it) from P(it) (registers) and dP(it)            -> ds_ready
+//                       P(it+1) from S(it+1) and bias tile it+1, registers  -> s_read   (while the
+//                       pipe runs dQ(it), dP(it+1) and S(it+2))
+//   issuer A:           dP(j) once dQ(j-1) has been issued (MMAs run in issue order, so it reads
+//                       dS before dP(j) overwrites it); S(j) once S(j-1) has been read
+//   issuer B:           dQ(j) once dS(j) is in place; all dQ MMAs come from this one thread, in
+//                       block order, so the order of the floating-point sums is fixed.
+// A bias stage is handed back when dS of its block has been stored (every value read from the
+// stage has been consumed by then).
+// ---------------------------------------------------------------------------
+template <int D>
+struct alignas(1024) DqBiasSmem {
+    unsigned char k[3][BT * D * 2], v[2][BT * D * 2];
+    unsigned char bias[2][BT * BT * 2];
+    uint64_t a_ready, g1_full, g2_full, s_read, ds_ready, g2_free, acc_full;
+    uint64_t k_full[3], k_empty[3], v_full[2], v_empty[2], bb_full[2], bb_empty[2];
+    uint32_t tmem_base;
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __grid_constant__ BwdTmaParams p,
+                                                                       const void *q_base, const void *do_base,
+                                                                       int64_t q_sb, int64_t q_sh, int64_t q_sn,
+                                                                       int64_t do_sb, int64_t do_sh, int64_t do_sn) {
+    constexpr int HALVES = D / 64;
+    constexpr uint32_t PANEL = 128 * 64 * 2;
+    constexpr uint32_t TILE_BYTES = BT * D * 2;
+    constexpr uint32_t BIAS_BYTES = BT * BT * 2;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t G1_COL = 0, G2_COL = 128, ACC_COL = 256, QA_COL = 384, DOA_COL = 448;
+    constexpr int ACOLS = D / 4;                           // packed columns each compute thread fills per operand
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+
+    extern __shared__ unsigned char smem_raw[];
+    DqBiasSmem<D> &sm = *reinterpret_cast<DqBiasSmem<D> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blk = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / p.H, h = bh - b * p.H;
+    const int r0 = blk * BT;                               // first query of this CTA
+    const int i_end = ((p.causal ? min(p.Tk, r0 + BT) : p.Tk) + BT - 1) / BT;
+    const int nit = max(i_end, 0);
+    int *status = p.status;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.a_ready, 256);
+        mbar_init(&sm.g1_full, 1);
+        mbar_init(&sm.g2_full, 1);
+        mbar_init(&sm.s_read, 256);
+        mbar_init(&sm.ds_ready, 256);
+        mbar_init(&sm.g2_free, 1);
+        mbar_init(&sm.acc_full, 1);
+        for (int s = 0; s < 3; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
+            mbar_init(&sm.bb_full[s], 1);
+            mbar_init(&sm.bb_empty[s], 256);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&sm.tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tbase = sm.tmem_base;
+
+    if (warp == 8) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0 && nit > 0) {
+            tma_prefetch_desc(&p.mk);
+            tma_prefetch_desc(&p.mv);
+            tma_prefetch_desc(&p.mbias);
+            bool ok = true;
+            int ks = 0;
+            uint32_t kph = 0;                              // phase of the K ring slot's previous use
+            for (int it = 0; it < nit; ++it) {
+                const int row = it * BT;
+                ok = mbar_wait(&sm.k_empty[ks], kph ^ 1u, status, 41);
+                if (!ok) break;
+                mbar_expect_tx(&sm.k_full[ks], TILE_BYTES);
+                for (int hh = 0; hh < HALVES; ++hh)
+                    tma_load_4d(sm.k[ks] + hh * PANEL, &p.mk, &sm.k_full[ks], hh * 64, row, h, b);
+                if (++ks == 3) { ks = 0; kph ^= 1u; }
+                const int vs = it & 1;
+                // bias tile of block it: rows = this CTA's queries, columns = the block's keys
+                ok = mbar_wait(&sm.bb_empty[vs], ((uint32_t)(it >> 1) & 1u) ^ 1u, status, 43);
+                if (!ok) break;
+                mbar_expect_tx(&sm.bb_full[vs], BIAS_BYTES);
+                for (int pn = 0; pn < 2; ++pn)
+                    tma_load_4d(sm.bias[vs] + pn * (BT * 128), &p.mbias, &sm.bb_full[vs], row + pn * 64, r0,
+                                p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                ok = mbar_wait(&sm.v_empty[vs], ((uint32_t)(it >> 1) & 1u) ^ 1u, status, 42);
+                if (!ok) break;
+                mbar_expect_tx(&sm.v_full[vs], TILE_BYTES);
+                for (int hh = 0; hh < HALVES; ++hh)
+                    tma_load_4d(sm.v[vs] + hh * PANEL, &p.mv, &sm.v_full[vs], hh * 64, row, h, b);
+            }
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 9) {
+        // ---------------------- MMA issuer A: the score GEMMs ----------------------
+        if (lane == 0 && nit > 0) {
+            constexpr uint32_t idesc_g = make_idesc(BF16, BT, BT, false, false);
+            // [128 queries, A in tensor memory] x [128 keys of the tile at `yd`], contraction over channels
+            auto issue_g = [&](uint32_t col, uint32_t a_col, uint64_t yd) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * PANEL + (kk % 4) * 32;
+                    umma_ts(tbase + col, tbase + a_col + kk * 8, sdesc_advance(yd, off), idesc_g, kk > 0);
+                }
+            };
+            int ks = 0;
+            uint32_t kph = 0;
+            // S of block j (K ring slot and phase advance with j)
+            auto issue_g1 = [&](int j) -> bool {
+                if (!mbar_wait(&sm.k_full[ks], kph, status, 52)) return false;
+                // the score columns are free once the compute warps have read S of block j - 1
+                if (j >= 1 && !mbar_wait(&sm.s_read, (uint32_t)(j - 1) & 1u, status, 53)) return false;
+                tc_fence_after_sync();
+                issue_g(G1_COL, QA_COL, make_sdesc(smem_u32(sm.k[ks]), 16, 1024));
+                umma_commit(&sm.g1_full);
+                if (++ks == 3) { ks = 0; kph ^= 1u; }
+                return true;
+            };
+            // dP of block j
+            auto issue_g2 = [&](int j) -> bool {
+                const int vs = j & 1;
+                if (!mbar_wait(&sm.v_full[vs], (uint32_t)(j >> 1) & 1u, status, 54)) return false;
+                // the columns are free once the dQ GEMM of block j - 1 (which reads dS from them) is issued
+                if (j >= 1 && !mbar_wait(&sm.g2_free, (uint32_t)(j - 1) & 1u, status, 55)) return false;
+                tc_fence_after_sync();
+                issue_g(G2_COL, DOA_COL, make_sdesc(smem_u32(sm.v[vs]), 16, 1024));
+                umma_commit(&sm.g2_full);
+                umma_commit(&sm.v_empty[vs]);
+                return true;
+            };
+            bool ok = mbar_wait(&sm.a_ready, 0, status, 51);       // Q and dO are in tensor memory
+            if (ok) ok = issue_g1(0);
+            if (ok) ok = issue_g2(0);
+            for (int it = 0; it < nit && ok; ++it) {
+                if (it + 1 < nit) ok = issue_g1(it + 1);
+                if (ok && it + 1 < nit) ok = issue_g2(it + 1);
+            }
+        }
+    } else if (warp == 10) {
+        // ---------------------- MMA issuer B: the dQ GEMMs ----------------------
+        if (lane == 0 && nit > 0) {
+            constexpr uint32_t idesc_acc = make_idesc(BF16, BT, D, false, true);
+            bool ok = true;
+            int ks = 0;
+            uint32_t kph = 0;
+            for (int it = 0; it < nit && ok; ++it) {
+                ok = mbar_wait(&sm.k_full[ks], kph, status, 56);
+                if (!ok) break;
+                ok = mbar_wait(&sm.ds_ready, (uint32_t)it & 1u, status, 57);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint64_t dkm = make_sdesc(smem_u32(sm.k[ks]), PANEL, 1024);   // K as [key][channel], MN-major
+                // each half of the compute threads packed its 64 keys into the first 32 of its own 64 columns
+#pragma unroll
+                for (int kk = 0; kk < BT / 16; ++kk)
+                    umma_ts(tbase + ACC_COL, tbase + G2_COL + (kk >> 2) * 64 + (kk & 3) * 8,
+                            sdesc_advance(dkm, kk * 2048), idesc_acc, it > 0 || kk > 0);
+                tc_fence_before_sync();
+                mbar_arrive(&sm.g2_free);           // issued, not finished: the tensor pipe runs MMAs in issue order
+                umma_commit(&sm.k_empty[ks]);
+                if (++ks == 3) { ks = 0; kph ^= 1u; }
+            }
+            umma_commit(&sm.acc_full);
+        }
+    } else {
+        // ------------------------------ compute warps ------------------------------
+        const int row_l = (warp & 3) * 32 + lane;          // query row of the tile == TMEM lane
+        const int half = warp >> 2;                        // which 64 of the block's 128 keys
+        const int row = r0 + row_l;
+        const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+
+        // Q and dO of this tile into tensor memory: this thread's row, its half of the channels,
+        // as they lie in global memory (two 16-bit channels per 32-bit column).  Rows past the
+        // end of Q are written as zeros.
+        if (nit > 0) {
+#pragma unroll
+            for (int op = 0; op < 2; ++op) {
+                const T *src = reinterpret_cast<const T *>(op == 0 ? q_base : do_base) +
+                               (int64_t)b * (op == 0 ? q_sb : do_sb) + (int64_t)h * (op == 0 ? q_sh : do_sh) +
+                               (int64_t)row * (op == 0 ? q_sn : do_sn) + half * (D / 2);
+                uint32_t a[ACOLS];
+#pragma unroll
+                for (int i = 0; i < ACOLS; i += 4) {
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (row < p.Tq) v = __ldg(reinterpret_cast<const uint4 *>(src) + (i >> 2));
+                    a[i] = v.x; a[i + 1] = v.y; a[i + 2] = v.z; a[i + 3] = v.w;
+                }
+                const uint32_t dst = lane_base + (op == 0 ? QA_COL : DOA_COL) + half * ACOLS;
+                if constexpr (ACOLS == 32) tmem_st32(dst, a);
+                else tmem_st16(dst, a);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.a_ready);
+        }
+        // rows past Tq hold +inf / 0, so they yield P = 0
+        const float lse_row = p.lse2[(int64_t)bh * p.Tq128 + row];
+        const float dsc_row = p.delta_s[(int64_t)bh * p.Tq128 + row];
+        const uint32_t scol = G1_COL + half * 64, dcol = G2_COL + half * 64;
+
+        // P of block j from this thread's 64 scores and its row of the block's bias tile; the
+        // score columns are released as soon as they are in registers
+        float pv[64];
+        auto load_p = [&](int j) -> bool {
+            if (!mbar_wait(&sm.bb_full[j & 1], (uint32_t)(j >> 1) & 1u, status, 65)) return false;
+            // 64 key columns = the whole 128-byte row of panel `half`; pv first holds
+            // bias * log2(e) - lse * log2(e)
+            const unsigned char *rowp = sm.bias[j & 1] + half * (BT * 128) + row_l * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                union { uint4 u; T v[8]; } cv;
+                cv.u = *reinterpret_cast<const uint4 *>(rowp + ((c ^ (row_l & 7)) << 4));
+#pragma unroll
+                for (int e = 0; e < 8; ++e) pv[8 * c + e] = fmaf(to_f32<T>(cv.v[e]), LOG2E, -lse_row);
+            }
+            if (!mbar_wait(&sm.g1_full, (uint32_t)j & 1u, status, 60)) return false;
+            tc_fence_after_sync();
+            uint32_t ra[32], rb[32];
+            tmem_ld32(lane_base + scol, ra);
+            tmem_ld32(lane_base + scol + 32, rb);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.s_read);
+            const int blk0 = j * BT;
+            // blocks that need per-element masking: the diagonal blocks under the causal mask
+            // and the block touching the end of the keys
+            const bool slow = (p.causal && blk0 + BT > r0) || blk0 + BT > p.Tk;
+            if (!slow) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    pv[i] = ex2b(fmaf(__uint_as_float(ra[i]), p.scale_log2, pv[i]));
+                    pv[32 + i] = ex2b(fmaf(__uint_as_float(rb[i]), p.scale_log2, pv[32 + i]));
+                }
+            } else {
+                const int c0 = blk0 + half * 64;
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int kj = c0 + i;
+                    const bool masked = kj >= p.Tk || row >= p.Tq || (p.causal && kj > row);
+                    const float sv = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]);
+                    pv[i] = masked ? 0.f : ex2b(fmaf(sv, p.scale_log2, pv[i]));
+                }
+            }
+            return true;
+        };
+
+        bool ok = nit > 0 ? load_p(0) : true;
+        for (int it = 0; it < nit && ok; ++it) {
+            // dS of block it
+            ok = mbar_wait(&sm.g2_full, (uint32_t)it & 1u, status, 62);
+            if (!ok) break;
+            tc_fence_after_sync();
+            {
+                uint32_t ga[32], gb[32], pk[32];
+                tmem_ld32(lane_base + dcol, ga);
+                tmem_ld32(lane_base + dcol + 32, gb);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float a0 = pv[2 * i] * fmaf(__uint_as_float(ga[2 * i]), p.scale, -dsc_row);
+                    const float a1 = pv[2 * i + 1] * fmaf(__uint_as_float(ga[2 * i + 1]), p.scale, -dsc_row);
+                    pk[i] = pack16b<BF16>(a0, a1);
+                    const float b0 = pv[32 + 2 * i] * fmaf(__uint_as_float(gb[2 * i]), p.scale, -dsc_row);
+                    const float b1 = pv[32 + 2 * i + 1] * fmaf(__uint_as_float(gb[2 * i + 1]), p.scale, -dsc_row);
+                    pk[16 + i] = pack16b<BF16>(b0, b1);
+                }
+                // packed dS goes to the first 32 of this thread's 64 columns, all read already
+                tmem_st32(lane_base + dcol, pk);
+                tmem_wait_st();
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&sm.ds_ready);
+            mbar_arrive(&sm.bb_empty[it & 1]);      // dS depends on every value read from the bias tile of block it
+            // P of block it + 1, while the tensor pipe runs dQ(it) and dP(it + 1)
+            if (it + 1 < nit) ok = load_p(it + 1);
+        }
+
+        // epilogue: dQ -> global
+        if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 63);
+        tc_fence_after_sync();
+        if (ok) {
+            T *orow = reinterpret_cast<T *>(p.out1) + (int64_t)b * p.o1_sb + (int64_t)h * p.o1_sh + (int64_t)row * p.o1_sn;
+#pragma unroll 1
+            for (int c = 0; c < D / 64; ++c) {
+                const int col = half * (D / 2) + c * 32;
+                uint32_t r[32];
+                if (nit > 0) {
+                    tmem_ld32(lane_base + ACC_COL + col, r);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = 0u;
+                }
+                if (row < p.Tq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack16b<BF16>(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                        v.y = pack16b<BF16>(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                        v.z = pack16b<BF16>(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                        v.w = pack16b<BF16>(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                        *reinterpret_cast<uint4 *>(orow + col + i) = v;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tbase, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
 // Row statistics for the backward: delta = rowsum(O * dO)
 // (flash_attn_triton_cached.py:249-292), stored pre-multiplied by the softmax
 // scale, and lse * log2(e).  Rows in [Tq, Tq128) get +inf / 0 so that query
@@ -1230,12 +1631,12 @@ static int launch_bwd_tmem(const BwdTmaParams &bp, int nblocks, int BH, cudaStre
     return launch_bwd_one<D, BF16, DKDV, 0>(bp, nblocks, BH, st);
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool BIAS>
 static int launch_dkdv_sub(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
-    const size_t smem = sizeof(DkdvSubSmem<D>) + 1024;
-    if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dkdv_sub<D, BF16>), smem)) return e;
+    const size_t smem = sizeof(DkdvSubSmem<D, BIAS>) + 1024;
+    if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dkdv_sub<D, BF16, BIAS>), smem)) return e;
     dim3 grid(nblocks, BH);
-    attn_bwd_dkdv_sub<D, BF16><<<grid, DKDV_SUB_THREADS, smem, st>>>(bp);
+    attn_bwd_dkdv_sub<D, BF16, BIAS><<<grid, DKDV_SUB_THREADS, smem, st>>>(bp);
     count_launch();
     return check_launch();
 }
@@ -1246,7 +1647,9 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     bp.out1 = p.dv; bp.o1_sb = p.dv_sb; bp.o1_sh = p.dv_sh; bp.o1_sn = p.dv_sn;
     bp.out2 = p.dk; bp.o2_sb = p.dk_sb; bp.o2_sh = p.dk_sh; bp.o2_sn = p.dk_sn;
     if (bp.bias_kind == RGD_BIAS_NONE) {
-        if (int e = launch_dkdv_sub<D, BF16>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
+        if (int e = launch_dkdv_sub<D, BF16, false>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
+    } else if (bp.bias_vec == 2) {       // matrix bias staged by TMA
+        if (int e = launch_dkdv_sub<D, BF16, true>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
     } else if (int e = launch_bwd_tmem<D, BF16, true>(bp, (p.Tk + BT - 1) / BT, BH, st)) {
         return e;
     }
@@ -1257,6 +1660,15 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
         if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dq_pipe<D, BF16>), smem)) return e;
         dim3 grid((p.Tq + BT - 1) / BT, BH);
         attn_bwd_dq_pipe<D, BF16><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp);
+        count_launch();
+        return check_launch();
+    }
+    if (bp.bias_vec == 2) {              // matrix bias staged by TMA
+        const size_t smem = sizeof(DqBiasSmem<D>) + 1024;
+        if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16>), smem)) return e;
+        dim3 grid((p.Tq + BT - 1) / BT, BH);
+        attn_bwd_dq_bias<D, BF16><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn, p.do_sb,
+                                                                         p.do_sh, p.do_sn);
         count_launch();
         return check_launch();
     }
@@ -1292,7 +1704,8 @@ int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st) 
     if (p.bias_kind != RGD_BIAS_NONE && !p.bias_f32 && is_aligned(p.bias, 16) && p.b_sb % 8 == 0 && p.b_sh % 8 == 0 &&
         (p.bias_kind != RGD_BIAS_MATRIX || p.b_sq % 8 == 0))
         bp.bias_vec = 1;
-    if (bias_tma_ok(p) && encode_bias_map(cache, &bp.mbias, p, bf16) == RGD_OK) {
+    if (bias_tma_ok(p) && encode_bias_map(cache, &bp.mbias, p, bf16, BT) == RGD_OK &&
+        encode_bias_map(cache, &bp.mbias64, p, bf16, 64) == RGD_OK) {
         bp.bias_vec = 2;
         bp.bias_h0 = p.b_sh == 0;
         bp.bias_b0 = p.b_sb == 0;

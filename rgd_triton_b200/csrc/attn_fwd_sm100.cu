@@ -685,9 +685,9 @@ bool bias_tma_ok(const AttnParams &p) {
 }
 
 // (Tk, Tq, H or 1, B or 1) map over the bias; broadcast dims (stride 0) become extent 1.
-int encode_bias_map(rgd_cache *cache, CUtensorMap *out, const AttnParams &p, bool bf16) {
+int encode_bias_map(rgd_cache *cache, CUtensorMap *out, const AttnParams &p, bool bf16, int box_q) {
     const int64_t Hb = p.b_sh == 0 ? 1 : p.H, Bb = p.b_sb == 0 ? 1 : p.B;
-    return encode_heads_map_cached(cache, out, p.bias, Bb, Hb, p.Tq, p.Tk, p.b_sb, p.b_sh, p.b_sq, 64, TM, bf16);
+    return encode_heads_map_cached(cache, out, p.bias, Bb, Hb, p.Tq, p.Tk, p.b_sb, p.b_sh, p.b_sq, 64, box_q, bf16);
 }
 
 // Returns TMEM_NOT_TAKEN (nothing launched) when a descriptor cannot be encoded after all; the
@@ -706,7 +706,7 @@ int tmem_fwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st) 
     fp.bias_vec = p.bias_kind != RGD_BIAS_NONE && is_aligned(p.bias, 16) && p.b_sb % bel == 0 && p.b_sh % bel == 0 &&
                   (p.bias_kind != RGD_BIAS_MATRIX || p.b_sq % bel == 0);
     int bias_mode = p.bias_kind == RGD_BIAS_NONE ? 0 : 1;
-    if (bias_mode == 1 && bias_tma_ok(p) && encode_bias_map(cache, &fp.mbias, p, bf16) == RGD_OK) {
+    if (bias_mode == 1 && bias_tma_ok(p) && encode_bias_map(cache, &fp.mbias, p, bf16, TM) == RGD_OK) {
         bias_mode = 2;
         fp.bias_h0 = p.b_sh == 0;
         fp.bias_b0 = p.b_sb == 0;
