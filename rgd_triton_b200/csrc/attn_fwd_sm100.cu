@@ -58,14 +58,18 @@ struct FwdTmaParams {
     int *status;        // device status word (bounded waits report here)
 };
 
-// NT: query tiles per CTA.  BTMA: bias tiles (128 x 128, 16-bit, two 64-column
-// panels with 128-byte swizzle) staged by TMA, two stages per query tile.
-template <int D, int NT, bool BTMA>
+// NT: query tiles per CTA.  VS: stages of V.  BS: stages of TMA-staged bias tiles per query tile
+// (128 x 128, 16-bit, two 64-column panels with 128-byte swizzle; 0 = bias not staged).  With
+// head_dim 128 and a staged bias everything but K is single-buffered, which is what lets both
+// query tiles and their bias tiles fit: a bias tile is handed back right after the first
+// softmax pass and V right after the second tile's P V product, so either reload still has most
+// of an iteration to land.
+template <int D, int NT, int VS, int BS>
 struct alignas(1024) FwdTmaSmem {
     unsigned char q[NT][TM * D * 2];
     unsigned char k[2][TN * D * 2];
-    unsigned char v[2][TN * D * 2];
-    unsigned char bias[BTMA ? NT * 2 : 1][BTMA ? TM * TN * 2 : 1024];
+    unsigned char v[VS][TN * D * 2];
+    unsigned char bias[BS > 0 ? NT * BS : 1][BS > 0 ? TM * TN * 2 : 1024];
     uint64_t q_full, o_full;
     uint64_t s_full[2], p_half[2][2];           // p_half[tile][h]: P of keys [64h, 64h+64) is in tensor memory
     uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
@@ -180,8 +184,9 @@ __device__ __forceinline__ void exp32(const uint32_t (&r)[32], float scale_log2,
 // bias, fp32 bias, unaligned views), 2 matrix bias staged tile by tile through TMA.
 template <int D, bool BF16, int BIAS>
 __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_constant__ FwdTmaParams p) {
-    // With staged bias tiles and head_dim 128 only one query tile fits in shared memory.
-    constexpr int NT = (BIAS == 2 && D == 128) ? 1 : 2;
+    constexpr int NT = 2;
+    constexpr int VS = (BIAS == 2 && D == 128) ? 1 : 2;          // stages of V
+    constexpr int BS = BIAS == 2 ? (D == 128 ? 1 : 2) : 0;       // stages of bias tiles per query tile
     constexpr uint32_t BIAS_BYTES = TM * TN * 2;
     constexpr int HALVES = D / 64;                 // 64-channel (128-byte) swizzle panels per tile
     constexpr uint32_t PANEL = 128 * 64 * 2;       // bytes of one 128-row panel
@@ -190,7 +195,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
 
     extern __shared__ unsigned char smem_raw[];
-    using Smem = FwdTmaSmem<D, NT, BIAS == 2>;
+    using Smem = FwdTmaSmem<D, NT, VS, BS>;
     Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -257,22 +262,26 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
                 for (int hh = 0; hh < HALVES; ++hh)
                     tma_load_4d(sm.k[s] + hh * PANEL, &p.mk, &sm.k_full[s], hh * 64, j * TN, h, b);
-                ok = mbar_wait(&sm.v_empty[s], ph ^ 1u, status, 12);
-                if (!ok) break;
-                mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
-                for (int hh = 0; hh < HALVES; ++hh)
-                    tma_load_4d(sm.v[s] + hh * PANEL, &p.mv, &sm.v_full[s], hh * 64, j * TN, h, b);
                 if constexpr (BIAS == 2) {
+                    const int bs = j % BS;
+                    const uint32_t bph = (uint32_t)(j / BS) & 1u;
                     for (int t = 0; t < NT && ok; ++t) {
                         if (j >= nb[t]) continue;
-                        ok = mbar_wait(&sm.b_empty[t][s], ph ^ 1u, status, 13);
+                        ok = mbar_wait(&sm.b_empty[t][bs], bph ^ 1u, status, 13);
                         if (!ok) break;
-                        mbar_expect_tx(&sm.b_full[t][s], BIAS_BYTES);
+                        mbar_expect_tx(&sm.b_full[t][bs], BIAS_BYTES);
                         for (int pn = 0; pn < 2; ++pn)
-                            tma_load_4d(sm.bias[t * 2 + s] + pn * (TM * 128), &p.mbias, &sm.b_full[t][s], j * TN + pn * 64,
-                                        m0 + t * TM, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                            tma_load_4d(sm.bias[t * BS + bs] + pn * (TM * 128), &p.mbias, &sm.b_full[t][bs],
+                                        j * TN + pn * 64, m0 + t * TM, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
                     }
+                    if (!ok) break;
                 }
+                const int vs = j % VS;
+                ok = mbar_wait(&sm.v_empty[vs], ((uint32_t)(j / VS) & 1u) ^ 1u, status, 12);
+                if (!ok) break;
+                mbar_expect_tx(&sm.v_full[vs], TILE_BYTES);
+                for (int hh = 0; hh < HALVES; ++hh)
+                    tma_load_4d(sm.v[vs] + hh * PANEL, &p.mv, &sm.v_full[vs], hh * 64, j * TN, h, b);
             }
             if (!ok) {
                 // Give copies already in flight time to land before the CTA goes away.
@@ -315,17 +324,18 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 const int s = j & 1;
                 const uint32_t ph = (uint32_t)(j >> 1) & 1u, par = (uint32_t)j & 1u;
                 const bool more = j + 1 < nblk;
-                ok = mbar_wait(&sm.v_full[s], ph, status, 23);
+                const int vs = j % VS;
+                ok = mbar_wait(&sm.v_full[vs], (uint32_t)(j / VS) & 1u, status, 23);
                 if (!ok) break;
                 if (j < nb[0]) {
                     ok = mbar_wait(&sm.p_half[0][0], par, status, 24);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_pv(0, s, 0, j == 0);
+                    issue_pv(0, vs, 0, j == 0);
                     ok = mbar_wait(&sm.p_half[0][1], par, status, 27);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_pv(0, s, 1, false);
+                    issue_pv(0, vs, 1, false);
                 }
                 if (more) {
                     ok = mbar_wait(&sm.k_full[s ^ 1], (uint32_t)((j + 1) >> 1) & 1u, status, 25);
@@ -337,13 +347,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                     ok = mbar_wait(&sm.p_half[1][0], par, status, 26);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_pv(1, s, 0, j == 0);
+                    issue_pv(1, vs, 0, j == 0);
                     ok = mbar_wait(&sm.p_half[1][1], par, status, 28);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_pv(1, s, 1, false);
+                    issue_pv(1, vs, 1, false);
                 }
-                umma_commit(&sm.v_empty[s]);
+                umma_commit(&sm.v_empty[vs]);
                 if (more) {
                     if (j + 1 < nb[1]) issue_s(1, s ^ 1);
                     umma_commit(&sm.k_empty[s ^ 1]);
@@ -372,10 +382,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
             if (!ok) break;
             tc_fence_after_sync();
             const unsigned char *btile = nullptr;
+            constexpr int BSD = BS > 0 ? BS : 1;
             if constexpr (BIAS == 2) {
-                ok = mbar_wait(&sm.b_full[t][j & 1], (uint32_t)(j >> 1) & 1u, status, 33);
+                ok = mbar_wait(&sm.b_full[t][j % BSD], (uint32_t)(j / BSD) & 1u, status, 33);
                 if (!ok) break;
-                btile = sm.bias[t * 2 + (j & 1)];
+                btile = sm.bias[t * BSD + (j % BSD)];
             }
             const int n0 = j * TN;
             const bool need_mask = (n0 + TN > p.Tk) || (p.causal && n0 + TN > m0 + t * TM);
@@ -438,6 +449,79 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 tmem_st16(s_addr + 32, pk);
                 tmem_wait_ld();
                 exp32<BF16>(rb, p.scale_log2, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr + 48, pk);
+                l_sum += ls0 + ls1;
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.p_half[t][1]);
+                continue;
+            }
+
+            if (BIAS != 0 && !need_mask) {
+                // ---- interior block with a bias: x = s * scale * log2e + bias * log2e is formed
+                // ONCE per element (the bias tile is read and converted once), written back over
+                // the score columns and reduced to the row maximum in the same pass; the second
+                // pass is the one of the no-bias path, on x.  Loads run one chunk ahead. ----
+                uint32_t ra[32], rb[32];
+                float m0 = -INFINITY, m1 = -INFINITY;
+                tmem_ld32(s_addr, ra);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t (&cur)[32] = (c & 1) ? rb : ra;
+                    uint32_t (&nxt)[32] = (c & 1) ? ra : rb;
+                    if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, nxt);
+                    float bb[32];
+                    if constexpr (BIAS == 1) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 32, bb);
+                    if constexpr (BIAS == 2) bias_from_smem<BF16>(btile, row_l, c * 32, bb);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) cur[i] = __float_as_uint(fmaf(__uint_as_float(cur[i]), p.scale_log2, bb[i]));
+                    if (c & 1) m1 = fmaxf(m1, max32(cur));
+                    else m0 = fmaxf(m0, max32(cur));
+                    tmem_st32(s_addr + c * 32, cur);
+                    if (c < 3) tmem_wait_ld();
+                }
+                tmem_wait_st();                              // x is in tensor memory; the bias tile is consumed
+                if constexpr (BIAS == 2) mbar_arrive(&sm.b_empty[t][j % BSD]);
+                tmem_ld32(s_addr, ra);                       // chunk 0 of x, for the second pass
+                const float mx = fmaxf(m0, m1);
+                const bool want = (mx > m_ref + RESCALE_THRESHOLD) || (m_ref == -INFINITY && mx > -INFINITY);
+                if (__any_sync(0xffffffffu, want)) {
+                    const float alpha = !want ? 1.f : (m_ref == -INFINITY ? 0.f : ex2(m_ref - mx));
+                    l_sum *= alpha;
+                    if (want) m_ref = mx;
+                    if (j > 0) {
+#pragma unroll 1
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t r[32];
+                            tmem_ld32(lane_base + o_col + c * 32, r);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                            tmem_st32(lane_base + o_col + c * 32, r);
+                        }
+                    }
+                }
+                const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+                float ls0 = 0.f, ls1 = 0.f;
+                uint32_t pk[16];
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 32, rb);
+                exp32<BF16>(ra, 1.0f, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr, pk);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 64, ra);
+                exp32<BF16>(rb, 1.0f, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr + 16, pk);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 96, rb);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.p_half[t][0]);
+                exp32<BF16>(ra, 1.0f, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr + 32, pk);
+                tmem_wait_ld();
+                exp32<BF16>(rb, 1.0f, m_use, pk, ls0, ls1);
                 tmem_st16(s_addr + 48, pk);
                 l_sum += ls0 + ls1;
                 tmem_wait_st();
@@ -578,7 +662,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
             tc_fence_before_sync();
             mbar_arrive(&sm.p_half[t][0]);
             mbar_arrive(&sm.p_half[t][1]);
-            if constexpr (BIAS == 2) mbar_arrive(&sm.b_empty[t][j & 1]);   // bias tile read twice, now free
+            if constexpr (BIAS == 2) mbar_arrive(&sm.b_empty[t][j % BSD]);   // bias tile read twice, now free
         }
 
         // epilogue: O / l, LSE
@@ -660,8 +744,10 @@ bool tmem_fwd_eligible(const AttnParams &p) {
 
 template <int D, bool BF16, int BIAS>
 static int launch_fwd_one(const FwdTmaParams &fp, int Tq, int BH, cudaStream_t st) {
-    constexpr int NT = (BIAS == 2 && D == 128) ? 1 : 2;
-    const size_t smem = sizeof(FwdTmaSmem<D, NT, BIAS == 2>) + 1024;
+    constexpr int NT = 2;
+    constexpr int VS = (BIAS == 2 && D == 128) ? 1 : 2;
+    constexpr int BS = BIAS == 2 ? (D == 128 ? 1 : 2) : 0;
+    const size_t smem = sizeof(FwdTmaSmem<D, NT, VS, BS>) + 1024;
     if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_fwd_tmem<D, BF16, BIAS>), smem)) return e;
     dim3 grid((Tq + NT * TM - 1) / (NT * TM), BH);
     attn_fwd_tmem<D, BF16, BIAS><<<grid, FWD_THREADS, smem, st>>>(fp);
