@@ -750,6 +750,13 @@ class FlashAttnFunc(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None
 
 
+def _pad_head_dim_pays(q, k) -> bool:
+    """Padding head_dim costs four extra passes over q, k, v, o (and as many in the backward);
+    it pays once the score matrix is large."""
+    return q.is_cuda and q.dtype in (torch.float16, torch.bfloat16) and \
+        q.shape[0] * q.shape[2] * q.shape[1] * k.shape[1] >= (1 << 24)
+
+
 def flash_attn_func(q, k, v, bias=None, causal=False, softmax_scale=None, return_lse=False, kernel_cache=None):
     """q: (batch, seqlen_q, nheads, headdim); k, v: (batch, seqlen_k, nheads,
     headdim); bias: optional, 4-D, last two dims (1, seqlen_k) or (seqlen_q,
@@ -759,6 +766,19 @@ def flash_attn_func(q, k, v, bias=None, causal=False, softmax_scale=None, return
     out, the call still returns and the results of that launch are invalid.
     ``rgd_triton_b200._lib.load().rgd_device_status()`` reports (and clears) that
     condition; poll it at a point where a device synchronisation is acceptable."""
+    d = q.shape[-1] if q.ndim == 4 else 0
+    if d not in (0, 64, 128) and d < 128 and _pad_head_dim_pays(q, k):
+        # Head dims other than 64 / 128 have no tensor-memory instantiation of their own: large
+        # problems are zero-padded to the next of the two (zero channels add nothing to q k^T, and
+        # the padded channels of v give output channels that are cut off again), which keeps them
+        # on the tcgen05 kernels; the softmax scale stays that of the true head_dim.  Small
+        # problems run on the general kernels, where the copies would cost more than they save.
+        dp = 64 if d < 64 else 128
+        pad = lambda t: torch.nn.functional.pad(t, (0, dp - d))
+        res = flash_attn_func(pad(q), pad(k), pad(v), bias, causal, softmax_scale or 1.0 / math.sqrt(d), True,
+                              kernel_cache)
+        o = res[0][..., :d].contiguous()
+        return (o, res[1]) if return_lse else o
     if not _needs_grad(q, k, v, bias):
         _, _, _, o, lse, _, _ = _attn_forward(q, k, v, bias, causal, softmax_scale, kernel_cache)
     else:

@@ -168,6 +168,28 @@ def test_batch_expanded_keys_and_values(d):
     assert_attn(dq, edq, ldq, "dq", floor=GRAD_FLOOR)
 
 
+@pytest.mark.parametrize("d,with_bias", [(96, False), (32, True), (40, False)])
+def test_odd_head_dims_large_problems_are_padded_onto_the_tensor_memory_kernels(d, with_bias):
+    """Head dims other than 64 / 128 run on the general kernels when the problem is small and are
+    zero-padded to 64 / 128 when it is large; both must agree with the oracle (same scale
+    1/sqrt(d), padded channels cut off again) and with each other."""
+    g = gen(200 + d)
+    B, Tn, H = 1, 2048, 4                             # B * H * Tq * Tk = 2^24: the padded path
+    q, k, v, do = (randn(g, B, Tn, H, d, dtype=torch.bfloat16) for _ in range(4))
+    bias = randn(g, B, H, Tn, Tn, dtype=torch.bfloat16) if with_bias else None
+    assert F_._pad_head_dim_pays(q.cuda(), k.cuda())
+    check(q, k, v, do, bias, False, f"padded d={d}")
+    o, lse, dq, dk, dv = run_attn(q, k, v, do, bias)
+    assert o.shape == q.shape and dq.shape == q.shape and dk.shape == k.shape and o.is_contiguous()
+    # the same rows through the general kernels (a slice small enough not to be padded)
+    qs, dos = q[:, :512].contiguous(), do[:, :512].contiguous()
+    bs = None if bias is None else bias[:, :, :512].contiguous()
+    assert not F_._pad_head_dim_pays(qs.cuda(), k.cuda())
+    o2, lse2, _, _, _ = run_attn(qs, k, v, dos, bs)
+    torch.testing.assert_close(o[:, :512].float(), o2.float(), rtol=2e-2, atol=2e-3)
+    torch.testing.assert_close(lse[:, :, :512], lse2[:, :, :512], rtol=1e-3, atol=2e-3)
+
+
 @pytest.mark.parametrize("d", [64, 32])
 def test_negative_softmax_scale(d):
     """The reference accepts any scale; a negative one must not reach the forward fast
