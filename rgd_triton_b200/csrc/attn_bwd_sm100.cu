@@ -552,8 +552,10 @@ struct alignas(1024) DkdvSubSmem {
     uint32_t tmem_base;
 };
 
-template <int D, bool BF16, bool BIAS>
+// BIASM: 0 no bias, 1 matrix bias staged by TMA, 2 vector bias (one value per key = per thread).
+template <int D, bool BF16, int BIASM>
 __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const __grid_constant__ BwdTmaParams p) {
+    constexpr bool BIAS = BIASM == 1;
     using Smem = DkdvSubSmem<D, BIAS>;
     constexpr bool STAGE_STATS = Smem::STAGE_STATS;
     constexpr uint32_t BIAS_BYTES = 64 * BT * 2;
@@ -744,6 +746,16 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
         const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
         const bool cta_key_tail = r0 + BT > p.Tk;
         const uint32_t col = sb * 64;                      // this group's columns inside G1 / G2
+        // vector bias: this thread's key has one value for every query, times log2(e)
+        float bk2 = 0.f;
+        if constexpr (BIASM == 2) {
+            if (row < p.Tk) {
+                const char *bias_bh = reinterpret_cast<const char *>(p.bias) +
+                                      ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
+                bk2 = (p.bias_f32 ? reinterpret_cast<const float *>(bias_bh)[row]
+                                  : to_f32<T>(reinterpret_cast<const T *>(bias_bh)[row])) * LOG2E;
+            }
+        }
 
         bool ok = true;
         for (int it = 0; it < nit; ++it) {
@@ -803,18 +815,18 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float4 l = lse4[i];
-                            pv[4 * i + 0] = ex2b(fmaf(__uint_as_float(ra[4 * i + 0]), p.scale_log2, -l.x));
-                            pv[4 * i + 1] = ex2b(fmaf(__uint_as_float(ra[4 * i + 1]), p.scale_log2, -l.y));
-                            pv[4 * i + 2] = ex2b(fmaf(__uint_as_float(ra[4 * i + 2]), p.scale_log2, -l.z));
-                            pv[4 * i + 3] = ex2b(fmaf(__uint_as_float(ra[4 * i + 3]), p.scale_log2, -l.w));
+                            pv[4 * i + 0] = ex2b(fmaf(__uint_as_float(ra[4 * i + 0]), p.scale_log2, bk2 - l.x));
+                            pv[4 * i + 1] = ex2b(fmaf(__uint_as_float(ra[4 * i + 1]), p.scale_log2, bk2 - l.y));
+                            pv[4 * i + 2] = ex2b(fmaf(__uint_as_float(ra[4 * i + 2]), p.scale_log2, bk2 - l.z));
+                            pv[4 * i + 3] = ex2b(fmaf(__uint_as_float(ra[4 * i + 3]), p.scale_log2, bk2 - l.w));
                         }
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float4 l = lse4[8 + i];
-                            pv[32 + 4 * i + 0] = ex2b(fmaf(__uint_as_float(rb[4 * i + 0]), p.scale_log2, -l.x));
-                            pv[32 + 4 * i + 1] = ex2b(fmaf(__uint_as_float(rb[4 * i + 1]), p.scale_log2, -l.y));
-                            pv[32 + 4 * i + 2] = ex2b(fmaf(__uint_as_float(rb[4 * i + 2]), p.scale_log2, -l.z));
-                            pv[32 + 4 * i + 3] = ex2b(fmaf(__uint_as_float(rb[4 * i + 3]), p.scale_log2, -l.w));
+                            pv[32 + 4 * i + 0] = ex2b(fmaf(__uint_as_float(rb[4 * i + 0]), p.scale_log2, bk2 - l.x));
+                            pv[32 + 4 * i + 1] = ex2b(fmaf(__uint_as_float(rb[4 * i + 1]), p.scale_log2, bk2 - l.y));
+                            pv[32 + 4 * i + 2] = ex2b(fmaf(__uint_as_float(rb[4 * i + 2]), p.scale_log2, bk2 - l.z));
+                            pv[32 + 4 * i + 3] = ex2b(fmaf(__uint_as_float(rb[4 * i + 3]), p.scale_log2, bk2 - l.w));
                         }
                     }
                 } else {
@@ -823,7 +835,7 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                         const int qi = c0 + i;
                         const bool masked = row >= p.Tk || qi >= p.Tq || (p.causal && row > qi);
                         const float sv = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]);
-                        const float off = BIAS ? x0[BIAS ? i : 0] : -lse_f[i];
+                        const float off = BIAS ? x0[BIAS ? i : 0] : bk2 - lse_f[i];
                         pv[i] = masked ? 0.f : ex2b(fmaf(sv, p.scale_log2, off));
                     }
                 }
@@ -936,7 +948,9 @@ struct alignas(1024) DqPipeSmem {
 };
 constexpr int DQ_PIPE_THREADS = 352;   // 8 compute warps, TMA producer, two MMA issuers
 
-template <int D, bool BF16>
+// VEC: a vector bias (one value per key) is added to the scores; each compute thread fetches the
+// values of its 64 keys per block (the same for every query row, so they come from L1).
+template <int D, bool BF16, bool VEC>
 __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __grid_constant__ BwdTmaParams p) {
     constexpr int HALVES = D / 64;
     constexpr uint32_t PANEL = 128 * 64 * 2;
@@ -1100,22 +1114,54 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
         const float lse_row = p.lse2[(int64_t)bh * p.Tq128 + row];
         const float dsc_row = p.delta_s[(int64_t)bh * p.Tq128 + row];
 
+        const char *bias_bh = nullptr;
+        if constexpr (VEC)
+            bias_bh = reinterpret_cast<const char *>(p.bias) +
+                      ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
+        // off[i] = bias * log2(e) - lse * log2(e) for the 32 keys starting at column c of this
+        // thread's 64 in block j (just -lse without a bias); keys past the end read as bias 0
+        auto offsets = [&](int j, int c, float *off) {
+            if constexpr (VEC) {
+                const int k0 = j * BT + half * 64 + c;
+                if (!p.bias_f32 && p.bias_vec && k0 + 32 <= p.Tk) {
+                    const T *src = reinterpret_cast<const T *>(bias_bh) + k0;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const Vec<T, 8> v8 = load_vec<T, 8>(src + 8 * q4);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) off[8 * q4 + e] = fmaf(to_f32<T>(v8.v[e]), LOG2E, -lse_row);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float bvl = 0.f;
+                        if (k0 + i < p.Tk)
+                            bvl = p.bias_f32 ? reinterpret_cast<const float *>(bias_bh)[k0 + i]
+                                             : to_f32<T>(reinterpret_cast<const T *>(bias_bh)[k0 + i]);
+                        off[i] = fmaf(bvl, LOG2E, -lse_row);
+                    }
+                }
+            }
+        };
         // P of block j from its scores (32 columns starting at column c of this thread's 64)
         auto p_from_s = [&](const uint32_t (&r)[32], float *pv, int j, int c) {
             const int blk0 = j * BT;
+            float off[VEC ? 32 : 1];
+            offsets(j, c, off);
             // blocks that need per-element masking: the diagonal blocks under the causal mask
             // and the block touching the end of the keys
             const bool slow = (p.causal && blk0 + BT > r0) || blk0 + BT > p.Tk;
             if (!slow) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) pv[i] = ex2b(fmaf(__uint_as_float(r[i]), p.scale_log2, -lse_row));
+                for (int i = 0; i < 32; ++i)
+                    pv[i] = ex2b(fmaf(__uint_as_float(r[i]), p.scale_log2, VEC ? off[VEC ? i : 0] : -lse_row));
             } else {
                 const int c0 = blk0 + half * 64 + c;
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int kj = c0 + i;
                     const bool masked = kj >= p.Tk || row >= p.Tq || (p.causal && kj > row);
-                    pv[i] = masked ? 0.f : ex2b(fmaf(__uint_as_float(r[i]), p.scale_log2, -lse_row));
+                    pv[i] = masked ? 0.f : ex2b(fmaf(__uint_as_float(r[i]), p.scale_log2, VEC ? off[VEC ? i : 0] : -lse_row));
                 }
             }
         };
@@ -1163,14 +1209,18 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_pipe(const __g
                 }
                 uint32_t pk[16];
                 if (next && !slow_next) {
+                    float off[VEC ? 32 : 1];
+                    offsets(it + 1, 32 * c, off);
                     // element by element, so that the exponentials of the next block (MUFU) and
                     // the dS arithmetic of this one (FMA pipe) issue side by side
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const float a0 = pv[32 * c + 2 * i] * fmaf(__uint_as_float(ga[2 * i]), p.scale, -dsc_row);
                         const float a1 = pv[32 * c + 2 * i + 1] * fmaf(__uint_as_float(ga[2 * i + 1]), p.scale, -dsc_row);
-                        pv[32 * c + 2 * i] = ex2b(fmaf(__uint_as_float(ra[2 * i]), p.scale_log2, -lse_row));
-                        pv[32 * c + 2 * i + 1] = ex2b(fmaf(__uint_as_float(ra[2 * i + 1]), p.scale_log2, -lse_row));
+                        pv[32 * c + 2 * i] = ex2b(fmaf(__uint_as_float(ra[2 * i]), p.scale_log2,
+                                                       VEC ? off[VEC ? 2 * i : 0] : -lse_row));
+                        pv[32 * c + 2 * i + 1] = ex2b(fmaf(__uint_as_float(ra[2 * i + 1]), p.scale_log2,
+                                                           VEC ? off[VEC ? 2 * i + 1 : 0] : -lse_row));
                         pk[i] = pack16b<BF16>(a0, a1);
                     }
                     // packed dS of chunk c goes to columns [c*16, c*16+16) of this thread's 64, all read already
@@ -1631,12 +1681,12 @@ static int launch_bwd_tmem(const BwdTmaParams &bp, int nblocks, int BH, cudaStre
     return launch_bwd_one<D, BF16, DKDV, 0>(bp, nblocks, BH, st);
 }
 
-template <int D, bool BF16, bool BIAS>
+template <int D, bool BF16, int BIASM>
 static int launch_dkdv_sub(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
-    const size_t smem = sizeof(DkdvSubSmem<D, BIAS>) + 1024;
-    if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dkdv_sub<D, BF16, BIAS>), smem)) return e;
+    const size_t smem = sizeof(DkdvSubSmem<D, BIASM == 1>) + 1024;
+    if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dkdv_sub<D, BF16, BIASM>), smem)) return e;
     dim3 grid(nblocks, BH);
-    attn_bwd_dkdv_sub<D, BF16, BIAS><<<grid, DKDV_SUB_THREADS, smem, st>>>(bp);
+    attn_bwd_dkdv_sub<D, BF16, BIASM><<<grid, DKDV_SUB_THREADS, smem, st>>>(bp);
     count_launch();
     return check_launch();
 }
@@ -1647,19 +1697,25 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     bp.out1 = p.dv; bp.o1_sb = p.dv_sb; bp.o1_sh = p.dv_sh; bp.o1_sn = p.dv_sn;
     bp.out2 = p.dk; bp.o2_sb = p.dk_sb; bp.o2_sh = p.dk_sh; bp.o2_sn = p.dk_sn;
     if (bp.bias_kind == RGD_BIAS_NONE) {
-        if (int e = launch_dkdv_sub<D, BF16, false>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
+        if (int e = launch_dkdv_sub<D, BF16, 0>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
     } else if (bp.bias_vec == 2) {       // matrix bias staged by TMA
-        if (int e = launch_dkdv_sub<D, BF16, true>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
+        if (int e = launch_dkdv_sub<D, BF16, 1>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
+    } else if (bp.bias_kind == RGD_BIAS_VECTOR) {
+        if (int e = launch_dkdv_sub<D, BF16, 2>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
     } else if (int e = launch_bwd_tmem<D, BF16, true>(bp, (p.Tk + BT - 1) / BT, BH, st)) {
         return e;
     }
     bp.out1 = p.dq; bp.o1_sb = p.dq_sb; bp.o1_sh = p.dq_sh; bp.o1_sn = p.dq_sn;
     bp.out2 = nullptr;
-    if (bp.bias_kind == RGD_BIAS_NONE) {
+    if (bp.bias_kind == RGD_BIAS_NONE || (bp.bias_kind == RGD_BIAS_VECTOR && bp.bias_vec != 2)) {
+        const bool vec = bp.bias_kind == RGD_BIAS_VECTOR;
         const size_t smem = sizeof(DqPipeSmem<D>) + 1024;
-        if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dq_pipe<D, BF16>), smem)) return e;
+        const void *kernel = vec ? reinterpret_cast<const void *>(attn_bwd_dq_pipe<D, BF16, true>)
+                                 : reinterpret_cast<const void *>(attn_bwd_dq_pipe<D, BF16, false>);
+        if (int e = ensure_dyn_smem(kernel, smem)) return e;
         dim3 grid((p.Tq + BT - 1) / BT, BH);
-        attn_bwd_dq_pipe<D, BF16><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp);
+        if (vec) attn_bwd_dq_pipe<D, BF16, true><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp);
+        else attn_bwd_dq_pipe<D, BF16, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp);
         count_launch();
         return check_launch();
     }

@@ -64,7 +64,10 @@ struct FwdTmaParams {
 // query tiles and their bias tiles fit: a bias tile is handed back right after the first
 // softmax pass and V right after the second tile's P V product, so either reload still has most
 // of an iteration to land.
-template <int D, int NT, int VS, int BS>
+// VEC: a vector bias (one value per key) is staged per key block by the softmax threads
+// themselves: thread r of a tile converts the value of key r, so every thread then reads all 128
+// from shared memory instead of fetching and converting them itself.
+template <int D, int NT, int VS, int BS, bool VEC>
 struct alignas(1024) FwdTmaSmem {
     unsigned char q[NT][TM * D * 2];
     unsigned char k[2][TN * D * 2];
@@ -74,6 +77,8 @@ struct alignas(1024) FwdTmaSmem {
     uint64_t s_full[2], p_half[2][2];           // p_half[tile][h]: P of keys [64h, 64h+64) is in tensor memory
     uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
     uint64_t b_full[2][2], b_empty[2][2];      // [tile][stage]
+    uint64_t vb_ready[2];                      // [tile]: the tile's 128 threads have staged their value
+    alignas(16) float vbias[VEC ? NT : 1][2][VEC ? TN : 4];   // [tile][block parity][key]: bias * log2(e)
     uint32_t tmem_base;
 };
 
@@ -195,7 +200,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
 
     extern __shared__ unsigned char smem_raw[];
-    using Smem = FwdTmaSmem<D, NT, VS, BS>;
+    using Smem = FwdTmaSmem<D, NT, VS, BS, BIAS == 1>;
     Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -220,6 +225,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
         mbar_init(&sm.o_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&sm.s_full[s], 1);
+            mbar_init(&sm.vb_ready[s], 128);
             mbar_init(&sm.p_half[s][0], 128);
             mbar_init(&sm.p_half[s][1], 128);
             mbar_init(&sm.k_full[s], 1);
@@ -375,11 +381,30 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                       ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
         const int brow = row < p.Tq ? row : (p.Tq - 1);     // rows past the end read a valid bias row
 
+        const bool vec_staged = BIAS == 1 && p.bias_kind == RGD_BIAS_VECTOR;
         float m_ref = -INFINITY, l_sum = 0.f;
         bool ok = true;
         for (int j = 0; j < my_nb; ++j) {
+            if constexpr (BIAS == 1) {
+                if (vec_staged) {
+                    // this thread's key of the block: one value, times log2(e), for the whole tile
+                    const int kj = j * TN + row_l;
+                    float bvl = 0.f;
+                    if (kj < p.Tk)
+                        bvl = p.bias_f32 ? reinterpret_cast<const float *>(bias_bh)[kj]
+                                         : to_f32<T>(reinterpret_cast<const T *>(bias_bh)[kj]);
+                    sm.vbias[t][j & 1][row_l] = bvl * LOG2E;
+                    mbar_arrive(&sm.vb_ready[t]);
+                }
+            }
             ok = mbar_wait(&sm.s_full[t], (uint32_t)j & 1u, status, 31);
             if (!ok) break;
+            if constexpr (BIAS == 1) {
+                if (vec_staged) {
+                    ok = mbar_wait(&sm.vb_ready[t], (uint32_t)j & 1u, status, 34);
+                    if (!ok) break;
+                }
+            }
             tc_fence_after_sync();
             const unsigned char *btile = nullptr;
             constexpr int BSD = BS > 0 ? BS : 1;
@@ -472,7 +497,18 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                     uint32_t (&nxt)[32] = (c & 1) ? ra : rb;
                     if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, nxt);
                     float bb[32];
-                    if constexpr (BIAS == 1) load_bias32<BF16>(p, bias_bh, brow, n0 + c * 32, bb);
+                    if constexpr (BIAS == 1) {
+                        if (vec_staged) {
+                            const float4 *src = reinterpret_cast<const float4 *>(&sm.vbias[BIAS == 1 ? t : 0][j & 1][c * 32]);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float4 f = src[i];
+                                bb[4 * i] = f.x; bb[4 * i + 1] = f.y; bb[4 * i + 2] = f.z; bb[4 * i + 3] = f.w;
+                            }
+                        } else {
+                            load_bias32<BF16>(p, bias_bh, brow, n0 + c * 32, bb);
+                        }
+                    }
                     if constexpr (BIAS == 2) bias_from_smem<BF16>(btile, row_l, c * 32, bb);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) cur[i] = __float_as_uint(fmaf(__uint_as_float(cur[i]), p.scale_log2, bb[i]));
@@ -747,7 +783,7 @@ static int launch_fwd_one(const FwdTmaParams &fp, int Tq, int BH, cudaStream_t s
     constexpr int NT = 2;
     constexpr int VS = (BIAS == 2 && D == 128) ? 1 : 2;
     constexpr int BS = BIAS == 2 ? (D == 128 ? 1 : 2) : 0;
-    const size_t smem = sizeof(FwdTmaSmem<D, NT, VS, BS>) + 1024;
+    const size_t smem = sizeof(FwdTmaSmem<D, NT, VS, BS, BIAS == 1>) + 1024;
     if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_fwd_tmem<D, BF16, BIAS>), smem)) return e;
     dim3 grid((Tq + NT * TM - 1) / (NT * TM), BH);
     attn_fwd_tmem<D, BF16, BIAS><<<grid, FWD_THREADS, smem, st>>>(fp);

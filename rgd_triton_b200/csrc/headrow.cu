@@ -569,10 +569,16 @@ template <int OP> struct FlatGeom {
     static constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
     static constexpr int VPT = HAS_DY ? 2 : 4;
     static constexpr int RPT = HAS_DY ? 2 : 1;
+    // The backward operators are bound by instruction issue with long dependent chains (four
+    // row reductions): a third CTA per SM (80 registers, two pipeline stages instead of three so
+    // that the shared memory fits) hides them better (LayerNorm+rotary backward 167 -> 155 us at
+    // the second benchmark configuration).  The forward operators lose by the same trade.
+    static constexpr int STAGES = HAS_DY ? 2 : PIPE_STAGES;
+    static constexpr int MIN_CTAS = HAS_DY ? 3 : 0;      // 0: no constraint for the forward operators
 };
 
 template <typename T, typename TP, int VPT, int FLAT_RPT, int OP, int D>
-__global__ void __launch_bounds__(HEAD_THREADS) head_kernel_flat(const __grid_constant__ HeadParams p) {
+__global__ void __launch_bounds__(HEAD_THREADS, FlatGeom<OP>::MIN_CTAS) head_kernel_flat(const __grid_constant__ HeadParams p) {
     constexpr int VE = VecElems<T>::value;
     constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
     constexpr bool HAS_ROPE = (OP == ROPE || OP == LNROPE_FWD || OP == LNROPE_BWD);
@@ -580,8 +586,9 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel_flat(const __grid_co
     constexpr int TPR = D / (VE * VPT);                  // threads per row
     constexpr int RPC = HEAD_THREADS / TPR;              // rows per CTA pass
     constexpr int SLOTS = NIN * FLAT_RPT * VPT;
+    constexpr int STAGES = FlatGeom<OP>::STAGES;
     using V = Vec<T, VE>;
-    extern __shared__ uint4 slots[];                     // [PIPE_STAGES][SLOTS][HEAD_THREADS]
+    extern __shared__ uint4 slots[];                     // [STAGES][SLOTS][HEAD_THREADS]
 
     const int rg = (int)threadIdx.x / TPR;
     const int t = (int)threadIdx.x - rg * TPR;
@@ -658,20 +665,20 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_kernel_flat(const __grid_co
     const int64_t step = gridDim.x;
     const int64_t tile0 = blockIdx.x;
 #pragma unroll
-    for (int s = 0; s < PIPE_STAGES - 1; ++s) {
+    for (int s = 0; s < STAGES - 1; ++s) {
         if (tile0 + s * step < total) issue(tile0 + s * step, s);
         cp_async_commit();
     }
     int stage = 0;
     for (int64_t tile = tile0; tile < total; tile += step) {
-        const int64_t ahead = tile + (PIPE_STAGES - 1) * step;
-        int fill = stage + PIPE_STAGES - 1;
-        if (fill >= PIPE_STAGES) fill -= PIPE_STAGES;
+        const int64_t ahead = tile + (STAGES - 1) * step;
+        int fill = stage + STAGES - 1;
+        if (fill >= STAGES) fill -= STAGES;
         if (ahead < total) issue(ahead, fill);
         cp_async_commit();
-        cp_async_wait<PIPE_STAGES - 1>();
+        cp_async_wait<STAGES - 1>();
         consume(tile, stage);
-        if (++stage == PIPE_STAGES) stage = 0;
+        if (++stage == STAGES) stage = 0;
     }
     cp_async_wait<0>();
 }
@@ -732,7 +739,7 @@ int launch_flat(const HeadParams &p, int64_t tiles, cudaStream_t st) {
     constexpr bool HAS_DY = (OP == LN_BWD || OP == LNROPE_BWD);
     constexpr int VPT = FlatGeom<OP>::VPT, RPT = FlatGeom<OP>::RPT;
     constexpr int SLOTS = (HAS_DY ? 2 : 1) * RPT * VPT;
-    const size_t smem = (size_t)PIPE_STAGES * SLOTS * HEAD_THREADS * 16;
+    const size_t smem = (size_t)FlatGeom<OP>::STAGES * SLOTS * HEAD_THREADS * 16;
     auto kernel = head_kernel_flat<T, TP, VPT, RPT, OP, D>;
     if (smem > 32 * 1024)
         if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(kernel), smem)) return e;

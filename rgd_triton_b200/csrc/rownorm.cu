@@ -331,7 +331,9 @@ __device__ __forceinline__ void named_bar_sync() {
 // TPR threads per row, RPC rows per CTA and iteration (CTA = TPR * RPC threads), VPT vectors per
 // thread.
 template <typename T, int VPT, int OP, int TPR, int RPC>
-__global__ void __launch_bounds__(TPR * RPC, OP == RMS_BWD ? 2 : 1) lean_row_kernel(const __grid_constant__ RowParams p) {
+// (three CTAs per SM for the forward operators: more rows in flight per SM; the backward ones,
+// which hold x and dy of two rows, stay at two)
+__global__ void __launch_bounds__(TPR * RPC, (OP == RMS_BWD || OP == L2_BWD) ? 2 : 3) lean_row_kernel(const __grid_constant__ RowParams p) {
     constexpr int THREADS = TPR * RPC;
     constexpr bool BWD = (OP == L2_BWD || OP == RMS_BWD);
     constexpr bool RMS = (OP == RMS_FWD || OP == RMS_BWD);
@@ -408,6 +410,9 @@ __global__ void __launch_bounds__(TPR * RPC, OP == RMS_BWD ? 2 : 1) lean_row_ker
     // copies or by rotating buffers through an unrolled loop, 60-73 us against 42 us; weight
     // row AND dweight sums in shared memory, 53 us.  Kept: weight row in shared memory plus
     // raw-register passes, two CTAs per SM, 40 us.)
+    // The dweight reduce that follows the RMS backward is launched as a programmatic dependent:
+    // let it be set up now; it waits for this grid's completion before it reads anything.
+    if constexpr (OP == RMS_BWD) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     V xq[VPT], xn[VPT];
     V dq[BWD ? VPT : 1], dn[BWD ? VPT : 1];
     if (n < s.N) {
@@ -655,6 +660,9 @@ struct DwReduceParams {
 
 __global__ void __launch_bounds__(1024) dw_reduce_kernel(const __grid_constant__ DwReduceParams p) {
     __shared__ float tile[32][33];
+    // Launched as a programmatic dependent of the kernel that writes the partial rows: the grid may
+    // be set up while that kernel drains; nothing is read before it has completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const DwReduceStream &s = p.s[blockIdx.z];
     const int o = blockIdx.y;
     if (o >= s.n_out) return;
@@ -1043,7 +1051,24 @@ extern "C" int rgd_rmsnorm_bwd(int nstreams, const rgd_rows *x, const void *cons
     }
     if (cmax == 0 || omax == 0) return RGD_OK;
     dim3 grid((cmax + 31) / 32, omax, nstreams), block(32, 32);
-    dw_reduce_kernel<<<grid, block, 0, st>>>(rp);
+    {
+        // programmatic dependent launch: the reduce grid is set up while the row kernel drains
+        // (it waits for that kernel's completion before reading); a plain launch if refused
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid;
+        cfg.blockDim = block;
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, dw_reduce_kernel, rp) != cudaSuccess) {
+            (void)cudaGetLastError();
+            dw_reduce_kernel<<<grid, block, 0, st>>>(rp);
+        }
+    }
     count_launch();
     return check_launch();
 }
