@@ -671,7 +671,18 @@ __global__ void __launch_bounds__(1024) dw_reduce_kernel(const __grid_constant__
     float a = 0.f;
     if (col < s.C) {
         const float *base = s.part + (int64_t)o * s.rows_per_out * s.C + col;
-        for (int r = threadIdx.y; r < s.rows_per_out; r += 32) a += base[(int64_t)r * s.C];
+        // four independent loads in flight per thread (a fixed order all the same): with one
+        // the kernel is a chain of L2 round trips
+        float a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int r = threadIdx.y;
+        for (; r + 96 < s.rows_per_out; r += 128) {
+            a += base[(int64_t)r * s.C];
+            a1 += base[(int64_t)(r + 32) * s.C];
+            a2 += base[(int64_t)(r + 64) * s.C];
+            a3 += base[(int64_t)(r + 96) * s.C];
+        }
+        for (; r < s.rows_per_out; r += 32) a += base[(int64_t)r * s.C];
+        a = (a + a1) + (a2 + a3);
     }
     tile[threadIdx.y][threadIdx.x] = a;
     __syncthreads();

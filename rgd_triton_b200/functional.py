@@ -100,6 +100,16 @@ def _native_cache(cache):
     return native() if native is not None else None
 
 
+def _tracing() -> bool:
+    """True while torch.compile is tracing: the entry points then call the registered custom
+    operators (rgd_triton_b200.library) instead of the eager path, which a tracer cannot follow
+    into ctypes."""
+    if torch.compiler.is_compiling():
+        from . import library  # noqa: F401  (registers torch.ops.rgd_b200.*)
+        return True
+    return False
+
+
 def _needs_grad(*tensors) -> bool:
     """Whether autograd has to record this call.  When it does not, the entry
     points run the forward directly instead of through autograd.Function, whose
@@ -222,6 +232,8 @@ class Norm_Func(torch.autograd.Function):
 
 def triton_norm_func_fn(x, norm_eps=1e-6, use_ptx=False, kernel_cache=None):
     """L2-normalise the rows of x.  ``use_ptx`` is accepted and ignored."""
+    if _tracing():
+        return torch.ops.rgd_b200.l2norm([x], float(norm_eps))[0]
     if not _needs_grad(x):
         return _l2_forward([x], norm_eps, kernel_cache, "L2Normalize")[1][0]
     return Norm_Func.apply(x, norm_eps, use_ptx, kernel_cache)
@@ -246,6 +258,9 @@ class Fused_Norm_Func(torch.autograd.Function):
 
 
 def triton_fused_norm_func_fn(x1, x2, norm_eps=1e-6, kernel_cache=None):
+    if _tracing():
+        y1, y2 = torch.ops.rgd_b200.l2norm([x1, x2], float(norm_eps))
+        return y1, y2
     if not _needs_grad(x1, x2):
         ys = _l2_forward([x1, x2], norm_eps, kernel_cache, "FusedL2Normalize2")[1]
         return ys[0], ys[1]
@@ -365,6 +380,8 @@ class RMS_Func(torch.autograd.Function):
 
 
 def triton_rms_func_fn(x, w, norm_eps=1e-6, kernel_cache=None):
+    if _tracing():
+        return torch.ops.rgd_b200.rmsnorm([x], [w], float(norm_eps))[0]
     if not _needs_grad(x, w):
         return _rms_forward([x], [w], norm_eps, kernel_cache, "FusedRMSNorm")[2][0]
     return RMS_Func.apply(x, w, norm_eps, kernel_cache)
@@ -391,6 +408,9 @@ class Fused_RMS_Func(torch.autograd.Function):
 
 
 def triton_fused_rms_func_fn(x1, x2, w1, w2, norm_eps=1e-6, kernel_cache=None):
+    if _tracing():
+        y1, y2 = torch.ops.rgd_b200.rmsnorm([x1, x2], [w1, w2], float(norm_eps))
+        return y1, y2
     if not _needs_grad(x1, x2, w1, w2):
         ys = _rms_forward([x1, x2], [w1, w2], norm_eps, kernel_cache, "FusedRMSNorm2")[2]
         return ys[0], ys[1]
@@ -500,6 +520,8 @@ class Fused_LNQK_Func(torch.autograd.Function):
 
 
 def triton_fused_ln_func_fn(query, key, heads_second=True, norm_eps=1e-6, kernel_cache=None):
+    if _tracing():
+        return torch.ops.rgd_b200.headln(query, key, bool(heads_second), float(norm_eps))
     if not _needs_grad(query, key):
         return _ln_forward(query, key, heads_second, norm_eps, kernel_cache)[2:]
     return Fused_LNQK_Func.apply(query, key, heads_second, norm_eps, kernel_cache)
@@ -577,6 +599,10 @@ def triton_rope_fn(query, key, pos_emb, seq_cutoff=None, heads_second=True, fuse
                    in_place=False):
     """Rotary embedding on (query, key).  ``fused_ln`` is accepted for
     signature parity and ignored, as in the reference."""
+    if _tracing() and not in_place:
+        nq, nk = (query.shape[2], key.shape[2]) if heads_second else (query.shape[1], key.shape[1])
+        cq, ck = _cutoffs(seq_cutoff, nq, nk)
+        return torch.ops.rgd_b200.rope(query, key, pos_emb, cq, ck, bool(heads_second), False)
     if not _needs_grad(query, key, pos_emb):
         return _rope_forward(query, key, pos_emb, seq_cutoff, heads_second, in_place, kernel_cache)[4:]
     return CombinedRoPEFunc.apply(query, key, pos_emb, seq_cutoff, heads_second, in_place, kernel_cache)
@@ -641,6 +667,10 @@ class FusedRoPEFunc(torch.autograd.Function):
 
 def triton_fused_ln_rope_fn(query, key, pos_emb, seq_cutoff=None, heads_second=True, norm_eps=1e-6,
                             kernel_cache=None):
+    if _tracing():
+        nq, nk = (query.shape[2], key.shape[2]) if heads_second else (query.shape[1], key.shape[1])
+        cq, ck = _cutoffs(seq_cutoff, nq, nk)
+        return torch.ops.rgd_b200.lnrope(query, key, pos_emb, cq, ck, bool(heads_second), float(norm_eps))
     if not _needs_grad(query, key, pos_emb):
         return _lnrope_forward(query, key, pos_emb, seq_cutoff, heads_second, norm_eps, kernel_cache)[4:]
     return FusedRoPEFunc.apply(query, key, pos_emb, seq_cutoff, heads_second, norm_eps, kernel_cache)
@@ -725,29 +755,34 @@ class FlashAttnFunc(torch.autograd.Function):
     def backward(ctx, do, dlse):
         q, k, v, o, lse, bias = ctx.saved_tensors
         _require(not ctx.needs_input_grad[3], "FlashAttention does not support bias gradient yet")
-        do = _last_contig(do)
         cache = ctx.kernel_cache
-        plan = _plan(cache, "bwd", _key(q, k, v, do, bias, extra=("attn", bool(ctx.causal))),
-                     lambda: _require(do.shape == q.shape and do.dtype == q.dtype, "dO must match q"))
+        dq, dk, dv = _attn_backward(q, k, v, bias, o, lse, do, ctx.causal, ctx.softmax_scale, cache)
         if cache is not None:
             cache.bwd_odot = cache.bwd
-        lib = _lib.load()
-        batch, seqlen_q, nheads, d = q.shape
-        seqlen_k = k.shape[1]
-        _, bias_s = _prep_bias(bias, q, seqlen_q, seqlen_k)
-        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        dt, nbytes = _const(plan, "c", lambda: (_lib.dtype_code(q.dtype), int(lib.rgd_attn_bwd_workspace_bytes(
-            batch, nheads, seqlen_q, seqlen_k, d, _lib.dtype_code(q.dtype)))))
-        _require(nbytes >= 0, "attn_bwd: bad sizes")
-        work = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
-        qh, kh, vh, oh, doh, dqh, dkh, dvh = _heads_refs(plan, "h", (q, k, v, o, do, dq, dk, dv), _attn_heads)
-        with _lib.device_guard(q):
-            code = lib.rgd_attn_bwd(qh, kh, vh, C.byref(bias_s), oh, lse.data_ptr(), doh, dqh, dkh, dvh, batch, nheads,
-                                    seqlen_q, seqlen_k, d, float(ctx.softmax_scale), 1 if ctx.causal else 0, dt,
-                                    work.data_ptr(), work.numel(), _native_cache(cache), _lib.stream_ptr())
-        if code:
-            _lib.check(code, "attn_bwd")
         return dq, dk, dv, None, None, None, None
+
+
+def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache):
+    do = _last_contig(do)
+    plan = _plan(cache, "bwd", _key(q, k, v, do, bias, extra=("attn", bool(causal))),
+                 lambda: _require(do.shape == q.shape and do.dtype == q.dtype, "dO must match q"))
+    lib = _lib.load()
+    batch, seqlen_q, nheads, d = q.shape
+    seqlen_k = k.shape[1]
+    _, bias_s = _prep_bias(bias, q, seqlen_q, seqlen_k)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dt, nbytes = _const(plan, "c", lambda: (_lib.dtype_code(q.dtype), int(lib.rgd_attn_bwd_workspace_bytes(
+        batch, nheads, seqlen_q, seqlen_k, d, _lib.dtype_code(q.dtype)))))
+    _require(nbytes >= 0, "attn_bwd: bad sizes")
+    work = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    qh, kh, vh, oh, doh, dqh, dkh, dvh = _heads_refs(plan, "h", (q, k, v, o, do, dq, dk, dv), _attn_heads)
+    with _lib.device_guard(q):
+        code = lib.rgd_attn_bwd(qh, kh, vh, C.byref(bias_s), oh, lse.data_ptr(), doh, dqh, dkh, dvh, batch, nheads,
+                                seqlen_q, seqlen_k, d, float(softmax_scale), 1 if causal else 0, dt,
+                                work.data_ptr(), work.numel(), _native_cache(cache), _lib.stream_ptr())
+    if code:
+        _lib.check(code, "attn_bwd")
+    return dq, dk, dv
 
 
 def _pad_head_dim_pays(q, k) -> bool:
@@ -766,6 +801,10 @@ def flash_attn_func(q, k, v, bias=None, causal=False, softmax_scale=None, return
     out, the call still returns and the results of that launch are invalid.
     ``rgd_triton_b200._lib.load().rgd_device_status()`` reports (and clears) that
     condition; poll it at a point where a device synchronisation is acceptable."""
+    if _tracing():
+        scale = float(softmax_scale or 1.0 / math.sqrt(q.shape[-1]))
+        o, lse = torch.ops.rgd_b200.attn(q, k, v, bias, bool(causal), scale)
+        return (o, lse) if return_lse else o
     d = q.shape[-1] if q.ndim == 4 else 0
     if d not in (0, 64, 128) and d < 128 and _pad_head_dim_pays(q, k):
         # Head dims other than 64 / 128 have no tensor-memory instantiation of their own: large
