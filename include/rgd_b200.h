@@ -270,6 +270,29 @@ int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v,
                  float softmax_scale, int causal, int dtype, void *workspace,
                  int64_t workspace_bytes, rgd_cache *cache, void *stream);
 
+/* rgd_attn_bwd plus the gradient of the additive bias, which the reference
+ * refuses (flash_attn_triton_cached.py:1107).  `dbias` (null or kind
+ * RGD_BIAS_NONE: exactly rgd_attn_bwd) describes the output and must have the
+ * kind of `bias`:
+ *   RGD_BIAS_VECTOR: dense fp32 [B, H, Tk] (dtype RGD_F32, stride_h = Tk,
+ *     stride_b = H * Tk): sum over the queries of P * (dP - delta); zeroed by
+ *     this call.
+ *   RGD_BIAS_MATRIX: [B, H, Tq, Tk] in the q dtype through element strides
+ *     (unit key stride): P * (dP - delta), one rounding.  With causal != 0 the
+ *     entries of key blocks that lie entirely above the diagonal are NOT
+ *     written: pass a zeroed tensor then.
+ * The output always has full batch and head extents; a caller whose bias is
+ * broadcast over batch, heads or queries sums over those dimensions. */
+int rgd_attn_bwd_dbias(const rgd_heads *q, const rgd_heads *k,
+                       const rgd_heads *v, const rgd_bias *bias,
+                       const rgd_heads *o, const float *lse,
+                       const rgd_heads *d_o, const rgd_heads *dq,
+                       const rgd_heads *dk, const rgd_heads *dv,
+                       const rgd_bias *dbias, int64_t B, int64_t H, int64_t Tq,
+                       int64_t Tk, int64_t d, float softmax_scale, int causal,
+                       int dtype, void *workspace, int64_t workspace_bytes,
+                       rgd_cache *cache, void *stream);
+
 /* Which attention implementation rgd_attn_fwd / rgd_attn_bwd take for these
  * views: 1 = tcgen05 / tensor-memory / TMA kernels, 0 = general mma.sync
  * kernels.  Evaluates exactly the test the entry points use (head_dim 64 or

@@ -279,6 +279,24 @@ def attn_bwd(q, k, v, do, bias=None, causal: bool = False, softmax_scale: float 
     return dq.to(q.dtype), dk.to(q.dtype), dv.to(q.dtype)
 
 
+def attn_bwd_dbias(q, k, v, do, bias, causal: bool = False, softmax_scale: float | None = None):
+    """Gradient of the additive bias in fp32, shaped like `bias`: the scores are
+    q k^T * scale + bias (flash_attn_triton_cached.py:151-175), so
+    d bias = dS / scale = P * (dP - delta), summed over the dimensions along which the
+    bias is broadcast.  The reference does not produce it (:1107)."""
+    scale = softmax_scale or 1.0 / math.sqrt(q.shape[-1])
+    s = _scores(q, k, bias, causal, scale)
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse[..., None])
+    dof, vf = _f(do), _f(v)
+    o = torch.einsum("bhts,bshd->bthd", p, vf)
+    delta = (o * dof).sum(-1).permute(0, 2, 1)
+    dp = torch.einsum("bthd,bshd->bhts", dof, vf)
+    ds = p * (dp - delta[..., None])
+    dims = [i for i in range(4) if bias.shape[i] == 1 and ds.shape[i] != 1]
+    return ds.sum(dim=dims, keepdim=True) if dims else ds
+
+
 def attn_lowp(q, k, v, do, bias=None, causal: bool = False, softmax_scale: float | None = None):
     """Low-precision eager attention (every op in q.dtype), forward and
     backward through autograd: the yardstick the reference's own tests use for

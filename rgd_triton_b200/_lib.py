@@ -78,6 +78,8 @@ SIGNATURES = {
     "rgd_attn_bwd_workspace_bytes": (_i64, [_i64] * 5 + [_i32]),
     "rgd_attn_bwd": (_i32, [_pHeads, _pHeads, _pHeads, _pBias, _pHeads, _vp, _pHeads, _pHeads, _pHeads, _pHeads]
                      + [_i64] * 5 + [_f32, _i32, _i32, _vp, _i64, _vp, _vp]),
+    "rgd_attn_bwd_dbias": (_i32, [_pHeads, _pHeads, _pHeads, _pBias, _pHeads, _vp, _pHeads, _pHeads, _pHeads, _pHeads, _pBias]
+                           + [_i64] * 5 + [_f32, _i32, _i32, _vp, _i64, _vp, _vp]),
     "rgd_attn_fwd_uses_tmem": (_i32, [_pHeads] * 4 + [_i64] * 5 + [_f32, _i32]),
     "rgd_attn_bwd_uses_tmem": (_i32, [_pHeads] * 8 + [_i64] * 5 + [_i32]),
 }

@@ -147,7 +147,29 @@ extern "C" int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_he
                             const rgd_heads *dk, const rgd_heads *dv, int64_t B, int64_t H, int64_t Tq, int64_t Tk,
                             int64_t d, float softmax_scale, int causal, int dtype, void *workspace,
                             int64_t workspace_bytes, rgd_cache *cache, void *stream) {
+    return rgd_attn_bwd_dbias(q, k, v, bias, o, lse, d_o, dq, dk, dv, nullptr, B, H, Tq, Tk, d, softmax_scale, causal, dtype,
+                              workspace, workspace_bytes, cache, stream);
+}
+
+extern "C" int rgd_attn_bwd_dbias(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
+                                  const rgd_heads *o, const float *lse, const rgd_heads *d_o, const rgd_heads *dq,
+                                  const rgd_heads *dk, const rgd_heads *dv, const rgd_bias *dbias, int64_t B, int64_t H,
+                                  int64_t Tq, int64_t Tk, int64_t d, float softmax_scale, int causal, int dtype,
+                                  void *workspace, int64_t workspace_bytes, rgd_cache *cache, void *stream) {
     if (int e = check_common(q, k, v, bias, B, H, Tq, Tk, d, dtype)) return e;
+    const bool want_dbias = dbias && dbias->kind != RGD_BIAS_NONE;
+    if (want_dbias) {
+        // same kind as the bias; vector: dense fp32 [B, H, Tk]; matrix: the tensor dtype, unit key stride
+        if (!bias || bias->kind != dbias->kind) return RGD_E_BIAS_SHAPE;
+        if (dbias->kind == RGD_BIAS_VECTOR) {
+            if (dbias->dtype != RGD_F32) return RGD_E_DTYPE;
+            if (dbias->stride_h != Tk || dbias->stride_b != H * Tk) return RGD_E_STRIDE;
+        } else {
+            if (dbias->dtype != dtype) return RGD_E_DTYPE;
+            if (dbias->stride_q < Tk || dbias->stride_h < 0 || dbias->stride_b < 0) return RGD_E_STRIDE;
+        }
+        if (!dbias->ptr && B > 0 && H > 0 && Tq > 0 && Tk > 0) return RGD_E_NULL;
+    }
     if (!o || !d_o || !dq || !dk || !dv) return RGD_E_NULL;
     const bool work = B > 0 && H > 0 && d > 0;
     if (work && Tq > 0 && (!o->ptr || !d_o->ptr || !dq->ptr || !lse)) return RGD_E_NULL;
@@ -159,6 +181,17 @@ extern "C" int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_he
     fill_bwd(p, q, k, v, bias, o, d_o, dq, dk, dv, B, H, Tq, Tk, d, softmax_scale, causal);
     p.lse = const_cast<float *>(lse);
     p.delta = reinterpret_cast<float *>(workspace);
+    if (want_dbias && B > 0 && H > 0 && Tk > 0) {
+        if (dbias->kind == RGD_BIAS_VECTOR &&
+            cudaMemsetAsync(const_cast<void *>(dbias->ptr), 0, (size_t)(B * H * Tk) * sizeof(float), (cudaStream_t)stream) != cudaSuccess)
+            return RGD_E_DEVICE;
+        if (work && Tq > 0) {
+            p.dbias = const_cast<void *>(dbias->ptr);
+            p.db_sb = dbias->stride_b; p.db_sh = dbias->stride_h;
+            p.db_sq = dbias->kind == RGD_BIAS_MATRIX ? dbias->stride_q : 0;
+            p.dbias_vec = is_aligned(dbias->ptr, 16) && p.db_sb % 8 == 0 && p.db_sh % 8 == 0 && p.db_sq % 8 == 0;
+        }
+    }
     if (work && attn::tmem_bwd_eligible(p)) {
         const int rc = attn::tmem_bwd(p, dtype, cache, (cudaStream_t)stream);
         if (rc != attn::TMEM_NOT_TAKEN) return rc;

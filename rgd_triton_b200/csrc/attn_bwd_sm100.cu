@@ -53,6 +53,12 @@ struct BwdTmaParams {
     int H, Tq, Tk, Tq128, causal;
     float scale, scale_log2;
     int *status;
+    // bias gradient (null when not wanted): vector form fp32 [B, H, Tk], matrix form [B, H, Tq, Tk] in
+    // the tensor dtype; the kernels hold dS = scale * P (dP - delta), so they multiply by 1 / scale
+    void *dbias;
+    int64_t db_sb, db_sh, db_sq;
+    int dbias_vec;
+    float inv_scale;
 };
 
 // BSTAGES: stages of TMA-staged bias tiles (query rows x key columns, 16-bit, two
@@ -757,6 +763,7 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
             }
         }
 
+        float bsum = 0.f;                                  // vector-bias gradient of this key over this group's queries
         bool ok = true;
         for (int it = 0; it < nit; ++it) {
             const uint32_t par = (uint32_t)it & 1u;
@@ -870,6 +877,7 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                     const float a3 = pv[4 * i + 3] * fmaf(__uint_as_float(g[j + 3]), p.scale, -dd.w);
                     pk[2 * i] = pack16b<BF16>(a0, a1);
                     pk[2 * i + 1] = pack16b<BF16>(a2, a3);
+                    if constexpr (BIASM == 2) bsum += (a0 + a1) + (a2 + a3);
                 }
                 tmem_st32(lane_base + G2_COL + col, pk);
                 tmem_wait_st();
@@ -878,6 +886,13 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
             mbar_arrive(&sm.ds_ready[sb]);
         }
 
+        // vector-bias gradient: the two groups each add their half of the queries (two addends:
+        // the result does not depend on which lands first)
+        if constexpr (BIASM == 2) {
+            if (ok && p.dbias != nullptr && row < p.Tk)
+                atomicAdd(reinterpret_cast<float *>(p.dbias) + (int64_t)b * p.db_sb + (int64_t)h * p.db_sh + row,
+                          bsum * p.inv_scale);
+        }
         // epilogue: dV, dK -> global
         if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 93);
         tc_fence_after_sync();
@@ -1306,7 +1321,7 @@ struct alignas(1024) DqBiasSmem {
     uint32_t tmem_base;
 };
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool DBIAS>
 __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __grid_constant__ BwdTmaParams p,
                                                                        const void *q_base, const void *do_base,
                                                                        int64_t q_sb, int64_t q_sh, int64_t q_sn,
@@ -1555,6 +1570,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
             tc_fence_after_sync();
             {
                 uint32_t ga[32], gb[32], pk[32];
+                uint32_t qk[DBIAS ? 32 : 1];
                 tmem_ld32(lane_base + dcol, ga);
                 tmem_ld32(lane_base + dcol + 32, gb);
                 tmem_wait_ld();
@@ -1566,9 +1582,35 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
                     const float b0 = pv[32 + 2 * i] * fmaf(__uint_as_float(gb[2 * i]), p.scale, -dsc_row);
                     const float b1 = pv[32 + 2 * i + 1] * fmaf(__uint_as_float(gb[2 * i + 1]), p.scale, -dsc_row);
                     pk[16 + i] = pack16b<BF16>(b0, b1);
+                    if constexpr (DBIAS) {
+                        qk[i] = pack16b<BF16>(a0 * p.inv_scale, a1 * p.inv_scale);
+                        qk[16 + i] = pack16b<BF16>(b0 * p.inv_scale, b1 * p.inv_scale);
+                    }
                 }
                 // packed dS goes to the first 32 of this thread's 64 columns, all read already
                 tmem_st32(lane_base + dcol, pk);
+                if constexpr (DBIAS) {
+                    // bias gradient: this thread's row, the 64 keys of its half of block it
+                    const int k0 = it * BT + half * 64;
+                    if (row < p.Tq && k0 < p.Tk) {
+                        T *dst = reinterpret_cast<T *>(p.dbias) + (int64_t)b * p.db_sb + (int64_t)h * p.db_sh +
+                                 (int64_t)row * p.db_sq + k0;
+                        if (p.dbias_vec && k0 + 64 <= p.Tk) {
+#pragma unroll
+                            for (int c = 0; c < 8; ++c)
+                                __stcs(reinterpret_cast<uint4 *>(dst) + c,
+                                       make_uint4(qk[4 * c], qk[4 * c + 1], qk[4 * c + 2], qk[4 * c + 3]));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                union { uint32_t u; T v[2]; } cv;
+                                cv.u = qk[i];
+                                if (k0 + 2 * i < p.Tk) dst[2 * i] = cv.v[0];
+                                if (k0 + 2 * i + 1 < p.Tk) dst[2 * i + 1] = cv.v[1];
+                            }
+                        }
+                    }
+                }
                 tmem_wait_st();
             }
             tc_fence_before_sync();
@@ -1721,10 +1763,17 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     }
     if (bp.bias_vec == 2) {              // matrix bias staged by TMA
         const size_t smem = sizeof(DqBiasSmem<D>) + 1024;
-        if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16>), smem)) return e;
+        const bool db = bp.dbias != nullptr;
+        const void *kernel = db ? reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, true>)
+                                : reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, false>);
+        if (int e = ensure_dyn_smem(kernel, smem)) return e;
         dim3 grid((p.Tq + BT - 1) / BT, BH);
-        attn_bwd_dq_bias<D, BF16><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn, p.do_sb,
-                                                                         p.do_sh, p.do_sn);
+        if (db)
+            attn_bwd_dq_bias<D, BF16, true><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
+                                                                                   p.do_sb, p.do_sh, p.do_sn);
+        else
+            attn_bwd_dq_bias<D, BF16, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
+                                                                                    p.do_sb, p.do_sh, p.do_sn);
         count_launch();
         return check_launch();
     }
@@ -1745,14 +1794,6 @@ int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st) 
         return TMEM_NOT_TAKEN;
     bp.status = tmem_status_ptr();
     if (!bp.status) return RGD_E_DEVICE;
-    {
-        const int rows_per_cta = 256 / (p.d / 8);
-        dim3 grid((Tq128 + rows_per_cta - 1) / rows_per_cta, p.B * p.H);
-        if (bf16) attn_bwd_prep_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, lse2, delta_s, Tq128);
-        else attn_bwd_prep_kernel<__half><<<grid, 256, 0, st>>>(p, lse2, delta_s, Tq128);
-        count_launch();
-        if (int e = check_launch()) return e;
-    }
     bp.bias = p.bias; bp.b_sb = p.b_sb; bp.b_sh = p.b_sh; bp.b_sq = p.b_sq;
     bp.bias_kind = p.bias_kind; bp.bias_f32 = p.bias_f32;
     // bias_vec: 0 scalar loads, 1 rows are 16-byte addressable (vector loads), 2 staged through TMA
@@ -1765,6 +1806,23 @@ int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st) 
         bp.bias_vec = 2;
         bp.bias_h0 = p.b_sh == 0;
         bp.bias_b0 = p.b_sb == 0;
+    }
+    // The bias gradient comes out of the kernels that stage a matrix bias by TMA or take a vector
+    // bias, and they recover P (dP - delta) from dS by 1 / scale; anything else: general kernels.
+    bp.dbias = p.dbias; bp.db_sb = p.db_sb; bp.db_sh = p.db_sh; bp.db_sq = p.db_sq; bp.dbias_vec = p.dbias_vec;
+    if (p.dbias != nullptr) {
+        if (p.scale == 0.f) return TMEM_NOT_TAKEN;
+        if (p.bias_kind == RGD_BIAS_MATRIX && bp.bias_vec != 2) return TMEM_NOT_TAKEN;
+        if (p.bias_kind == RGD_BIAS_VECTOR && bp.bias_vec == 2) return TMEM_NOT_TAKEN;
+        bp.inv_scale = 1.f / p.scale;
+    }
+    {
+        const int rows_per_cta = 256 / (p.d / 8);
+        dim3 grid((Tq128 + rows_per_cta - 1) / rows_per_cta, p.B * p.H);
+        if (bf16) attn_bwd_prep_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, lse2, delta_s, Tq128);
+        else attn_bwd_prep_kernel<__half><<<grid, 256, 0, st>>>(p, lse2, delta_s, Tq128);
+        count_launch();
+        if (int e = check_launch()) return e;
     }
     bp.lse2 = lse2; bp.delta_s = delta_s;
     bp.H = p.H; bp.Tq = p.Tq; bp.Tk = p.Tk; bp.Tq128 = Tq128; bp.causal = p.causal;

@@ -207,6 +207,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_kv_general(const __grid_con
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc_dv[i][e] = acc_dk[i][e] = 0.f;
     const int krow[2] = {n0 + warp * 16 + g, n0 + warp * 16 + g + 8};
+    float dbs[2] = {0.f, 0.f};   // vector-bias gradient: sum over the queries of P (dP - delta) per key row
 
     // Causal: queries before this key block see none of its keys.
     const int m_begin = p.causal ? (n0 / BM) * BM : 0;
@@ -242,7 +243,9 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_kv_general(const __grid_con
                 if (bias_bh != nullptr && !masked) v += bias_at_t<T>(p, bias_bh, qi, kj);
                 const float pv = masked ? 0.f : exp2f((v - sm.lse[ql]) * LOG2E);
                 st[nt][e] = pv;                                            // P^T
-                dpt[nt][e] = pv * (dpt[nt][e] - sm.delta[ql]) * p.scale;   // dS^T
+                const float dsr = pv * (dpt[nt][e] - sm.delta[ql]);
+                dbs[e >> 1] += dsr;
+                dpt[nt][e] = dsr * p.scale;                                // dS^T
             }
         uint32_t pf[4][4];
         pack_p<T>(pf, st);
@@ -251,6 +254,17 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_kv_general(const __grid_con
         gemm_pn<T, DPAD>(acc_dk, pf, sm.q);               // dK += dS^T Q
     }
 
+    if (p.dbias != nullptr && p.bias_kind == RGD_BIAS_VECTOR) {
+        // the four lanes of a quad hold the same two key rows; one add per key in the whole grid
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            float v = dbs[hh];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if (t == 0 && krow[hh] < p.Tk)
+                atomicAdd(reinterpret_cast<float *>(p.dbias) + (int64_t)b * p.db_sb + (int64_t)h * p.db_sh + krow[hh], v);
+        }
+    }
     T *dvp = reinterpret_cast<T *>(p.dv) + (int64_t)b * p.dv_sb + (int64_t)h * p.dv_sh +
              (int64_t)(n0 + warp * 16) * p.dv_sn;
     T *dkp = reinterpret_cast<T *>(p.dk) + (int64_t)b * p.dk_sb + (int64_t)h * p.dk_sh +
@@ -282,6 +296,10 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_q_general(const __grid_cons
     if (p.bias_kind != RGD_BIAS_NONE)
         bias_bh = reinterpret_cast<const char *>(p.bias) +
                   ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : (int)sizeof(T));
+
+    T *dbias_bh = nullptr;       // matrix-bias gradient: P (dP - delta) element by element
+    if (p.dbias != nullptr && p.bias_kind == RGD_BIAS_MATRIX)
+        dbias_bh = reinterpret_cast<T *>(p.dbias) + (int64_t)b * p.db_sb + (int64_t)h * p.db_sh;
 
     load_tile<T, DPAD>(sm.q, qp, p.q_sn, q_valid, p.d, p.vec_q);
     load_tile<T, DPAD>(sm.d_o, gp, p.do_sn, q_valid, p.d, p.vec_do);
@@ -326,7 +344,9 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_q_general(const __grid_cons
                 const bool masked = kj >= p.Tk || qi >= p.Tq || (p.causal && kj > qi);
                 if (bias_bh != nullptr && !masked) v += bias_at_t<T>(p, bias_bh, qi, kj);
                 const float pv = masked ? 0.f : exp2f((v - lse_r[e >> 1]) * LOG2E);
-                s[nt][e] = pv * (dp[nt][e] - delta_r[e >> 1]) * p.scale;   // dS
+                const float dsr = pv * (dp[nt][e] - delta_r[e >> 1]);
+                if (dbias_bh != nullptr && qi < p.Tq && kj < p.Tk) dbias_bh[(int64_t)qi * p.db_sq + kj] = from_f32<T>(dsr);
+                s[nt][e] = dsr * p.scale;                                  // dS
             }
         uint32_t pf[4][4];
         pack_p<T>(pf, s);

@@ -32,6 +32,13 @@ struct AttnParams {
     int causal;
     float scale;
     int vec_q, vec_k, vec_v, vec_o, vec_do, vec_dq, vec_dk, vec_dv;   // 16-byte addressable
+    // Bias gradient (backward only), null when not wanted.  Vector bias: fp32 [B, H, Tk], zeroed by
+    // the entry point, each key's sum over the queries is added once or twice (the sum of two
+    // numbers does not depend on their order).  Matrix bias: [B, H, Tq, Tk] in the tensor dtype
+    // through element strides; entries of key blocks a causal mask skips are not written.
+    void *dbias;
+    int64_t db_sb, db_sh, db_sq;
+    int dbias_vec;                     // matrix form: rows are 16-byte addressable
 };
 
 template <typename T> struct Mma;

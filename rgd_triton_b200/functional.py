@@ -754,17 +754,21 @@ class FlashAttnFunc(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dlse):
         q, k, v, o, lse, bias = ctx.saved_tensors
-        _require(not ctx.needs_input_grad[3], "FlashAttention does not support bias gradient yet")
         cache = ctx.kernel_cache
-        dq, dk, dv = _attn_backward(q, k, v, bias, o, lse, do, ctx.causal, ctx.softmax_scale, cache)
+        want_dbias = bias is not None and ctx.needs_input_grad[3]
+        dq, dk, dv, dbias = _attn_backward(q, k, v, bias, o, lse, do, ctx.causal, ctx.softmax_scale, cache, want_dbias)
         if cache is not None:
             cache.bwd_odot = cache.bwd
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, dbias, None, None, None
 
 
-def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache):
+def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache, want_dbias=False):
+    """dq, dk, dv and, when asked for, the gradient of the bias (the reference refuses it,
+    flash_attn_triton_cached.py:1107): d bias = P * (dP - delta), summed over the dimensions along
+    which the bias is broadcast; a vector bias's sum over the queries is formed inside the dK/dV
+    kernel, a matrix bias's gradient is written by the dQ kernel."""
     do = _last_contig(do)
-    plan = _plan(cache, "bwd", _key(q, k, v, do, bias, extra=("attn", bool(causal))),
+    plan = _plan(cache, "bwd", _key(q, k, v, do, bias, extra=("attn", bool(causal), bool(want_dbias))),
                  lambda: _require(do.shape == q.shape and do.dtype == q.dtype, "dO must match q"))
     lib = _lib.load()
     batch, seqlen_q, nheads, d = q.shape
@@ -776,13 +780,31 @@ def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache):
     _require(nbytes >= 0, "attn_bwd: bad sizes")
     work = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
     qh, kh, vh, oh, doh, dqh, dkh, dvh = _heads_refs(plan, "h", (q, k, v, o, do, dq, dk, dv), _attn_heads)
+    dbias_s, dbuf = None, None
+    if want_dbias:
+        if bias_s.kind == _lib.RGD_BIAS_VECTOR:
+            dbuf = torch.empty((batch, nheads, 1, seqlen_k), dtype=torch.float32, device=q.device)   # zeroed by the call
+            dbias_s = Bias(dbuf.data_ptr(), nheads * seqlen_k, seqlen_k, 0, bias_s.kind, _lib.RGD_F32)
+        else:
+            # key blocks above the diagonal are skipped, not written, under a causal mask
+            make = torch.zeros if causal else torch.empty
+            dbuf = make((batch, nheads, seqlen_q, seqlen_k), dtype=q.dtype, device=q.device)
+            dbias_s = Bias(dbuf.data_ptr(), dbuf.stride(0), dbuf.stride(1), dbuf.stride(2), bias_s.kind,
+                           _lib.dtype_code(q.dtype))
     with _lib.device_guard(q):
-        code = lib.rgd_attn_bwd(qh, kh, vh, C.byref(bias_s), oh, lse.data_ptr(), doh, dqh, dkh, dvh, batch, nheads,
-                                seqlen_q, seqlen_k, d, float(softmax_scale), 1 if causal else 0, dt,
-                                work.data_ptr(), work.numel(), _native_cache(cache), _lib.stream_ptr())
+        code = lib.rgd_attn_bwd_dbias(qh, kh, vh, C.byref(bias_s), oh, lse.data_ptr(), doh, dqh, dkh, dvh,
+                                      None if dbias_s is None else C.byref(dbias_s), batch, nheads,
+                                      seqlen_q, seqlen_k, d, float(softmax_scale), 1 if causal else 0, dt,
+                                      work.data_ptr(), work.numel(), _native_cache(cache), _lib.stream_ptr())
     if code:
         _lib.check(code, "attn_bwd")
-    return dq, dk, dv
+    dbias = None
+    if want_dbias:
+        # sum over the dimensions along which the bias is broadcast, in fp32, one rounding
+        dims = [i for i in range(3) if bias.shape[i] == 1 and dbuf.shape[i] != 1]
+        dbias = (dbuf.sum(dim=dims, keepdim=True, dtype=torch.float32) if dims else dbuf).to(bias.dtype)
+        dbias = dbias.reshape(bias.shape)
+    return dq, dk, dv, dbias
 
 
 def _pad_head_dim_pays(q, k) -> bool:

@@ -15,7 +15,7 @@ on this route (a compiled graph calls the operator directly).
     torch.ops.rgd_b200.headln(q, k, heads_second, eps) -> (qo, ko)
     torch.ops.rgd_b200.rope(q, k, pos, cut_q, cut_k, heads_second, transposed) -> (qo, ko)
     torch.ops.rgd_b200.lnrope(q, k, pos, cut_q, cut_k, heads_second, eps) -> (qo, ko)
-    torch.ops.rgd_b200.attn(q, k, v, bias, causal, softmax_scale) -> (o, lse)
+    torch.ops.rgd_b200.attn(q, k, v, bias, causal, softmax_scale) -> (o, lse)      (bias may require grad)
 
 plus a ``*_bwd`` operator for each, which the autograd formulas call.
 """
@@ -205,8 +205,9 @@ def attn(q: Tensor, k: Tensor, v: Tensor, bias: Optional[Tensor], causal: bool,
 
 @_op("rgd_b200::attn_bwd", mutates_args=())
 def attn_bwd(q: Tensor, k: Tensor, v: Tensor, bias: Optional[Tensor], o: Tensor, lse: Tensor, do: Tensor,
-             causal: bool, softmax_scale: float) -> Tuple[Tensor, Tensor, Tensor]:
-    return F_._attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, None)
+             causal: bool, softmax_scale: float, want_dbias: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+    dq, dk, dv, dbias = F_._attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, None, want_dbias)
+    return dq, dk, dv, (q.new_empty(0) if dbias is None else dbias)
 
 
 def _attn_fake(q, k, v, bias, causal, softmax_scale):
@@ -215,8 +216,9 @@ def _attn_fake(q, k, v, bias, causal, softmax_scale):
 
 
 attn.register_fake(_attn_fake)
-attn_bwd.register_fake(lambda q, k, v, bias, o, lse, do, causal, softmax_scale:
-                       (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)))
+attn_bwd.register_fake(lambda q, k, v, bias, o, lse, do, causal, softmax_scale, want_dbias:
+                       (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v),
+                        torch.empty_like(bias) if want_dbias and bias is not None else q.new_empty(0)))
 
 
 def _attn_setup(ctx, inputs, output):
@@ -228,10 +230,9 @@ def _attn_setup(ctx, inputs, output):
 
 def _attn_backward(ctx, do, dlse):
     q, k, v, bias, o, lse = ctx.saved_tensors
-    if ctx.bias_needs_grad:
-        raise AssertionError("FlashAttention does not support bias gradient yet")
-    dq, dk, dv = torch.ops.rgd_b200.attn_bwd(q, k, v, bias, o, lse, do.contiguous(), ctx.causal, ctx.scale)
-    return dq, dk, dv, None, None, None
+    dq, dk, dv, dbias = torch.ops.rgd_b200.attn_bwd(q, k, v, bias, o, lse, do.contiguous(), ctx.causal, ctx.scale,
+                                                    ctx.bias_needs_grad)
+    return dq, dk, dv, (dbias if ctx.bias_needs_grad else None), None, None
 
 
 attn.register_autograd(_attn_backward, setup_context=_attn_setup)

@@ -219,10 +219,12 @@ def test_bias_shape_error_is_runtime_error():
         F_.flash_attn_func(q, q, q, torch.zeros(1, 2, 4, 8, device="cuda", dtype=torch.float16))
     with pytest.raises(AssertionError):
         F_.flash_attn_func(q, q, q, torch.zeros(1, 2, 8, 8, device="cuda", dtype=torch.float64))
+    # a bias that requires grad is not refused (the reference does, flash_attn_triton_cached.py:1107):
+    # its gradient is produced, see test_bias_gradient
     b = torch.zeros(1, 2, 8, 8, device="cuda", dtype=torch.float16, requires_grad=True)
     o = F_.flash_attn_func(q.clone().requires_grad_(True), q, q, b)
-    with pytest.raises(AssertionError):
-        o.sum().backward()
+    o.sum().backward()
+    assert b.grad is not None and b.grad.shape == b.shape
 
 
 def test_golden_vectors(golden):
@@ -404,3 +406,80 @@ def test_bounded_wait_gives_up_and_reports():
     g = gen(12)
     q, k, v, do = (randn(g, 1, 256, 2, 64, dtype=torch.bfloat16) for _ in range(4))
     check(q, k, v, do, None, False, "after time-out")
+
+
+# ----------------------------------------------------------------------------- bias gradient
+BIAS_GRAD_SHAPES = {
+    "vector": lambda B, H, tq, tk: (B, H, 1, tk),
+    "vector-shared": lambda B, H, tq, tk: (1, 1, 1, tk),
+    "vector-per-head": lambda B, H, tq, tk: (1, H, 1, tk),
+    "matrix": lambda B, H, tq, tk: (B, H, tq, tk),
+    "matrix-batch-shared": lambda B, H, tq, tk: (1, H, tq, tk),
+    "matrix-shared": lambda B, H, tq, tk: (1, 1, tq, tk),
+}
+
+
+def _lowp_bias_grad(q, k, v, do, bias, causal):
+    """Bias gradient of the low-precision eager attention (every op in q.dtype)."""
+    scale = 1.0 / math.sqrt(q.shape[-1])
+    b = bias.detach().clone().requires_grad_(True)
+    s = torch.einsum("bthd,bshd->bhts", q * scale, k) + b
+    if causal:
+        tq, tk = s.shape[-2:]
+        keep = torch.arange(tq)[:, None] >= torch.arange(tk)[None, :]
+        s = s.masked_fill(~keep, float("-inf"))
+    o = torch.einsum("bhts,bshd->bthd", torch.softmax(s, dim=-1), v)
+    return torch.autograd.grad(o, b, do)[0]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("kind", sorted(BIAS_GRAD_SHAPES))
+@pytest.mark.parametrize("d,tq,tk", [(64, 300, 328), (128, 257, 384), (128, 200, 333), (32, 130, 77), (64, 128, 128)])
+def test_bias_gradient(d, tq, tk, kind, causal, dt):
+    """The gradient of the additive bias (which the reference refuses,
+    flash_attn_triton_cached.py:1107): d bias = P (dP - delta) summed over the broadcast
+    dimensions, against the exact fp32 evaluation with the low-precision eager error as the
+    yardstick.  Sizes cover the kernels that stage a matrix bias by TMA (key count a multiple
+    of 8), the general kernels (odd key count, head_dim 32) and both vector-bias kernels."""
+    dtype = DTYPES[dt]
+    g = gen(7 * d + tq + len(kind) + int(causal))
+    B, H = 2, 3
+    q, do = randn(g, B, tq, H, d, dtype=dtype), randn(g, B, tq, H, d, dtype=dtype)
+    k, v = randn(g, B, tk, H, d, dtype=dtype), randn(g, B, tk, H, d, dtype=dtype)
+    bias = randn(g, *BIAS_GRAD_SHAPES[kind](B, H, tq, tk), dtype=dtype)
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    bd = bias.cuda().requires_grad_(True)
+    o = F_.flash_attn_func(qd, kd, vd, bd, causal)
+    dq, dk, dv, db = torch.autograd.grad(o, (qd, kd, vd, bd), do.cuda())
+    torch.cuda.synchronize()
+    assert db.shape == bias.shape and db.dtype == bias.dtype
+    exact = O.attn_bwd_dbias(q.float(), k.float(), v.float(), do.float(), bias.float(), causal)
+    lowp = _lowp_bias_grad(q, k, v, do, bias, causal)
+    # sums over up to B * H * tq terms: the floor scales with the magnitude of the result
+    floor = GRAD_FLOOR * max(1.0, exact.abs().max().item())
+    assert_attn(db.cpu(), exact, lowp, f"dbias {kind} d={d} causal={causal}", factor=2.0, floor=floor)
+    # dq, dk, dv of the same call hold the usual bar (a call that also wants the bias gradient may
+    # take other kernels than one that does not)
+    fb = bias.float()
+    exact3 = O.attn_bwd(q.float(), k.float(), v.float(), do.float(), fb, causal)
+    lowp3 = O.attn_lowp(q, k, v, do, bias, causal)[1:]
+    for got, e, l, name in zip((dq, dk, dv), exact3, lowp3, ("dq", "dk", "dv")):
+        assert_attn(got.cpu(), e, l, f"{name} with dbias {kind} d={d}", factor=2.0, floor=GRAD_FLOOR)
+
+
+def test_bias_gradient_fp32_bias_and_module():
+    """fp32 bias (its gradient comes back in fp32) through the module API."""
+    g = gen(77)
+    q, k, v, do = (randn(g, 1, 256, 2, 64, dtype=torch.bfloat16) for _ in range(4))
+    bias = randn(g, 1, 2, 256, 256, dtype=torch.float32)
+    m = ops.FlashAttention()
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    bd = bias.cuda().requires_grad_(True)
+    for _ in range(2):      # second call: launch cache hit
+        o = m(qd, kd, vd, bd)
+        db, = torch.autograd.grad(o, (bd,), do.cuda())
+    assert db.dtype == torch.float32
+    exact = O.attn_bwd_dbias(q.float(), k.float(), v.float(), do.float(), bias, False)
+    lowp = _lowp_bias_grad(q, k, v, do, bias.to(torch.bfloat16), False)
+    assert_attn(db.cpu(), exact, lowp.float(), "dbias fp32", factor=2.0, floor=GRAD_FLOOR)

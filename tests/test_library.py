@@ -32,5 +32,5 @@ def test_fake_implementations_give_the_kernels_shapes():
         assert qo.shape == q.shape
         o, lse = torch.ops.rgd_b200.attn(q, k, k, None, False, 0.1)
         assert o.shape == q.shape and lse.shape == (2, 4, 128) and lse.dtype == torch.float32
-        dq, dk, dv = torch.ops.rgd_b200.attn_bwd(q, k, k, None, o, lse, o, False, 0.1)
+        dq, dk, dv, dbias = torch.ops.rgd_b200.attn_bwd(q, k, k, None, o, lse, o, False, 0.1, False)
         assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == k.shape
