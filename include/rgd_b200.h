@@ -235,7 +235,28 @@ typedef struct rgd_bias {
     int64_t stride_q;   /* ignored for RGD_BIAS_VECTOR */
     int     kind;       /* RGD_BIAS_*                   */
     int     dtype;      /* the q dtype or RGD_F32       */
+    const void *tiles;  /* null, or the tile lists rgd_attn_bias_tiles_build
+                           made for exactly this tensor (RGD_BIAS_MATRIX only) */
 } rgd_bias;
+
+/* Block-sparse skip of masked bias tiles (the reference has only the dense
+ * form, flash_attn_triton_cached.py:151-175).  rgd_attn_bias_tiles_build reads
+ * a matrix bias once (16-bit dtype, dims as for the attention call, stride 0 on
+ * broadcast dims) and records which 128 x 128 tiles have an element above
+ * `threshold` (the additive-mask convention is -1e4; use -9984, which is what
+ * bf16 stores for it, so that masks of either 16-bit type count).  Passed back through
+ * rgd_bias.tiles, the tensor-memory kernels skip the other tiles: their
+ * probabilities are exp(-1e4 + ...) = 0 exactly in fp32, so the results are
+ * bit-identical PROVIDED |score * scale| stays far below |threshold| / 2.  A
+ * query block with a row that has no element >= threshold / 2 keeps its full
+ * list.  The lists are ignored with a causal mask, by the general kernels and by
+ * rgd_attn_bwd_dbias.  They describe the VALUES of the bias: rebuild after the
+ * tensor changes.  `tiles` must hold rgd_attn_bias_tiles_bytes(B, H, Tq, Tk)
+ * bytes, 16-byte aligned. */
+int64_t rgd_attn_bias_tiles_bytes(int64_t B, int64_t H, int64_t Tq, int64_t Tk);
+int rgd_attn_bias_tiles_build(const rgd_bias *bias, int64_t B, int64_t H,
+                              int64_t Tq, int64_t Tk, float threshold,
+                              void *tiles, int64_t tiles_bytes, void *stream);
 
 /* Rows of the log-sum-exp buffer: Tq rounded up to a multiple of 64, the
  * same rule as flash_attn_triton_cached.py:790-792. */
@@ -261,7 +282,8 @@ int64_t rgd_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq,
 
 /* dQ, dK, dV given dO.  Replaces _flash_attn_backward, including the
  * delta = rowsum(O * dO) pre-pass (flash_attn_triton_cached.py:885-1075).
- * Bias gradient is not produced (the reference refuses it, :1107). */
+ * The bias gradient (which the reference refuses, :1107) comes from
+ * rgd_attn_bwd_dbias. */
 int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v,
                  const rgd_bias *bias, const rgd_heads *o, const float *lse,
                  const rgd_heads *d_o, const rgd_heads *dq,

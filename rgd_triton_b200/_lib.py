@@ -39,7 +39,7 @@ class Heads(C.Structure):
 class Bias(C.Structure):
     """rgd_bias: additive attention bias, logically (B, H, Tq, Tk)."""
     _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_q", C.c_int64),
-                ("kind", C.c_int), ("dtype", C.c_int)]
+                ("kind", C.c_int), ("dtype", C.c_int), ("tiles", C.c_void_p)]
 
 
 _i64, _i32, _f32, _vp = C.c_int64, C.c_int, C.c_float, C.c_void_p
@@ -80,6 +80,8 @@ SIGNATURES = {
                      + [_i64] * 5 + [_f32, _i32, _i32, _vp, _i64, _vp, _vp]),
     "rgd_attn_bwd_dbias": (_i32, [_pHeads, _pHeads, _pHeads, _pBias, _pHeads, _vp, _pHeads, _pHeads, _pHeads, _pHeads, _pBias]
                            + [_i64] * 5 + [_f32, _i32, _i32, _vp, _i64, _vp, _vp]),
+    "rgd_attn_bias_tiles_bytes": (_i64, [_i64] * 4),
+    "rgd_attn_bias_tiles_build": (_i32, [_pBias, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _vp]),
     "rgd_attn_fwd_uses_tmem": (_i32, [_pHeads] * 4 + [_i64] * 5 + [_f32, _i32]),
     "rgd_attn_bwd_uses_tmem": (_i32, [_pHeads] * 8 + [_i64] * 5 + [_i32]),
 }

@@ -86,7 +86,7 @@ int cached_occupancy(const void *kernel, int threads, size_t smem) {
 
 }  // namespace rgd
 
-extern "C" int rgd_abi_version(void) { return 2; }
+extern "C" int rgd_abi_version(void) { return 3; }
 
 extern "C" int64_t rgd_launch_count(void) { return rgd::g_launches.load(std::memory_order_relaxed); }
 

@@ -14,6 +14,8 @@ bool tmem_bwd_eligible(const AttnParams &p);
 int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st);
 int bounded_wait_selftest(int64_t limit_ns, cudaStream_t st);
 int64_t tmem_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq);
+int build_bias_tiles(const void *bias, int64_t sb, int64_t sh, int64_t sq, int64_t Bb, int64_t Hb, int64_t Tq, int64_t Tk,
+                     int dtype, float thr, void *tiles, cudaStream_t st);
 }  // namespace attn
 }  // namespace rgd
 
@@ -62,6 +64,8 @@ void fill_common(AttnParams &p, const rgd_heads *q, const rgd_heads *k, const rg
         p.b_sq = bias->kind == RGD_BIAS_MATRIX ? bias->stride_q : 0;
         p.bias_kind = bias->kind;
         p.bias_f32 = bias->dtype == RGD_F32;
+        if (bias->kind == RGD_BIAS_MATRIX && !causal && bias->dtype != RGD_F32 && is_aligned(bias->tiles, 16))
+            p.tiles = reinterpret_cast<const uint16_t *>(bias->tiles);
     }
     p.B = (int)B; p.H = (int)H; p.Tq = (int)Tq; p.Tk = (int)Tk; p.d = (int)d;
     p.Tq_rounded = (int)lse_rows(Tq);
@@ -185,6 +189,7 @@ extern "C" int rgd_attn_bwd_dbias(const rgd_heads *q, const rgd_heads *k, const 
         if (dbias->kind == RGD_BIAS_VECTOR &&
             cudaMemsetAsync(const_cast<void *>(dbias->ptr), 0, (size_t)(B * H * Tk) * sizeof(float), (cudaStream_t)stream) != cudaSuccess)
             return RGD_E_DEVICE;
+        p.tiles = nullptr;      // a skipped tile's gradient entries would not be written
         if (work && Tq > 0) {
             p.dbias = const_cast<void *>(dbias->ptr);
             p.db_sb = dbias->stride_b; p.db_sh = dbias->stride_h;
@@ -207,6 +212,27 @@ extern "C" int rgd_attn_bwd_uses_tmem(const rgd_heads *q, const rgd_heads *k, co
     AttnParams p{};
     fill_bwd(p, q, k, v, nullptr, o, d_o, dq, dk, dv, B, H, Tq, Tk, d, 1.f, 0);
     return (B > 0 && H > 0 && d > 0 && attn::tmem_bwd_eligible(p)) ? 1 : 0;
+}
+
+extern "C" int64_t rgd_attn_bias_tiles_bytes(int64_t B, int64_t H, int64_t Tq, int64_t Tk) {
+    if (B < 0 || H < 0 || Tq < 0 || Tk < 0) return RGD_E_INVALID;
+    return attn::tile_layout(B, H, Tq, Tk).total_bytes;
+}
+
+extern "C" int rgd_attn_bias_tiles_build(const rgd_bias *bias, int64_t B, int64_t H, int64_t Tq, int64_t Tk,
+                                         float threshold, void *tiles, int64_t tiles_bytes, void *stream) {
+    if (!bias || !tiles) return RGD_E_NULL;
+    if (B < 0 || H < 0 || Tq < 0 || Tk < 0 || !(threshold < 0.f)) return RGD_E_INVALID;
+    if (bias->kind != RGD_BIAS_MATRIX) return RGD_E_BIAS_SHAPE;
+    if (bias->dtype != RGD_F16 && bias->dtype != RGD_BF16) return RGD_E_DTYPE;
+    if (bias->stride_b < 0 || bias->stride_h < 0 || bias->stride_q < Tk) return RGD_E_STRIDE;
+    if (!is_aligned(tiles, 16)) return RGD_E_STRIDE;
+    if (tiles_bytes < rgd_attn_bias_tiles_bytes(B, H, Tq, Tk)) return RGD_E_WORKSPACE;
+    if (B == 0 || H == 0 || Tq == 0 || Tk == 0) return RGD_OK;
+    if (!bias->ptr) return RGD_E_NULL;
+    const int64_t Bb = bias->stride_b == 0 ? 1 : B, Hb = bias->stride_h == 0 ? 1 : H;
+    return attn::build_bias_tiles(bias->ptr, bias->stride_b, bias->stride_h, bias->stride_q, Bb, Hb, Tq, Tk, bias->dtype,
+                                  threshold, tiles, (cudaStream_t)stream);
 }
 
 extern "C" int rgd_selftest_bounded_wait(int64_t limit_ns, void *stream) {

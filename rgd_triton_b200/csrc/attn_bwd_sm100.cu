@@ -59,6 +59,10 @@ struct BwdTmaParams {
     int64_t db_sb, db_sh, db_sq;
     int dbias_vec;
     float inv_scale;
+    // matrix bias with tile lists (optional, never with a causal mask): per key block of each bias
+    // slice the query blocks to visit (dK/dV kernel), per query block the key blocks (dQ kernel)
+    const uint16_t *tlk_cnt, *tlk_list, *tlq_cnt, *tlq_list;
+    int tl_nqb, tl_nkb;
 };
 
 // BSTAGES: stages of TMA-staged bias tiles (query rows x key columns, 16-bit, two
@@ -582,7 +586,18 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
     const int r0 = blk * BT;                               // first key of this CTA
     const int i_begin = p.causal ? r0 / BT : 0;
     const int i_end = (p.Tq + BT - 1) / BT;
-    const int nit = max(i_end - i_begin, 0);
+    int nit = max(i_end - i_begin, 0);
+    // query blocks to visit when the bias came with tile lists: the others hold only masked values
+    const uint16_t *tl = nullptr;
+    if constexpr (BIASM == 1) {
+        if (p.tlk_cnt != nullptr) {
+            const int64_t slice = (int64_t)(p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h);
+            const int64_t idx = slice * gridDim.x + blk;
+            tl = p.tlk_list + idx * p.tl_nqb;
+            nit = p.tlk_cnt[idx];
+        }
+    }
+    auto qblk = [&](int it) -> int { return tl != nullptr ? (int)tl[it] : i_begin + it; };
     const int nsub = 2 * nit;
     int *status = p.status;
 
@@ -632,7 +647,7 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 ok = mbar_wait(&sm.y_empty[s], ph ^ 1u, status, 71);
                 if (!ok) break;
                 mbar_expect_tx(&sm.y_full[s], 2 * TILE_BYTES + (STAGE_STATS ? 2 * BT * 4 : 0));
-                const int row = (i_begin + it) * BT;
+                const int row = qblk(it) * BT;
                 if constexpr (STAGE_STATS) {
                     bulk_load_1d(sm.lse_s[s], p.lse2 + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
                     bulk_load_1d(sm.dsc_s[s], p.delta_s + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
@@ -767,7 +782,7 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
         bool ok = true;
         for (int it = 0; it < nit; ++it) {
             const uint32_t par = (uint32_t)it & 1u;
-            const int blk0 = (i_begin + it) * BT;
+            const int blk0 = qblk(it) * BT;
             const int c0 = blk0 + sb * 64;                 // first query of the sub-block
             const bool slow = cta_key_tail || (p.causal && blk0 == r0);
             const int s = it & 1;
@@ -1343,7 +1358,16 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
     const int b = bh / p.H, h = bh - b * p.H;
     const int r0 = blk * BT;                               // first query of this CTA
     const int i_end = ((p.causal ? min(p.Tk, r0 + BT) : p.Tk) + BT - 1) / BT;
-    const int nit = max(i_end, 0);
+    int nit = max(i_end, 0);
+    // key blocks to visit when the bias came with tile lists: the others hold only masked values
+    const uint16_t *tl = nullptr;
+    if (p.tlq_cnt != nullptr) {
+        const int64_t slice = (int64_t)(p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h);
+        const int64_t idx = slice * gridDim.x + blk;
+        tl = p.tlq_list + idx * p.tl_nkb;
+        nit = p.tlq_cnt[idx];
+    }
+    auto kblk = [&](int it) -> int { return tl != nullptr ? (int)tl[it] : it; };
     int *status = p.status;
 
     if (threadIdx.x == 0) {
@@ -1385,7 +1409,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
             int ks = 0;
             uint32_t kph = 0;                              // phase of the K ring slot's previous use
             for (int it = 0; it < nit; ++it) {
-                const int row = it * BT;
+                const int row = kblk(it) * BT;
                 ok = mbar_wait(&sm.k_empty[ks], kph ^ 1u, status, 41);
                 if (!ok) break;
                 mbar_expect_tx(&sm.k_full[ks], TILE_BYTES);
@@ -1539,7 +1563,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
             tmem_wait_ld();
             tc_fence_before_sync();
             mbar_arrive(&sm.s_read);
-            const int blk0 = j * BT;
+            const int blk0 = kblk(j) * BT;
             // blocks that need per-element masking: the diagonal blocks under the causal mask
             // and the block touching the end of the keys
             const bool slow = (p.causal && blk0 + BT > r0) || blk0 + BT > p.Tk;
@@ -1591,7 +1615,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
                 tmem_st32(lane_base + dcol, pk);
                 if constexpr (DBIAS) {
                     // bias gradient: this thread's row, the 64 keys of its half of block it
-                    const int k0 = it * BT + half * 64;
+                    const int k0 = kblk(it) * BT + half * 64;
                     if (row < p.Tq && k0 < p.Tk) {
                         T *dst = reinterpret_cast<T *>(p.dbias) + (int64_t)b * p.db_sb + (int64_t)h * p.db_sh +
                                  (int64_t)row * p.db_sq + k0;
@@ -1809,6 +1833,15 @@ int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st) 
     }
     // The bias gradient comes out of the kernels that stage a matrix bias by TMA or take a vector
     // bias, and they recover P (dP - delta) from dS by 1 / scale; anything else: general kernels.
+    if (bp.bias_vec == 2 && p.tiles != nullptr && !p.causal && p.dbias == nullptr) {
+        const TileLayout L = tile_layout(bp.bias_b0 ? 1 : p.B, bp.bias_h0 ? 1 : p.H, p.Tq, p.Tk);
+        bp.tlk_cnt = p.tiles + L.kcnt;
+        bp.tlk_list = p.tiles + L.klist;
+        bp.tlq_cnt = p.tiles + L.qcnt;
+        bp.tlq_list = p.tiles + L.qlist;
+        bp.tl_nqb = L.nqb;
+        bp.tl_nkb = L.nkb;
+    }
     bp.dbias = p.dbias; bp.db_sb = p.db_sb; bp.db_sh = p.db_sh; bp.db_sq = p.db_sq; bp.dbias_vec = p.dbias_vec;
     if (p.dbias != nullptr) {
         if (p.scale == 0.f) return TMEM_NOT_TAKEN;

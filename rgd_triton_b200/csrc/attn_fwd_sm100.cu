@@ -56,6 +56,10 @@ struct FwdTmaParams {
     int H, Tq, Tk, Tq_rounded, causal;
     float scale_log2;   // softmax_scale * log2(e)
     int *status;        // device status word (bounded waits report here)
+    // BIAS == 2, optional: per 256-query block of each bias slice, the key blocks to visit (the
+    // others hold only masked bias values); null = all of them
+    const uint16_t *tl_cnt, *tl_list;
+    int tl_nkb;
 };
 
 // NT: query tiles per CTA.  VS: stages of V.  BS: stages of TMA-staged bias tiles per query tile
@@ -217,6 +221,19 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
         const int n_end = p.causal ? min(p.Tk, mt + TM) : p.Tk;
         nb[t] = (t < NT && mt < p.Tq) ? (n_end + TN - 1) / TN : 0;
     }
+    // Key blocks to visit when the bias came with tile lists (never together with a causal mask)
+    const uint16_t *tl = nullptr;
+    if constexpr (BIAS == 2) {
+        if (p.tl_cnt != nullptr) {
+            const int64_t slice = (int64_t)(p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h);
+            const int64_t idx = slice * gridDim.x + mblk;
+            tl = p.tl_list + idx * p.tl_nkb;
+            const int cnt = p.tl_cnt[idx];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) nb[t] = nb[t] > 0 ? cnt : 0;
+        }
+    }
+    auto kblk = [&](int j) -> int { return tl != nullptr ? (int)tl[j] : j; };
     const int nblk = max(nb[0], nb[1]);
     int *status = p.status;
 
@@ -267,7 +284,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 if (!ok) break;
                 mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
                 for (int hh = 0; hh < HALVES; ++hh)
-                    tma_load_4d(sm.k[s] + hh * PANEL, &p.mk, &sm.k_full[s], hh * 64, j * TN, h, b);
+                    tma_load_4d(sm.k[s] + hh * PANEL, &p.mk, &sm.k_full[s], hh * 64, kblk(j) * TN, h, b);
                 if constexpr (BIAS == 2) {
                     const int bs = j % BS;
                     const uint32_t bph = (uint32_t)(j / BS) & 1u;
@@ -278,7 +295,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                         mbar_expect_tx(&sm.b_full[t][bs], BIAS_BYTES);
                         for (int pn = 0; pn < 2; ++pn)
                             tma_load_4d(sm.bias[t * BS + bs] + pn * (TM * 128), &p.mbias, &sm.b_full[t][bs],
-                                        j * TN + pn * 64, m0 + t * TM, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                                        kblk(j) * TN + pn * 64, m0 + t * TM, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
                     }
                     if (!ok) break;
                 }
@@ -287,7 +304,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 if (!ok) break;
                 mbar_expect_tx(&sm.v_full[vs], TILE_BYTES);
                 for (int hh = 0; hh < HALVES; ++hh)
-                    tma_load_4d(sm.v[vs] + hh * PANEL, &p.mv, &sm.v_full[vs], hh * 64, j * TN, h, b);
+                    tma_load_4d(sm.v[vs] + hh * PANEL, &p.mv, &sm.v_full[vs], hh * 64, kblk(j) * TN, h, b);
             }
             if (!ok) {
                 // Give copies already in flight time to land before the CTA goes away.
@@ -413,7 +430,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 if (!ok) break;
                 btile = sm.bias[t * BSD + (j % BSD)];
             }
-            const int n0 = j * TN;
+            const int n0 = kblk(j) * TN;
             const bool need_mask = (n0 + TN > p.Tk) || (p.causal && n0 + TN > m0 + t * TM);
 
             const uint32_t s_addr = lane_base + s_col;
@@ -832,6 +849,12 @@ int tmem_fwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st) 
         bias_mode = 2;
         fp.bias_h0 = p.b_sh == 0;
         fp.bias_b0 = p.b_sb == 0;
+    }
+    if (bias_mode == 2 && p.tiles != nullptr && !p.causal) {
+        const TileLayout L = tile_layout(fp.bias_b0 ? 1 : p.B, fp.bias_h0 ? 1 : p.H, p.Tq, p.Tk);
+        fp.tl_cnt = p.tiles + L.q2cnt;
+        fp.tl_list = p.tiles + L.q2list;
+        fp.tl_nkb = L.nkb;
     }
     fp.lse = p.lse;
     fp.H = p.H; fp.Tq = p.Tq; fp.Tk = p.Tk; fp.Tq_rounded = p.Tq_rounded; fp.causal = p.causal;

@@ -39,7 +39,40 @@ struct AttnParams {
     void *dbias;
     int64_t db_sb, db_sh, db_sq;
     int dbias_vec;                     // matrix form: rows are 16-byte addressable
+    // Tile lists of a matrix bias (attn_tiles.cu), null when not given: which 128 x 128 tiles are
+    // not entirely masked.  Used by the kernels that stage the bias by TMA, without a causal mask.
+    const uint16_t *tiles;
 };
+
+// Layout of the tile-list buffer of one bias tensor with Bb x Hb distinct (batch, head) slices
+// (1 where the bias is broadcast), in 16-bit words from its start; the byte bitmap follows.
+//   qcnt [Bb Hb][nqb], qlist [Bb Hb][nqb][nkb]: per 128-query block, the key blocks to visit
+//   q2cnt [Bb Hb][nq2], q2list [Bb Hb][nq2][nkb]: the same per 256-query block (union of two)
+//   kcnt [Bb Hb][nkb], klist [Bb Hb][nkb][nqb]: per 128-key block, the query blocks to visit
+struct TileLayout {
+    int64_t slices;
+    int nqb, nq2, nkb;
+    int64_t qcnt, qlist, q2cnt, q2list, kcnt, klist, words;   // offsets in 16-bit words
+    int64_t bitmap_bytes, total_bytes;
+};
+inline TileLayout tile_layout(int64_t Bb, int64_t Hb, int64_t Tq, int64_t Tk) {
+    TileLayout L{};
+    L.slices = Bb * Hb;
+    L.nqb = (int)((Tq + 127) / 128);
+    L.nq2 = (int)((Tq + 255) / 256);
+    L.nkb = (int)((Tk + 127) / 128);
+    int64_t w = 0;
+    L.qcnt = w;   w += L.slices * L.nqb;
+    L.qlist = w;  w += L.slices * L.nqb * L.nkb;
+    L.q2cnt = w;  w += L.slices * L.nq2;
+    L.q2list = w; w += L.slices * L.nq2 * L.nkb;
+    L.kcnt = w;   w += L.slices * L.nkb;
+    L.klist = w;  w += L.slices * L.nkb * L.nqb;
+    L.words = (w + 7) / 8 * 8;
+    L.bitmap_bytes = L.slices * L.nqb * L.nkb;
+    L.total_bytes = L.words * 2 + (L.bitmap_bytes + 15) / 16 * 16;
+    return L;
+}
 
 template <typename T> struct Mma;
 template <> struct Mma<__half> {

@@ -37,6 +37,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import weakref
 
 import torch
 
@@ -688,7 +689,7 @@ def _prep_bias(bias, q, seqlen_q: int, seqlen_k: int):
     """Validate the bias and return (last-dim-contiguous bias, rgd_bias struct).
     Same rules as flash_attn_triton_cached.py:771-788."""
     if bias is None:
-        return None, Bias(None, 0, 0, 0, _lib.RGD_BIAS_NONE, _lib.RGD_F32)
+        return None, Bias(None, 0, 0, 0, _lib.RGD_BIAS_NONE, _lib.RGD_F32, None)
     batch, _, nheads, _ = q.shape
     _require(bias.dtype in (q.dtype, torch.float32), "bias must have q's dtype or float32")
     _require(bias.is_cuda and bias.device == q.device, "bias must be on q's device")
@@ -703,7 +704,7 @@ def _prep_bias(bias, q, seqlen_q: int, seqlen_k: int):
         raise RuntimeError("Last 2 dimensions of bias must be (1, seqlen_k) or (seqlen_q, seqlen_k)")
     full = bias.expand(batch, nheads, seqlen_q, seqlen_k)   # broadcast dims get stride 0
     sq = full.stride(2) if kind == _lib.RGD_BIAS_MATRIX else 0
-    return bias, Bias(full.data_ptr(), full.stride(0), full.stride(1), sq, kind, _lib.dtype_code(full.dtype))
+    return bias, Bias(full.data_ptr(), full.stride(0), full.stride(1), sq, kind, _lib.dtype_code(full.dtype), None)
 
 
 def _check_attn(q, k, v) -> None:
@@ -719,6 +720,49 @@ def _check_attn(q, k, v) -> None:
         _lib.require_device(t)
 
 
+# Block-sparse skip of masked bias tiles.  A matrix bias that a module's cache sees for the second
+# time (the same tensor object, unchanged: identity through a weak reference plus the tensor's
+# version counter) is scanned once for 128 x 128 tiles whose every element is <= -1e4 (-9984, which is
+# what bf16 makes of -1e4); the
+# tensor-memory kernels then skip those tiles (their probabilities are exactly zero, so results are
+# bit-identical as long as |score * scale| stays far below 5e3; a query block containing a row with
+# no unmasked key keeps all its tiles).  One-shot biases are never scanned: the scan reads the
+# whole bias once, which only pays when the result is reused.
+_SKIP_MASKED_TILES = True
+_SKIP_THRESHOLD = -9984.0   # -1e4 as bf16 stores it (fp16 and fp32 hold -1e4 itself): masked means <= this
+_SKIP_MIN_TILES = 64        # score tiles per (batch, head) below which the lists are not worth making
+
+
+def set_skip_masked_tiles(enable: bool) -> bool:
+    """Turn the block-sparse skip of masked bias tiles on or off; returns the previous setting."""
+    global _SKIP_MASKED_TILES
+    prev, _SKIP_MASKED_TILES = _SKIP_MASKED_TILES, bool(enable)
+    return prev
+
+
+def _bias_tiles(cache, bias, bias_t, bias_s, q, seqlen_q, seqlen_k, causal):
+    """The tile-list buffer for this bias, or None (see above)."""
+    if (cache is None or bias is None or causal or not _SKIP_MASKED_TILES or bias_s.kind != _lib.RGD_BIAS_MATRIX
+            or bias_t.dtype == torch.float32 or bias.requires_grad or _tracing()
+            or ((seqlen_q + 127) // 128) * ((seqlen_k + 127) // 128) < _SKIP_MIN_TILES):
+        return None
+    ent = getattr(cache, "_tiles", None)
+    ver = bias._version
+    if ent is not None and ent[0]() is bias and ent[1] == ver:
+        if ent[2] is None:          # seen before, unchanged: scan it now
+            lib = _lib.load()
+            batch, _, nheads, _ = q.shape
+            nbytes = int(lib.rgd_attn_bias_tiles_bytes(batch, nheads, seqlen_q, seqlen_k))
+            buf = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+            with _lib.device_guard(q):
+                code = lib.rgd_attn_bias_tiles_build(C.byref(bias_s), batch, nheads, seqlen_q, seqlen_k,
+                                                     _SKIP_THRESHOLD, buf.data_ptr(), buf.numel(), _lib.stream_ptr())
+            ent[2] = buf if code == 0 else False
+        return ent[2] if torch.is_tensor(ent[2]) else None
+    cache._tiles = [weakref.ref(bias), ver, None]
+    return None
+
+
 def _attn_forward(q, k, v, bias, causal, softmax_scale, cache):
     q, k, v = _last_contig(q), _last_contig(k), _last_contig(v)
     plan = _plan(cache, "fwd", _key(q, k, v, bias, extra=("attn", bool(causal))), lambda: _check_attn(q, k, v))
@@ -727,6 +771,9 @@ def _attn_forward(q, k, v, bias, causal, softmax_scale, cache):
     seqlen_k = k.shape[1]
     softmax_scale = softmax_scale or 1.0 / math.sqrt(d)
     bias_t, bias_s = _prep_bias(bias, q, seqlen_q, seqlen_k)
+    tiles = _bias_tiles(cache, bias, bias_t, bias_s, q, seqlen_q, seqlen_k, causal)
+    if tiles is not None:
+        bias_s.tiles = tiles.data_ptr()
     o = torch.empty_like(q)
     lse_rows, dt = _const(plan, "c", lambda: (int(lib.rgd_attn_lse_rows(seqlen_q)), _lib.dtype_code(q.dtype)))
     lse = torch.empty((batch, nheads, lse_rows), device=q.device, dtype=torch.float32)
@@ -736,7 +783,7 @@ def _attn_forward(q, k, v, bias, causal, softmax_scale, cache):
                                 float(softmax_scale), 1 if causal else 0, dt, _native_cache(cache), _lib.stream_ptr())
     if code:
         _lib.check(code, "attn_fwd")
-    return q, k, v, o, lse, bias_t, softmax_scale
+    return q, k, v, o, lse, bias_t, softmax_scale, tiles
 
 
 class FlashAttnFunc(torch.autograd.Function):
@@ -745,9 +792,10 @@ class FlashAttnFunc(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, bias=None, causal=False, softmax_scale=None, kernel_cache=None):
-        q, k, v, o, lse, bias_t, softmax_scale = _attn_forward(q, k, v, bias, causal, softmax_scale, kernel_cache)
+        q, k, v, o, lse, bias_t, softmax_scale, tiles = _attn_forward(q, k, v, bias, causal, softmax_scale, kernel_cache)
         ctx.save_for_backward(q, k, v, o, lse, bias_t)
         ctx.causal, ctx.softmax_scale, ctx.kernel_cache = causal, softmax_scale, kernel_cache
+        ctx.tiles = tiles           # the backward of this call skips the same tiles
         ctx.mark_non_differentiable(lse)
         return o, lse
 
@@ -756,13 +804,14 @@ class FlashAttnFunc(torch.autograd.Function):
         q, k, v, o, lse, bias = ctx.saved_tensors
         cache = ctx.kernel_cache
         want_dbias = bias is not None and ctx.needs_input_grad[3]
-        dq, dk, dv, dbias = _attn_backward(q, k, v, bias, o, lse, do, ctx.causal, ctx.softmax_scale, cache, want_dbias)
+        dq, dk, dv, dbias = _attn_backward(q, k, v, bias, o, lse, do, ctx.causal, ctx.softmax_scale, cache, want_dbias,
+                                           ctx.tiles)
         if cache is not None:
             cache.bwd_odot = cache.bwd
         return dq, dk, dv, dbias, None, None, None
 
 
-def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache, want_dbias=False):
+def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache, want_dbias=False, tiles=None):
     """dq, dk, dv and, when asked for, the gradient of the bias (the reference refuses it,
     flash_attn_triton_cached.py:1107): d bias = P * (dP - delta), summed over the dimensions along
     which the bias is broadcast; a vector bias's sum over the queries is formed inside the dK/dV
@@ -774,6 +823,8 @@ def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache, want
     batch, seqlen_q, nheads, d = q.shape
     seqlen_k = k.shape[1]
     _, bias_s = _prep_bias(bias, q, seqlen_q, seqlen_k)
+    if tiles is not None and not want_dbias:
+        bias_s.tiles = tiles.data_ptr()
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dt, nbytes = _const(plan, "c", lambda: (_lib.dtype_code(q.dtype), int(lib.rgd_attn_bwd_workspace_bytes(
         batch, nheads, seqlen_q, seqlen_k, d, _lib.dtype_code(q.dtype)))))
@@ -784,13 +835,13 @@ def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache, want
     if want_dbias:
         if bias_s.kind == _lib.RGD_BIAS_VECTOR:
             dbuf = torch.empty((batch, nheads, 1, seqlen_k), dtype=torch.float32, device=q.device)   # zeroed by the call
-            dbias_s = Bias(dbuf.data_ptr(), nheads * seqlen_k, seqlen_k, 0, bias_s.kind, _lib.RGD_F32)
+            dbias_s = Bias(dbuf.data_ptr(), nheads * seqlen_k, seqlen_k, 0, bias_s.kind, _lib.RGD_F32, None)
         else:
             # key blocks above the diagonal are skipped, not written, under a causal mask
             make = torch.zeros if causal else torch.empty
             dbuf = make((batch, nheads, seqlen_q, seqlen_k), dtype=q.dtype, device=q.device)
             dbias_s = Bias(dbuf.data_ptr(), dbuf.stride(0), dbuf.stride(1), dbuf.stride(2), bias_s.kind,
-                           _lib.dtype_code(q.dtype))
+                           _lib.dtype_code(q.dtype), None)
     with _lib.device_guard(q):
         code = lib.rgd_attn_bwd_dbias(qh, kh, vh, C.byref(bias_s), oh, lse.data_ptr(), doh, dqh, dkh, dvh,
                                       None if dbias_s is None else C.byref(dbias_s), batch, nheads,
@@ -841,7 +892,7 @@ def flash_attn_func(q, k, v, bias=None, causal=False, softmax_scale=None, return
         o = res[0][..., :d].contiguous()
         return (o, res[1]) if return_lse else o
     if not _needs_grad(q, k, v, bias):
-        _, _, _, o, lse, _, _ = _attn_forward(q, k, v, bias, causal, softmax_scale, kernel_cache)
+        _, _, _, o, lse, _, _, _ = _attn_forward(q, k, v, bias, causal, softmax_scale, kernel_cache)
     else:
         o, lse = FlashAttnFunc.apply(q, k, v, bias, causal, softmax_scale, kernel_cache)
     return (o, lse) if return_lse else o

@@ -199,7 +199,7 @@ lnrope.register_autograd(_lnrope_backward, setup_context=_lnrope_setup)
 @_op("rgd_b200::attn", mutates_args=())
 def attn(q: Tensor, k: Tensor, v: Tensor, bias: Optional[Tensor], causal: bool,
          softmax_scale: float) -> Tuple[Tensor, Tensor]:
-    _, _, _, o, lse, _, _ = F_._attn_forward(q, k, v, bias, causal, softmax_scale, None)
+    _, _, _, o, lse, _, _, _ = F_._attn_forward(q, k, v, bias, causal, softmax_scale, None)
     return o, lse
 
 

@@ -56,16 +56,17 @@ class _LaunchCache:
                 pass
 
     # the native handle belongs to this process and this object only
-    # (the marshalled arguments kept under "_plan_*" hold raw pointers: they stay behind too)
+    # (the marshalled arguments kept under "_plan_*" hold raw pointers and "_tiles" the tile lists of
+    # the last bias tensor: they stay behind too)
     def __getstate__(self):
-        state = {k: v for k, v in vars(self).items() if not k.startswith("_plan_")}
+        state = {k: v for k, v in vars(self).items() if not k.startswith("_plan_") and k != "_tiles"}
         state["_native"] = None
         return state
 
     def __deepcopy__(self, memo):
         new = _LaunchCache(())
         for k, v in vars(self).items():
-            if not k.startswith("_plan_"):
+            if not k.startswith("_plan_") and k != "_tiles":
                 setattr(new, k, None if k == "_native" else v)
         return new
 

@@ -47,7 +47,7 @@ def test_status_strings_and_version(lib):
     assert lib.rgd_status_string(0) == b"ok"
     assert b"bias" in lib.rgd_status_string(-8)
     assert b"unknown" in lib.rgd_status_string(-999)
-    assert lib.rgd_abi_version() >= 2
+    assert lib.rgd_abi_version() >= 3
     lib.rgd_attn_lse_rows.restype = ctypes.c_int64
     lib.rgd_attn_lse_rows.argtypes = [ctypes.c_int64]
     assert [lib.rgd_attn_lse_rows(n) for n in (0, 1, 64, 65, 4096)] == [0, 64, 64, 128, 4096]
@@ -67,7 +67,7 @@ def test_argument_errors_need_no_gpu(lib):
     h = _lib.Heads(None, 0, 0, 0)
     hp = ctypes.byref(h)
     assert L.rgd_headln_fwd(hp, hp, hp, hp, 1, 1, 4, 4, 512, 1e-6, 0, None) == _lib.RGD_E_SIZE
-    b = _lib.Bias(None, 0, 0, 0, 5, 0)
+    b = _lib.Bias(None, 0, 0, 0, 5, 0, None)
     assert L.rgd_attn_fwd(hp, hp, hp, ctypes.byref(b), hp, None, 1, 1, 4, 4, 64, 1.0, 0, 2, None, None) \
         == _lib.RGD_E_BIAS_SHAPE
     assert L.rgd_attn_fwd(hp, hp, hp, None, hp, None, 1, 1, 4, 4, 256, 1.0, 0, 2, None, None) == _lib.RGD_E_SIZE

@@ -483,3 +483,120 @@ def test_bias_gradient_fp32_bias_and_module():
     exact = O.attn_bwd_dbias(q.float(), k.float(), v.float(), do.float(), bias, False)
     lowp = _lowp_bias_grad(q, k, v, do, bias.to(torch.bfloat16), False)
     assert_attn(db.cpu(), exact, lowp.float(), "dbias fp32", factor=2.0, floor=GRAD_FLOOR)
+
+
+# ----------------------------------------------------------------------------- masked bias tiles
+def _tile_layout(slices, tq, tk):
+    """Offsets (16-bit words) of the tile-list buffer, as include/rgd_b200.h's builder lays it out."""
+    nqb, nq2, nkb = (tq + 127) // 128, (tq + 255) // 256, (tk + 127) // 128
+    off, w = {}, 0
+    for name, n in (("qcnt", nqb), ("qlist", nqb * nkb), ("q2cnt", nq2), ("q2list", nq2 * nkb), ("kcnt", nkb),
+                    ("klist", nkb * nqb)):
+        off[name] = w
+        w += slices * n
+    return off, nqb, nq2, nkb
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("form", ["full", "batch-shared", "head-shared"])
+@pytest.mark.parametrize("mask", ["blocks", "key-padding", "dead-row"])
+def test_masked_bias_tiles_are_skipped_with_identical_results(d, form, mask):
+    """Block-sparse skip (SURVEY 8(f)2 of the reference has only the dense form,
+    flash_attn_triton_cached.py:151-175): a bias reused through a module's cache gets tile lists
+    from its second forward on, the kernels visit only listed tiles, and o, dq, dk, dv are
+    bit-identical to the dense evaluation.  The lists themselves are checked against the mask."""
+    dt = torch.bfloat16 if d == 128 else torch.float16
+    g = gen(31 * d + len(form) + len(mask))
+    B, H, tq, tk = 2, 3, 1100, 1160
+    q, do = randn(g, B, tq, H, d, dtype=dt), randn(g, B, tq, H, d, dtype=dt)
+    k, v = randn(g, B, tk, H, d, dtype=dt), randn(g, B, tk, H, d, dtype=dt)
+    Bb, Hb = (1 if form == "batch-shared" else B), (1 if form == "head-shared" else H)
+    bias = torch.randn(Bb, Hb, tq, tk, generator=g)
+    nqb, nkb = (tq + 127) // 128, (tk + 127) // 128
+    if mask == "blocks":
+        blk = torch.rand(Bb, Hb, nqb, nkb, generator=g) < 0.4
+        blk[..., torch.arange(nqb), torch.arange(nqb)] = False          # every row keeps its diagonal tile
+        big = blk.repeat_interleave(128, 2).repeat_interleave(128, 3)[:, :, :tq, :tk]
+    elif mask == "key-padding":
+        big = torch.zeros(Bb, Hb, tq, tk, dtype=torch.bool)
+        big[..., tk - 300:] = True                                       # 300 padded keys: two whole tiles and a part
+    else:
+        big = torch.zeros(Bb, Hb, tq, tk, dtype=torch.bool)
+        big[..., 128:] = True                                            # only the first key tile is alive ...
+        big[0, 0, 700, :] = True                                         # ... and one row has no unmasked key at all
+    bias = (bias - 1e4 * big).to(dt)
+
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    bd, dod = bias.cuda(), do.cuda()
+
+    def run(module):
+        o = module(qd, kd, vd, bd)
+        return [o.detach(), *torch.autograd.grad(o, (qd, kd, vd), dod)]
+
+    prev = F_.set_skip_masked_tiles(False)
+    try:
+        dense = run(ops.FlashAttention())
+    finally:
+        F_.set_skip_masked_tiles(prev)
+    m = ops.FlashAttention()
+    for call in range(3):
+        got = run(m)
+        for a, b_, name in zip(got, dense, ("o", "dq", "dk", "dv")):
+            assert torch.equal(a, b_), f"call {call}: {name} differs from the dense evaluation"
+    torch.cuda.synchronize()
+    ent = m.cache._tiles
+    assert ent[0]() is bd and torch.is_tensor(ent[2]), "the bias was not scanned on its second use"
+
+    # the lists against the mask: a tile is listed iff it has an element > -9984 (bf16's -1e4), except
+    # that a query block holding a row without any element >= -4992 lists every tile
+    words = ent[2].cpu().view(torch.int16).to(torch.int32) & 0xFFFF
+    off, nqb, nq2, nkb = _tile_layout(Bb * Hb, tq, tk)
+    bf = bias.float()
+    for s_ in range(Bb * Hb):
+        sl = bf[s_ // Hb, s_ % Hb]
+        live = torch.zeros(nqb, nkb, dtype=torch.bool)
+        for i in range(nqb):
+            rows = sl[128 * i:128 * i + 128]
+            for j in range(nkb):
+                live[i, j] = bool((rows[:, 128 * j:128 * j + 128] > -9984.0).any())
+            if bool((rows.max(dim=1).values < -4992.0).any()):
+                live[i, :] = True
+        for i in range(nqb):
+            n = int(words[off["qcnt"] + s_ * nqb + i])
+            lst = words[off["qlist"] + (s_ * nqb + i) * nkb:][:n].tolist()
+            assert lst == torch.nonzero(live[i]).flatten().tolist(), f"slice {s_} query block {i}"
+        for j in range(nkb):
+            n = int(words[off["kcnt"] + s_ * nkb + j])
+            lst = words[off["klist"] + (s_ * nkb + j) * nqb:][:n].tolist()
+            assert lst == torch.nonzero(live[:, j]).flatten().tolist(), f"slice {s_} key block {j}"
+        for i2 in range(nq2):
+            n = int(words[off["q2cnt"] + s_ * nq2 + i2])
+            lst = words[off["q2list"] + (s_ * nq2 + i2) * nkb:][:n].tolist()
+            both = live[2 * i2] | live[min(2 * i2 + 1, nqb - 1)]
+            assert lst == torch.nonzero(both).flatten().tolist(), f"slice {s_} 256-query block {i2}"
+    if mask != "dead-row":
+        assert int(words[off["qcnt"]:off["qcnt"] + Bb * Hb * nqb].sum()) < Bb * Hb * nqb * nkb, "nothing was skipped"
+
+
+def test_masked_bias_tiles_follow_the_tensor():
+    """A bias modified in place, or another tensor of the same shape, is not served stale lists."""
+    g = gen(5)
+    B, H, T_, d = 1, 2, 1024, 64
+    q, k, v, do = (randn(g, B, T_, H, d, dtype=torch.float16) for _ in range(4))
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    bias = torch.zeros(B, H, T_, T_)
+    bias[..., 512:] = -1e4
+    bd = bias.half().cuda()
+    m = ops.FlashAttention()
+    for _ in range(3):
+        m(qd, kd, vd, bd)
+    assert torch.is_tensor(m.cache._tiles[2])
+    bd[..., 512:] = 0.0                                   # unmask in place: the version counter moves
+    o = m(qd, kd, vd, bd)
+    eo, _ = O.attn_fwd(q.float(), k.float(), v.float(), bd.float().cpu())
+    lo = O.attn_lowp(q, k, v, do, bd.cpu())[0]
+    assert_attn(o.detach().cpu(), eo, lo, "after in-place unmasking")
+    other = torch.zeros_like(bd)
+    o2 = m(qd, kd, vd, other)
+    eo2, _ = O.attn_fwd(q.float(), k.float(), v.float(), None)
+    assert_attn(o2.detach().cpu(), eo2, O.attn_lowp(q, k, v, do, None)[0], "another bias tensor")
