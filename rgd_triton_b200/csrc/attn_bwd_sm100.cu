@@ -559,6 +559,7 @@ struct alignas(1024) DkdvSubSmem {
     uint64_t g1_full[2], g2_full[2], p_ready[2], ds_ready[2];   // per sub-block parity
     uint64_t g1_free[2], g2_free[2];                            // accumulation GEMM has read P / dS
     uint64_t bb_full[2], bb_empty[2];                           // bias sub-tile of parity b
+    int qblk[2];                                                // query block index of the staged block (tile lists)
     uint32_t tmem_base;
 };
 
@@ -586,18 +587,15 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
     const int r0 = blk * BT;                               // first key of this CTA
     const int i_begin = p.causal ? r0 / BT : 0;
     const int i_end = (p.Tq + BT - 1) / BT;
-    int nit = max(i_end - i_begin, 0);
-    // query blocks to visit when the bias came with tile lists: the others hold only masked values
-    const uint16_t *tl = nullptr;
+    // With tile lists (matrix bias only) the CTA visits the listed query blocks: the count bounds
+    // every role's loop, the TMA producer alone reads the list and posts each stage's block index
+    // in shared memory (sm.qblk) before the stage's barrier, where the compute threads pick it up.
+    int tl_idx = -1;
     if constexpr (BIASM == 1) {
-        if (p.tlk_cnt != nullptr) {
-            const int64_t slice = (int64_t)(p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h);
-            const int64_t idx = slice * gridDim.x + blk;
-            tl = p.tlk_list + idx * p.tl_nqb;
-            nit = p.tlk_cnt[idx];
-        }
+        if (p.tlk_cnt != nullptr)
+            tl_idx = (int)(((p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h)) * (int)gridDim.x + blk);
     }
-    auto qblk = [&](int it) -> int { return tl != nullptr ? (int)tl[it] : i_begin + it; };
+    const int nit = tl_idx >= 0 ? (int)p.tlk_cnt[tl_idx] : max(i_end - i_begin, 0);
     const int nsub = 2 * nit;
     int *status = p.status;
 
@@ -646,8 +644,13 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 const uint32_t ph = (uint32_t)(it >> 1) & 1u;
                 ok = mbar_wait(&sm.y_empty[s], ph ^ 1u, status, 71);
                 if (!ok) break;
+                int qb = i_begin + it;
+                if constexpr (BIASM == 1) {
+                    if (tl_idx >= 0) qb = p.tlk_list[(int64_t)tl_idx * p.tl_nqb + it];
+                    sm.qblk[s] = qb;        // ordered before the arrive below (release), read after the wait on y_full
+                }
                 mbar_expect_tx(&sm.y_full[s], 2 * TILE_BYTES + (STAGE_STATS ? 2 * BT * 4 : 0));
-                const int row = qblk(it) * BT;
+                const int row = qb * BT;
                 if constexpr (STAGE_STATS) {
                     bulk_load_1d(sm.lse_s[s], p.lse2 + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
                     bulk_load_1d(sm.dsc_s[s], p.delta_s + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
@@ -782,10 +785,13 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
         bool ok = true;
         for (int it = 0; it < nit; ++it) {
             const uint32_t par = (uint32_t)it & 1u;
-            const int blk0 = qblk(it) * BT;
+            const int s = it & 1;
+            // the block's tiles, its row statistics and (with tile lists) its index have landed
+            ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
+            if (!ok) break;
+            const int blk0 = (BIASM == 1 ? sm.qblk[s] : i_begin + it) * BT;
             const int c0 = blk0 + sb * 64;                 // first query of the sub-block
             const bool slow = cta_key_tail || (p.causal && blk0 == r0);
-            const int s = it & 1;
             // row statistics of this sub-block's 64 queries: staged in shared memory, else from global
             const float *lse_f = STAGE_STATS ? &sm.lse_s[s][sb * 64] : p.lse2 + (int64_t)bh * p.Tq128 + c0;
             const float *dsc_f = STAGE_STATS ? &sm.dsc_s[s][sb * 64] : p.delta_s + (int64_t)bh * p.Tq128 + c0;
@@ -793,9 +799,6 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
             const float4 *dsc4 = reinterpret_cast<const float4 *>(dsc_f);
             float pv[64];
 
-            // row statistics of this block have landed
-            ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
-            if (!ok) break;
             // x0[i] = bias * log2(e) - lse * log2(e) of query i (only -lse without a bias), formed
             // before the scores are waited for
             float x0[BIAS ? 64 : 1];
@@ -1367,7 +1370,6 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
         tl = p.tlq_list + idx * p.tl_nkb;
         nit = p.tlq_cnt[idx];
     }
-    auto kblk = [&](int it) -> int { return tl != nullptr ? (int)tl[it] : it; };
     int *status = p.status;
 
     if (threadIdx.x == 0) {
@@ -1409,7 +1411,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
             int ks = 0;
             uint32_t kph = 0;                              // phase of the K ring slot's previous use
             for (int it = 0; it < nit; ++it) {
-                const int row = kblk(it) * BT;
+                const int row = (tl != nullptr ? (int)tl[it] : it) * BT;
                 ok = mbar_wait(&sm.k_empty[ks], kph ^ 1u, status, 41);
                 if (!ok) break;
                 mbar_expect_tx(&sm.k_full[ks], TILE_BYTES);
@@ -1563,7 +1565,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
             tmem_wait_ld();
             tc_fence_before_sync();
             mbar_arrive(&sm.s_read);
-            const int blk0 = kblk(j) * BT;
+            const int blk0 = (tl != nullptr ? (int)tl[j] : j) * BT;
             // blocks that need per-element masking: the diagonal blocks under the causal mask
             // and the block touching the end of the keys
             const bool slow = (p.causal && blk0 + BT > r0) || blk0 + BT > p.Tk;
@@ -1615,7 +1617,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
                 tmem_st32(lane_base + dcol, pk);
                 if constexpr (DBIAS) {
                     // bias gradient: this thread's row, the 64 keys of its half of block it
-                    const int k0 = kblk(it) * BT + half * 64;
+                    const int k0 = (tl != nullptr ? (int)tl[it] : it) * BT + half * 64;
                     if (row < p.Tq && k0 < p.Tk) {
                         T *dst = reinterpret_cast<T *>(p.dbias) + (int64_t)b * p.db_sb + (int64_t)h * p.db_sh +
                                  (int64_t)row * p.db_sq + k0;

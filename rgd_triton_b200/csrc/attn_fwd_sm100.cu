@@ -233,7 +233,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
             for (int t = 0; t < 2; ++t) nb[t] = nb[t] > 0 ? cnt : 0;
         }
     }
-    auto kblk = [&](int j) -> int { return tl != nullptr ? (int)tl[j] : j; };
     const int nblk = max(nb[0], nb[1]);
     int *status = p.status;
 
@@ -284,7 +283,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 if (!ok) break;
                 mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
                 for (int hh = 0; hh < HALVES; ++hh)
-                    tma_load_4d(sm.k[s] + hh * PANEL, &p.mk, &sm.k_full[s], hh * 64, kblk(j) * TN, h, b);
+                    tma_load_4d(sm.k[s] + hh * PANEL, &p.mk, &sm.k_full[s], hh * 64, (tl != nullptr ? (int)tl[j] : j) * TN, h, b);
                 if constexpr (BIAS == 2) {
                     const int bs = j % BS;
                     const uint32_t bph = (uint32_t)(j / BS) & 1u;
@@ -295,7 +294,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                         mbar_expect_tx(&sm.b_full[t][bs], BIAS_BYTES);
                         for (int pn = 0; pn < 2; ++pn)
                             tma_load_4d(sm.bias[t * BS + bs] + pn * (TM * 128), &p.mbias, &sm.b_full[t][bs],
-                                        kblk(j) * TN + pn * 64, m0 + t * TM, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                                        (tl != nullptr ? (int)tl[j] : j) * TN + pn * 64, m0 + t * TM, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
                     }
                     if (!ok) break;
                 }
@@ -304,7 +303,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 if (!ok) break;
                 mbar_expect_tx(&sm.v_full[vs], TILE_BYTES);
                 for (int hh = 0; hh < HALVES; ++hh)
-                    tma_load_4d(sm.v[vs] + hh * PANEL, &p.mv, &sm.v_full[vs], hh * 64, kblk(j) * TN, h, b);
+                    tma_load_4d(sm.v[vs] + hh * PANEL, &p.mv, &sm.v_full[vs], hh * 64, (tl != nullptr ? (int)tl[j] : j) * TN, h, b);
             }
             if (!ok) {
                 // Give copies already in flight time to land before the CTA goes away.
@@ -430,7 +429,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 if (!ok) break;
                 btile = sm.bias[t * BSD + (j % BSD)];
             }
-            const int n0 = kblk(j) * TN;
+            const int n0 = (tl != nullptr ? (int)tl[j] : j) * TN;
             const bool need_mask = (n0 + TN > p.Tk) || (p.causal && n0 + TN > m0 + t * TM);
 
             const uint32_t s_addr = lane_base + s_col;

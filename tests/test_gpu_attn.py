@@ -538,6 +538,14 @@ def test_masked_bias_tiles_are_skipped_with_identical_results(d, form, mask):
         dense = run(ops.FlashAttention())
     finally:
         F_.set_skip_masked_tiles(prev)
+    # the dense evaluation itself against the oracle (so that "identical" cannot mean "equally wrong")
+    fb = bias.float()
+    eo, _ = O.attn_fwd(q.float(), k.float(), v.float(), fb)
+    exact = [eo, *O.attn_bwd(q.float(), k.float(), v.float(), do.float(), fb)]
+    lowp = O.attn_lowp(q, k, v, do, bias)
+    for got_, e_, l_, name in zip(dense, exact, lowp, ("o", "dq", "dk", "dv")):
+        assert_attn(got_.cpu(), e_, l_, f"dense {name} ({mask}, {form}, d={d})", factor=2.0,
+                    floor=1e-4 if name == "o" else GRAD_FLOOR)
     m = ops.FlashAttention()
     for call in range(3):
         got = run(m)
