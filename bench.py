@@ -536,7 +536,9 @@ def config5_block(dev, steps, hbm_peak, tf_burst):
                       "fwd_tflops": ff / (a_fwd * 1e-3) / 1e12, "bwd_tflops": fb / (a_bwd * 1e-3) / 1e12,
                       "fwd_bias_gbs": nbias / (a_fwd * 1e-3) / 1e9, "bias_bytes_per_pass": nbias,
                       "flop_fwd_bwd": ff + fb, "masked_key_fraction": masked,
-                      "key_blocks_skipped_fraction": skipped, "without_skip_fwd_ms": d_fwd, "without_skip_bwd_ms": d_bwd,
+                      "key_blocks_skipped_fraction": skipped,
+                      "tile_lists_used": bool(torch.is_tensor(getattr(fa.cache, "_tiles", [None, None, None])[2])),
+                      "without_skip_fwd_ms": d_fwd, "without_skip_bwd_ms": d_bwd,
                       "roofline_ms": sum(max(f / (tf_burst * 1e12), nbias / (hbm_peak * 1e9)) for f in (ff, fb)) * 1e3},
         "fused_form": fused,
     }
@@ -575,6 +577,42 @@ def config4(dev, attn, steps, broadcast, hbm_peak, tf_burst):
             "fwd_bias_gbs": nbias / (fwd * 1e-3) / 1e9, "bwd_bias_gbs": nbias / (bwd * 1e-3) / 1e9,
             "bias_bytes_per_pass": nbias, "masked_block_fraction": float(blk.float().mean()),
             "roofline_ms": sum(max(f / (tf_burst * 1e12), nbias / (hbm_peak * 1e9)) for f in (ff, fb)) * 1e3}
+
+
+def block_sparse_case(dev, steps):
+    """The block-sparse skip where it applies: configuration 4's shapes (fp16, [2,4096,24,64]) with a
+    bias whose 128 x 128 tiles are masked (-1e4) with probability 0.5, diagonal tiles kept.  The
+    module scans the bias on its second use and then visits only unmasked tiles; timed against the
+    same module with the skip turned off."""
+    from rgd_triton_b200 import functional as F_, ops
+    g = torch.Generator().manual_seed(44)
+    B, T_, H, D = 2, 4096, 24, 64
+    q, k, v, do = (torch.randn(B, T_, H, D, generator=g).to(torch.float16).to(dev) for _ in range(4))
+    gd = torch.Generator(device=dev).manual_seed(44)
+    bias = torch.randn(B, H, T_, T_, generator=gd, device=dev, dtype=torch.float32).to(torch.float16)
+    nb = T_ // 128
+    blk = (torch.rand(B, H, nb, nb, generator=gd, device=dev) < 0.5) & ~torch.eye(nb, dtype=torch.bool, device=dev)
+    bias.view(B, H, nb, 128, nb, 128).masked_fill_(blk[:, :, :, None, :, None], -1e4)
+    out = {"workload": "fp16 q/k/v [2,4096,24,64], bias [2,24,4096,4096] with 128x128 tiles masked Bernoulli(0.5)",
+           "masked_tile_fraction": float(blk.float().mean())}
+    n = max(3, min(steps, 10))
+    for name, enable in (("dense", False), ("skip", True)):
+        prev = F_.set_skip_masked_tiles(enable)
+        try:
+            fa = ops.FlashAttention()
+            qi, ki, vi = (t.detach().requires_grad_(True) for t in (q, k, v))
+            for _ in range(3):
+                o = fa(qi, ki, vi, bias)
+                torch.autograd.grad(o, (qi, ki, vi), do)
+            o = fa(qi, ki, vi, bias)
+            out[name + "_fwd_ms"] = timed_median(lambda: fa(qi, ki, vi, bias), n)
+            out[name + "_bwd_ms"] = timed_median(lambda: torch.autograd.grad(o, (qi, ki, vi), do, retain_graph=True), n)
+            if enable:
+                out["tile_lists_used"] = bool(torch.is_tensor(getattr(fa.cache, "_tiles", [None, None, None])[2]))
+        finally:
+            F_.set_skip_masked_tiles(prev)
+    out["speedup_fwd_bwd"] = (out["dense_fwd_ms"] + out["dense_bwd_ms"]) / (out["skip_fwd_ms"] + out["skip_bwd_ms"])
+    return out
 
 
 def reference_triton(dev):
@@ -1063,6 +1101,10 @@ def main():
                 config4(dev, attn, args.steps, True, hbm_peak, tf_burst)]
         torch.cuda.empty_cache()
         waits_ok("attention, configuration 4")
+        if rank == 0:
+            cfg4.append(block_sparse_case(dev, args.steps))
+            torch.cuda.empty_cache()
+            waits_ok("attention, block-sparse bias")
     cfg5 = None
     if not args.no_config5:
         cfg5 = config5_block(dev, args.steps, hbm_peak, tf_burst)

@@ -563,10 +563,13 @@ struct alignas(1024) DkdvSubSmem {
     uint32_t tmem_base;
 };
 
-// BIASM: 0 no bias, 1 matrix bias staged by TMA, 2 vector bias (one value per key = per thread).
+// BIASM: 0 no bias, 1 matrix bias staged by TMA, 2 vector bias (one value per key = per thread),
+// 3 matrix bias with tile lists (an instantiation of its own: the list plumbing costs the dense
+// form 5-11 % when it shares the code).
 template <int D, bool BF16, int BIASM>
 __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const __grid_constant__ BwdTmaParams p) {
-    constexpr bool BIAS = BIASM == 1;
+    constexpr bool BIAS = BIASM == 1 || BIASM == 3;
+    constexpr bool LISTS = BIASM == 3;
     using Smem = DkdvSubSmem<D, BIAS>;
     constexpr bool STAGE_STATS = Smem::STAGE_STATS;
     constexpr uint32_t BIAS_BYTES = 64 * BT * 2;
@@ -591,11 +594,9 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
     // every role's loop, the TMA producer alone reads the list and posts each stage's block index
     // in shared memory (sm.qblk) before the stage's barrier, where the compute threads pick it up.
     int tl_idx = -1;
-    if constexpr (BIASM == 1) {
-        if (p.tlk_cnt != nullptr)
-            tl_idx = (int)(((p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h)) * (int)gridDim.x + blk);
-    }
-    const int nit = tl_idx >= 0 ? (int)p.tlk_cnt[tl_idx] : max(i_end - i_begin, 0);
+    if constexpr (LISTS)
+        tl_idx = (int)(((p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h)) * (int)gridDim.x + blk);
+    const int nit = LISTS ? (int)p.tlk_cnt[LISTS ? tl_idx : 0] : max(i_end - i_begin, 0);
     const int nsub = 2 * nit;
     int *status = p.status;
 
@@ -639,16 +640,20 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
                 tma_load_4d(sm.x2 + hh * PANEL, &p.mv, &sm.x_full, hh * 64, r0, h, b);
             }
             bool ok = true;
+            // the list entry of the next block is fetched while waiting for this block's stage
+            const uint16_t *lst = LISTS ? p.tlk_list + (int64_t)tl_idx * p.tl_nqb : nullptr;
+            int qb_next = LISTS ? (int)lst[0] : 0;
             for (int it = 0; it < nit; ++it) {
                 const int s = it & 1;
                 const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+                int qb = i_begin + it;
+                if constexpr (LISTS) {
+                    qb = qb_next;
+                    if (it + 1 < nit) qb_next = lst[it + 1];
+                }
                 ok = mbar_wait(&sm.y_empty[s], ph ^ 1u, status, 71);
                 if (!ok) break;
-                int qb = i_begin + it;
-                if constexpr (BIASM == 1) {
-                    if (tl_idx >= 0) qb = p.tlk_list[(int64_t)tl_idx * p.tl_nqb + it];
-                    sm.qblk[s] = qb;        // ordered before the arrive below (release), read after the wait on y_full
-                }
+                if constexpr (LISTS) sm.qblk[s] = qb;   // ordered before the arrive below (release), read after the wait on y_full
                 mbar_expect_tx(&sm.y_full[s], 2 * TILE_BYTES + (STAGE_STATS ? 2 * BT * 4 : 0));
                 const int row = qb * BT;
                 if constexpr (STAGE_STATS) {
@@ -786,10 +791,13 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
         for (int it = 0; it < nit; ++it) {
             const uint32_t par = (uint32_t)it & 1u;
             const int s = it & 1;
-            // the block's tiles, its row statistics and (with tile lists) its index have landed
-            ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
-            if (!ok) break;
-            const int blk0 = (BIASM == 1 ? sm.qblk[s] : i_begin + it) * BT;
+            int blk0 = (i_begin + it) * BT;
+            if constexpr (LISTS) {
+                // the block's index is posted with its tiles
+                ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
+                if (!ok) break;
+                blk0 = sm.qblk[s] * BT;
+            }
             const int c0 = blk0 + sb * 64;                 // first query of the sub-block
             const bool slow = cta_key_tail || (p.causal && blk0 == r0);
             // row statistics of this sub-block's 64 queries: staged in shared memory, else from global
@@ -798,6 +806,12 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
             const float4 *lse4 = reinterpret_cast<const float4 *>(lse_f);
             const float4 *dsc4 = reinterpret_cast<const float4 *>(dsc_f);
             float pv[64];
+
+            if constexpr (!LISTS) {
+                // row statistics of this block have landed
+                ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
+                if (!ok) break;
+            }
 
             // x0[i] = bias * log2(e) - lse * log2(e) of query i (only -lse without a bias), formed
             // before the scores are waited for
@@ -1339,7 +1353,7 @@ struct alignas(1024) DqBiasSmem {
     uint32_t tmem_base;
 };
 
-template <int D, bool BF16, bool DBIAS>
+template <int D, bool BF16, bool DBIAS, bool LISTS>
 __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __grid_constant__ BwdTmaParams p,
                                                                        const void *q_base, const void *do_base,
                                                                        int64_t q_sb, int64_t q_sh, int64_t q_sn,
@@ -1362,9 +1376,10 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
     const int r0 = blk * BT;                               // first query of this CTA
     const int i_end = ((p.causal ? min(p.Tk, r0 + BT) : p.Tk) + BT - 1) / BT;
     int nit = max(i_end, 0);
-    // key blocks to visit when the bias came with tile lists: the others hold only masked values
+    // key blocks to visit when the bias came with tile lists (an instantiation of its own): the
+    // others hold only masked values
     const uint16_t *tl = nullptr;
-    if (p.tlq_cnt != nullptr) {
+    if constexpr (LISTS) {
         const int64_t slice = (int64_t)(p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h);
         const int64_t idx = slice * gridDim.x + blk;
         tl = p.tlq_list + idx * p.tl_nkb;
@@ -1411,7 +1426,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
             int ks = 0;
             uint32_t kph = 0;                              // phase of the K ring slot's previous use
             for (int it = 0; it < nit; ++it) {
-                const int row = (tl != nullptr ? (int)tl[it] : it) * BT;
+                const int row = (LISTS ? (int)tl[it] : it) * BT;
                 ok = mbar_wait(&sm.k_empty[ks], kph ^ 1u, status, 41);
                 if (!ok) break;
                 mbar_expect_tx(&sm.k_full[ks], TILE_BYTES);
@@ -1565,7 +1580,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
             tmem_wait_ld();
             tc_fence_before_sync();
             mbar_arrive(&sm.s_read);
-            const int blk0 = (tl != nullptr ? (int)tl[j] : j) * BT;
+            const int blk0 = (LISTS ? (int)tl[j] : j) * BT;
             // blocks that need per-element masking: the diagonal blocks under the causal mask
             // and the block touching the end of the keys
             const bool slow = (p.causal && blk0 + BT > r0) || blk0 + BT > p.Tk;
@@ -1617,7 +1632,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
                 tmem_st32(lane_base + dcol, pk);
                 if constexpr (DBIAS) {
                     // bias gradient: this thread's row, the 64 keys of its half of block it
-                    const int k0 = (tl != nullptr ? (int)tl[it] : it) * BT + half * 64;
+                    const int k0 = it * BT + half * 64;
                     if (row < p.Tq && k0 < p.Tk) {
                         T *dst = reinterpret_cast<T *>(p.dbias) + (int64_t)b * p.db_sb + (int64_t)h * p.db_sh +
                                  (int64_t)row * p.db_sq + k0;
@@ -1751,7 +1766,7 @@ static int launch_bwd_tmem(const BwdTmaParams &bp, int nblocks, int BH, cudaStre
 
 template <int D, bool BF16, int BIASM>
 static int launch_dkdv_sub(const BwdTmaParams &bp, int nblocks, int BH, cudaStream_t st) {
-    const size_t smem = sizeof(DkdvSubSmem<D, BIASM == 1>) + 1024;
+    const size_t smem = sizeof(DkdvSubSmem<D, BIASM == 1 || BIASM == 3>) + 1024;
     if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_bwd_dkdv_sub<D, BF16, BIASM>), smem)) return e;
     dim3 grid(nblocks, BH);
     attn_bwd_dkdv_sub<D, BF16, BIASM><<<grid, DKDV_SUB_THREADS, smem, st>>>(bp);
@@ -1766,8 +1781,12 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     bp.out2 = p.dk; bp.o2_sb = p.dk_sb; bp.o2_sh = p.dk_sh; bp.o2_sn = p.dk_sn;
     if (bp.bias_kind == RGD_BIAS_NONE) {
         if (int e = launch_dkdv_sub<D, BF16, 0>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
-    } else if (bp.bias_vec == 2) {       // matrix bias staged by TMA
-        if (int e = launch_dkdv_sub<D, BF16, 1>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
+    } else if (bp.bias_vec == 2) {       // matrix bias staged by TMA, with or without tile lists
+        if (bp.tlk_cnt != nullptr) {
+            if (int e = launch_dkdv_sub<D, BF16, 3>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
+        } else if (int e = launch_dkdv_sub<D, BF16, 1>(bp, (p.Tk + BT - 1) / BT, BH, st)) {
+            return e;
+        }
     } else if (bp.bias_kind == RGD_BIAS_VECTOR) {
         if (int e = launch_dkdv_sub<D, BF16, 2>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
     } else if (int e = launch_bwd_tmem<D, BF16, true>(bp, (p.Tk + BT - 1) / BT, BH, st)) {
@@ -1789,17 +1808,22 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     }
     if (bp.bias_vec == 2) {              // matrix bias staged by TMA
         const size_t smem = sizeof(DqBiasSmem<D>) + 1024;
-        const bool db = bp.dbias != nullptr;
-        const void *kernel = db ? reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, true>)
-                                : reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, false>);
+        // three instantiations: plain, writing the bias gradient, following tile lists (never both)
+        const int mode = bp.dbias != nullptr ? 1 : (bp.tlq_cnt != nullptr ? 2 : 0);
+        const void *kernel = mode == 1   ? reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, true, false>)
+                             : mode == 2 ? reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, false, true>)
+                                         : reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, false, false>);
         if (int e = ensure_dyn_smem(kernel, smem)) return e;
         dim3 grid((p.Tq + BT - 1) / BT, BH);
-        if (db)
-            attn_bwd_dq_bias<D, BF16, true><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
-                                                                                   p.do_sb, p.do_sh, p.do_sn);
+        if (mode == 1)
+            attn_bwd_dq_bias<D, BF16, true, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
+                                                                                          p.do_sb, p.do_sh, p.do_sn);
+        else if (mode == 2)
+            attn_bwd_dq_bias<D, BF16, false, true><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
+                                                                                          p.do_sb, p.do_sh, p.do_sn);
         else
-            attn_bwd_dq_bias<D, BF16, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
-                                                                                    p.do_sb, p.do_sh, p.do_sn);
+            attn_bwd_dq_bias<D, BF16, false, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh,
+                                                                                           p.q_sn, p.do_sb, p.do_sh, p.do_sn);
         count_launch();
         return check_launch();
     }

@@ -191,7 +191,9 @@ __device__ __forceinline__ void exp32(const uint32_t (&r)[32], float scale_log2,
 
 // BIAS: 0 none, 1 read straight from global memory by the softmax threads (vector
 // bias, fp32 bias, unaligned views), 2 matrix bias staged tile by tile through TMA.
-template <int D, bool BF16, int BIAS>
+// LISTS: a matrix bias came with tile lists (an instantiation of its own: the dense form pays for
+// the plumbing otherwise).
+template <int D, bool BF16, int BIAS, bool LISTS>
 __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_constant__ FwdTmaParams p) {
     constexpr int NT = 2;
     constexpr int VS = (BIAS == 2 && D == 128) ? 1 : 2;          // stages of V
@@ -223,15 +225,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
     }
     // Key blocks to visit when the bias came with tile lists (never together with a causal mask)
     const uint16_t *tl = nullptr;
-    if constexpr (BIAS == 2) {
-        if (p.tl_cnt != nullptr) {
-            const int64_t slice = (int64_t)(p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h);
-            const int64_t idx = slice * gridDim.x + mblk;
-            tl = p.tl_list + idx * p.tl_nkb;
-            const int cnt = p.tl_cnt[idx];
+    if constexpr (LISTS) {
+        const int64_t slice = (int64_t)(p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h);
+        const int64_t idx = slice * gridDim.x + mblk;
+        tl = p.tl_list + idx * p.tl_nkb;
+        const int cnt = p.tl_cnt[idx];
 #pragma unroll
-            for (int t = 0; t < 2; ++t) nb[t] = nb[t] > 0 ? cnt : 0;
-        }
+        for (int t = 0; t < 2; ++t) nb[t] = nb[t] > 0 ? cnt : 0;
     }
     const int nblk = max(nb[0], nb[1]);
     int *status = p.status;
@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 if (!ok) break;
                 mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
                 for (int hh = 0; hh < HALVES; ++hh)
-                    tma_load_4d(sm.k[s] + hh * PANEL, &p.mk, &sm.k_full[s], hh * 64, (tl != nullptr ? (int)tl[j] : j) * TN, h, b);
+                    tma_load_4d(sm.k[s] + hh * PANEL, &p.mk, &sm.k_full[s], hh * 64, (LISTS ? (int)tl[j] : j) * TN, h, b);
                 if constexpr (BIAS == 2) {
                     const int bs = j % BS;
                     const uint32_t bph = (uint32_t)(j / BS) & 1u;
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                         mbar_expect_tx(&sm.b_full[t][bs], BIAS_BYTES);
                         for (int pn = 0; pn < 2; ++pn)
                             tma_load_4d(sm.bias[t * BS + bs] + pn * (TM * 128), &p.mbias, &sm.b_full[t][bs],
-                                        (tl != nullptr ? (int)tl[j] : j) * TN + pn * 64, m0 + t * TM, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                                        (LISTS ? (int)tl[j] : j) * TN + pn * 64, m0 + t * TM, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
                     }
                     if (!ok) break;
                 }
@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 if (!ok) break;
                 mbar_expect_tx(&sm.v_full[vs], TILE_BYTES);
                 for (int hh = 0; hh < HALVES; ++hh)
-                    tma_load_4d(sm.v[vs] + hh * PANEL, &p.mv, &sm.v_full[vs], hh * 64, (tl != nullptr ? (int)tl[j] : j) * TN, h, b);
+                    tma_load_4d(sm.v[vs] + hh * PANEL, &p.mv, &sm.v_full[vs], hh * 64, (LISTS ? (int)tl[j] : j) * TN, h, b);
             }
             if (!ok) {
                 // Give copies already in flight time to land before the CTA goes away.
@@ -429,7 +429,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 if (!ok) break;
                 btile = sm.bias[t * BSD + (j % BSD)];
             }
-            const int n0 = (tl != nullptr ? (int)tl[j] : j) * TN;
+            const int n0 = (LISTS ? (int)tl[j] : j) * TN;
             const bool need_mask = (n0 + TN > p.Tk) || (p.causal && n0 + TN > m0 + t * TM);
 
             const uint32_t s_addr = lane_base + s_col;
@@ -794,21 +794,22 @@ bool tmem_fwd_eligible(const AttnParams &p) {
            tma_view_ok(p.v, p.B, p.H, p.Tk, p.v_sb, p.v_sh, p.v_sn);
 }
 
-template <int D, bool BF16, int BIAS>
+template <int D, bool BF16, int BIAS, bool LISTS = false>
 static int launch_fwd_one(const FwdTmaParams &fp, int Tq, int BH, cudaStream_t st) {
     constexpr int NT = 2;
     constexpr int VS = (BIAS == 2 && D == 128) ? 1 : 2;
     constexpr int BS = BIAS == 2 ? (D == 128 ? 1 : 2) : 0;
     const size_t smem = sizeof(FwdTmaSmem<D, NT, VS, BS, BIAS == 1>) + 1024;
-    if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_fwd_tmem<D, BF16, BIAS>), smem)) return e;
+    if (int e = ensure_dyn_smem(reinterpret_cast<const void *>(attn_fwd_tmem<D, BF16, BIAS, LISTS>), smem)) return e;
     dim3 grid((Tq + NT * TM - 1) / (NT * TM), BH);
-    attn_fwd_tmem<D, BF16, BIAS><<<grid, FWD_THREADS, smem, st>>>(fp);
+    attn_fwd_tmem<D, BF16, BIAS, LISTS><<<grid, FWD_THREADS, smem, st>>>(fp);
     count_launch();
     return check_launch();
 }
 
 template <int D, bool BF16>
 static int launch_fwd_tmem(const FwdTmaParams &fp, int bias_mode, int Tq, int BH, cudaStream_t st) {
+    if (bias_mode == 2 && fp.tl_cnt != nullptr) return launch_fwd_one<D, BF16, 2, true>(fp, Tq, BH, st);
     if (bias_mode == 2) return launch_fwd_one<D, BF16, 2>(fp, Tq, BH, st);
     if (bias_mode == 1) return launch_fwd_one<D, BF16, 1>(fp, Tq, BH, st);
     return launch_fwd_one<D, BF16, 0>(fp, Tq, BH, st);
