@@ -76,3 +76,38 @@ def test_argument_errors_need_no_gpu(lib):
         _lib.check(_lib.RGD_E_SIZE, "x")
     with pytest.raises(RuntimeError):
         _lib.check(_lib.RGD_E_BIAS_SHAPE, "x")
+
+
+def test_bias_gradient_and_tile_list_arguments_need_no_gpu(lib):
+    """rgd_attn_bwd_dbias and the tile-list entry points validate before any CUDA call."""
+    from rgd_triton_b200 import _lib
+    L = _lib.load()
+    h = _lib.Heads(None, 0, 0, 0)
+    hp = ctypes.byref(h)
+    mat = _lib.Bias(None, 0, 0, 8, _lib.RGD_BIAS_MATRIX, _lib.RGD_F16, None)
+    vec = _lib.Bias(None, 0, 0, 0, _lib.RGD_BIAS_VECTOR, _lib.RGD_F16, None)
+    # the gradient's kind must be the bias's kind
+    rc = L.rgd_attn_bwd_dbias(hp, hp, hp, ctypes.byref(mat), hp, None, hp, hp, hp, hp, ctypes.byref(vec),
+                              0, 1, 8, 8, 64, 1.0, 0, _lib.RGD_F16, None, 0, None, None)
+    assert rc == _lib.RGD_E_BIAS_SHAPE
+    # a vector-bias gradient is dense fp32 [B, H, Tk]
+    rc = L.rgd_attn_bwd_dbias(hp, hp, hp, ctypes.byref(vec), hp, None, hp, hp, hp, hp, ctypes.byref(vec),
+                              0, 1, 8, 8, 64, 1.0, 0, _lib.RGD_F16, None, 0, None, None)
+    assert rc == _lib.RGD_E_DTYPE
+    # tile lists: size formula, and refusals
+    def layout_bytes(B, H, tq, tk):
+        nqb, nq2, nkb = (tq + 127) // 128, (tq + 255) // 256, (tk + 127) // 128
+        words = B * H * (nqb + nqb * nkb + nq2 + nq2 * nkb + nkb + nkb * nqb)
+        words = (words + 7) // 8 * 8
+        return words * 2 + (B * H * nqb * nkb + 15) // 16 * 16
+    for dims in ((2, 3, 1100, 1160), (1, 1, 1, 1), (4, 16, 4096, 4096), (2, 24, 4608, 4608)):
+        assert L.rgd_attn_bias_tiles_bytes(*dims) == layout_bytes(*dims)
+    assert L.rgd_attn_bias_tiles_bytes(0, 3, 5, 5) == 0
+    buf = ctypes.create_string_buffer(64)
+    assert L.rgd_attn_bias_tiles_build(ctypes.byref(vec), 1, 1, 8, 8, -9984.0, buf, 64, None) == _lib.RGD_E_BIAS_SHAPE
+    assert L.rgd_attn_bias_tiles_build(ctypes.byref(mat), 1, 1, 8, 8, 1.0, buf, 64, None) == _lib.RGD_E_INVALID
+    f32 = _lib.Bias(None, 0, 0, 8, _lib.RGD_BIAS_MATRIX, _lib.RGD_F32, None)
+    assert L.rgd_attn_bias_tiles_build(ctypes.byref(f32), 1, 1, 8, 8, -9984.0, buf, 64, None) == _lib.RGD_E_DTYPE
+    big = _lib.Bias(None, 0, 0, 4096, _lib.RGD_BIAS_MATRIX, _lib.RGD_F16, None)
+    assert L.rgd_attn_bias_tiles_build(ctypes.byref(big), 1, 1, 4096, 4096, -9984.0, buf, 64, None) == _lib.RGD_E_WORKSPACE
+    assert L.rgd_attn_bias_tiles_build(ctypes.byref(mat), 1, 1, 4096, 4096, -9984.0, buf, 64, None) == _lib.RGD_E_STRIDE
