@@ -501,7 +501,7 @@ def _tile_layout(slices, tq, tk):
 @pytest.mark.parametrize("form", ["full", "batch-shared", "head-shared"])
 @pytest.mark.parametrize("mask", ["blocks", "key-padding", "dead-row"])
 def test_masked_bias_tiles_are_skipped_with_identical_results(d, form, mask):
-    """Block-sparse skip (SURVEY 8(f)2 of the reference has only the dense form,
+    """Block-sparse skip (the reference has only the dense form,
     flash_attn_triton_cached.py:151-175): a bias reused through a module's cache gets tile lists
     from its second forward on, the kernels visit only listed tiles, and o, dq, dk, dv are
     bit-identical to the dense evaluation.  The lists themselves are checked against the mask."""
