@@ -143,7 +143,16 @@ def require_device(t: torch.Tensor) -> None:
     _checked_devices.add(idx)
 
 
+# The raw accessors skip the Stream / device-index objects torch.cuda.current_stream() builds (several
+# microseconds per call, as much as a small operator's whole launch); the public path is the fallback.
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_RAW_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def stream_ptr() -> int:
+    """The current CUDA stream of the current device as an integer handle."""
+    if _RAW_STREAM is not None and _RAW_DEVICE is not None:
+        return _RAW_STREAM(_RAW_DEVICE())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -162,7 +171,7 @@ def device_guard(t: torch.Tensor):
     """Context that makes t's device current for the launch; free of charge
     when it already is (the common case), which matters for the small operators
     whose host path is as long as their kernel."""
-    if t.device.index == torch.cuda.current_device():
+    if t.device.index == (_RAW_DEVICE() if _RAW_DEVICE is not None else torch.cuda.current_device()):
         return _NO_GUARD
     return torch.cuda.device(t.device)
 
