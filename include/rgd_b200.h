@@ -276,9 +276,25 @@ int rgd_attn_fwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v,
 /* Scratch bytes for rgd_attn_bwd: one fp32 row of delta = rowsum(O * dO) per
  * (batch, head) on the general path; on the tensor-memory path two fp32 rows
  * per (batch, head), lse * log2(e) and delta * scale, each Tq rounded up to
- * 128.  There is no fp32 dQ accumulator on either path. */
+ * 128.  With exactly this much, no fp32 dQ accumulator is used on either path. */
 int64_t rgd_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq,
                                      int64_t Tk, int64_t d, int dtype);
+
+/* Scratch bytes that select the single-pass backward (0 where there is none:
+ * it exists for head_dim 64 on the tensor-memory path, without tile lists and
+ * without a bias gradient): the bytes above, rounded up to 256, plus an fp32 dQ
+ * accumulator of B * H * Tq (rounded up to 128) * d elements, which the entry
+ * point zeroes itself.  Given at least this much 256-byte aligned workspace,
+ * rgd_attn_bwd evaluates S, dP and the exponentials once per tile pair and adds
+ * the dQ partial tiles into the accumulator with vector reductions, the scheme
+ * of the reference's sequence-parallel backward (tl.atomic_add into dq,
+ * flash_attn_triton_cached.py:556-561): dK and dV are bit-reproducible, dQ may
+ * differ in its last bits from run to run (the reference's own test allows
+ * that, tests/test_flash_attn.py:341-388).  Given less, rgd_attn_bwd runs the
+ * two-kernel form, in which dQ is bit-reproducible too. */
+int64_t rgd_attn_bwd_single_pass_workspace_bytes(int64_t B, int64_t H,
+                                                 int64_t Tq, int64_t Tk,
+                                                 int64_t d, int dtype);
 
 /* dQ, dK, dV given dO.  Replaces _flash_attn_backward, including the
  * delta = rowsum(O * dO) pre-pass (flash_attn_triton_cached.py:885-1075).

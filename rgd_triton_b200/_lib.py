@@ -76,6 +76,7 @@ SIGNATURES = {
     "rgd_attn_fwd": (_i32, [_pHeads, _pHeads, _pHeads, _pBias, _pHeads, _vp] + [_i64] * 5
                      + [_f32, _i32, _i32, _vp, _vp]),
     "rgd_attn_bwd_workspace_bytes": (_i64, [_i64] * 5 + [_i32]),
+    "rgd_attn_bwd_single_pass_workspace_bytes": (_i64, [_i64] * 5 + [_i32]),
     "rgd_attn_bwd": (_i32, [_pHeads, _pHeads, _pHeads, _pBias, _pHeads, _vp, _pHeads, _pHeads, _pHeads, _pHeads]
                      + [_i64] * 5 + [_f32, _i32, _i32, _vp, _i64, _vp, _vp]),
     "rgd_attn_bwd_dbias": (_i32, [_pHeads, _pHeads, _pHeads, _pBias, _pHeads, _vp, _pHeads, _pHeads, _pHeads, _pHeads, _pBias]

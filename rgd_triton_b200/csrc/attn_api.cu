@@ -11,7 +11,9 @@ bool tmem_fwd_eligible(const AttnParams &p);
 int tmem_fwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st);
 int tmem_status_fetch();
 bool tmem_bwd_eligible(const AttnParams &p);
-int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st);
+int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, float *dq_acc, cudaStream_t st);
+int64_t single_pass_acc_offset(int64_t B, int64_t H, int64_t Tq);
+int64_t single_pass_acc_bytes(int64_t B, int64_t H, int64_t Tq, int64_t d);
 int bounded_wait_selftest(int64_t limit_ns, cudaStream_t st);
 int64_t tmem_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq);
 int build_bias_tiles(const void *bias, int64_t sb, int64_t sh, int64_t sq, int64_t Bb, int64_t Hb, int64_t Tq, int64_t Tk,
@@ -146,6 +148,15 @@ extern "C" int64_t rgd_attn_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq
     return general > tmem ? general : tmem;
 }
 
+extern "C" int64_t rgd_attn_bwd_single_pass_workspace_bytes(int64_t B, int64_t H, int64_t Tq, int64_t Tk, int64_t d,
+                                                            int dtype) {
+    const int64_t base = rgd_attn_bwd_workspace_bytes(B, H, Tq, Tk, d, dtype);
+    if (base < 0) return base;
+    const int64_t acc = attn::single_pass_acc_bytes(B, H, Tq, d);
+    if (acc == 0) return 0;
+    return attn::single_pass_acc_offset(B, H, Tq) + acc;
+}
+
 extern "C" int rgd_attn_bwd(const rgd_heads *q, const rgd_heads *k, const rgd_heads *v, const rgd_bias *bias,
                             const rgd_heads *o, const float *lse, const rgd_heads *d_o, const rgd_heads *dq,
                             const rgd_heads *dk, const rgd_heads *dv, int64_t B, int64_t H, int64_t Tq, int64_t Tk,
@@ -198,7 +209,12 @@ extern "C" int rgd_attn_bwd_dbias(const rgd_heads *q, const rgd_heads *k, const 
         }
     }
     if (work && attn::tmem_bwd_eligible(p)) {
-        const int rc = attn::tmem_bwd(p, dtype, cache, (cudaStream_t)stream);
+        // a workspace with room for the fp32 dQ accumulator selects the single-pass form
+        float *dq_acc = nullptr;
+        const int64_t single = rgd_attn_bwd_single_pass_workspace_bytes(B, H, Tq, Tk, d, dtype);
+        if (single > 0 && workspace_bytes >= single && is_aligned(workspace, 256))
+            dq_acc = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + attn::single_pass_acc_offset(B, H, Tq));
+        const int rc = attn::tmem_bwd(p, dtype, cache, dq_acc, (cudaStream_t)stream);
         if (rc != attn::TMEM_NOT_TAKEN) return rc;
     }
     return attn::general_bwd(p, dtype, (cudaStream_t)stream);

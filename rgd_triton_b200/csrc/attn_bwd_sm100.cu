@@ -37,6 +37,7 @@ int encode_bias_map(rgd_cache *cache, CUtensorMap *out, const AttnParams &p, boo
 
 constexpr int BWD_THREADS = 320;
 constexpr int DKDV_SUB_THREADS = 384;   // 8 compute warps, TMA producer, three MMA issuers
+constexpr int SINGLE64_THREADS = 512;   // the same plus four warps that read dQ partial tiles back
 constexpr int BT = 128;   // tile edge (queries and keys)
 
 struct BwdTmaParams {
@@ -63,6 +64,7 @@ struct BwdTmaParams {
     // slice the query blocks to visit (dK/dV kernel), per query block the key blocks (dQ kernel)
     const uint16_t *tlk_cnt, *tlk_list, *tlq_cnt, *tlq_list;
     int tl_nqb, tl_nkb;
+    float *dq_acc;                      // single-pass form (head_dim 64): fp32 dQ accumulator [B, H, 16, Tq128, 4], else null
 };
 
 // BSTAGES: stages of TMA-staged bias tiles (query rows x key columns, 16-bit, two
@@ -969,6 +971,504 @@ __global__ void __launch_bounds__(DKDV_SUB_THREADS, 1) attn_bwd_dkdv_sub(const _
 }
 
 // ---------------------------------------------------------------------------
+// Single-pass backward for head_dim 64: the dK/dV kernel above (same roles, tiles, tensor-memory
+// map and arithmetic: dK and dV are bit-identical to it) which ALSO forms the dQ partial tile of
+// every 128-query block, dQp = dS K, as a fifth GEMM from the dS^T it already holds, and adds it
+// to an fp32 accumulator in global memory with 16-byte vector reductions.  No second kernel
+// re-reads K, V (and the bias) or recomputes S, dP and the exponentials; a small kernel rounds
+// the accumulator into dQ afterwards.  As in the reference (tl.atomic_add into dq,
+// flash_attn_triton_cached.py:556-561) the order of the sums into dQ is not fixed: dQ may differ in
+// its last bits from run to run, dK and dV do not.  head_dim 64 leaves the 64 tensor-memory
+// columns the partial tile needs (448..511) and the shared memory for dS^T (32 KB); at head_dim
+// 128 the same scheme is bound by the L2's reduction throughput and loses to the two-kernel form.
+// Four extra warps read the partial tiles back, so that reduction stalls do not hold up the
+// compute warps; registers are moved between the roles with setmaxnreg.
+// ---------------------------------------------------------------------------
+template <bool BIAS>
+struct alignas(1024) Single64Smem {
+    static constexpr int D = 64;
+    static constexpr bool STAGE_STATS = true;
+    unsigned char x1[BT * D * 2], x2[BT * D * 2];            // K, V
+    unsigned char y1[2][BT * D * 2], y2[2][BT * D * 2];      // Q, dO, 2 stages
+    unsigned char bias[BIAS ? 2 : 1][BIAS ? 64 * BT * 2 : 1024];
+    unsigned char dsm[2 * BT * 64 * 2];                      // dS^T of the block: per sub-block [key][64 queries]
+    alignas(16) float lse_s[2][BT], dsc_s[2][BT];            // row statistics of the staged query block
+    uint64_t x_full, acc_full;
+    uint64_t y_full[2], y_empty[2];
+    uint64_t g1_full[2], g2_full[2], p_ready[2], ds_ready[2];
+    uint64_t g1_free[2], g2_free[2];
+    uint64_t bb_full[2], bb_empty[2];
+    uint64_t dq_full, dq_read;                               // dQ partial tile complete / read back
+    int qblk[2];
+    uint32_t tmem_base;
+};
+
+// BIASM: 0 no bias, 1 matrix bias staged by TMA, 2 vector bias.
+template <bool BF16, int BIASM>
+__global__ void __launch_bounds__(SINGLE64_THREADS, 1) attn_bwd_single64(const __grid_constant__ BwdTmaParams p) {
+    static_assert(BIASM >= 0 && BIASM <= 2, "no tile lists here");
+    constexpr int D = 64;
+    constexpr bool BIAS = BIASM == 1;
+    constexpr bool LISTS = false;
+    using Smem = Single64Smem<BIAS>;
+    constexpr bool STAGE_STATS = Smem::STAGE_STATS;
+    constexpr uint32_t BIAS_BYTES = 64 * BT * 2;
+    constexpr int HALVES = D / 64;
+    constexpr uint32_t PANEL = 128 * 64 * 2;
+    constexpr uint32_t TILE_BYTES = BT * D * 2;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t G1_COL = 0, G2_COL = 128, ACC1_COL = 256, ACC2_COL = 384, DQ_COL = 448;
+    constexpr uint32_t SUB_ROWS = 64 * 128;          // byte offset of query row 64 inside a panel
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+
+    extern __shared__ unsigned char smem_raw[];
+    Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blk = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / p.H, h = bh - b * p.H;
+    const int r0 = blk * BT;                               // first key of this CTA
+    const int i_begin = p.causal ? r0 / BT : 0;
+    const int i_end = (p.Tq + BT - 1) / BT;
+    // With tile lists (matrix bias only) the CTA visits the listed query blocks: the count bounds
+    // every role's loop, the TMA producer alone reads the list and posts each stage's block index
+    // in shared memory (sm.qblk) before the stage's barrier, where the compute threads pick it up.
+    int tl_idx = -1;
+    if constexpr (LISTS)
+        tl_idx = (int)(((p.bias_b0 ? 0 : b) * (p.bias_h0 ? 1 : p.H) + (p.bias_h0 ? 0 : h)) * (int)gridDim.x + blk);
+    const int nit = LISTS ? (int)p.tlk_cnt[LISTS ? tl_idx : 0] : max(i_end - i_begin, 0);
+    const int nsub = 2 * nit;
+    int *status = p.status;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.x_full, 1);
+        mbar_init(&sm.acc_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.y_full[s], 1);
+            mbar_init(&sm.y_empty[s], 1);
+            mbar_init(&sm.g1_full[s], 1);
+            mbar_init(&sm.g2_full[s], 1);
+            mbar_init(&sm.g1_free[s], 1);
+            mbar_init(&sm.g2_free[s], 1);
+            mbar_init(&sm.p_ready[s], 128);
+            mbar_init(&sm.ds_ready[s], 128);
+            mbar_init(&sm.bb_full[s], 1);
+            mbar_init(&sm.bb_empty[s], 128);
+        }
+        mbar_init(&sm.dq_full, 1);
+        mbar_init(&sm.dq_read, 128);
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&sm.tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tbase = sm.tmem_base;
+
+    // Registers move from the helper and read-back warps to the compute warps (the launch gives every
+    // thread 65536 / 512 = 128): each role's first instruction resizes its warpgroup.
+    if (warp >= 8 && warp < 12) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    if (warp == 8) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0 && nit > 0) {
+            tma_prefetch_desc(&p.mk);
+            tma_prefetch_desc(&p.mv);
+            tma_prefetch_desc(&p.mq);
+            tma_prefetch_desc(&p.mdo);
+            if constexpr (BIAS) tma_prefetch_desc(&p.mbias64);
+            mbar_expect_tx(&sm.x_full, 2 * TILE_BYTES);
+            for (int hh = 0; hh < HALVES; ++hh) {
+                tma_load_4d(sm.x1 + hh * PANEL, &p.mk, &sm.x_full, hh * 64, r0, h, b);
+                tma_load_4d(sm.x2 + hh * PANEL, &p.mv, &sm.x_full, hh * 64, r0, h, b);
+            }
+            bool ok = true;
+            // the list entry of the next block is fetched while waiting for this block's stage
+            const uint16_t *lst = LISTS ? p.tlk_list + (int64_t)tl_idx * p.tl_nqb : nullptr;
+            int qb_next = LISTS ? (int)lst[0] : 0;
+            for (int it = 0; it < nit; ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+                int qb = i_begin + it;
+                if constexpr (LISTS) {
+                    qb = qb_next;
+                    if (it + 1 < nit) qb_next = lst[it + 1];
+                }
+                ok = mbar_wait(&sm.y_empty[s], ph ^ 1u, status, 71);
+                if (!ok) break;
+                if constexpr (LISTS) sm.qblk[s] = qb;   // ordered before the arrive below (release), read after the wait on y_full
+                mbar_expect_tx(&sm.y_full[s], 2 * TILE_BYTES + (STAGE_STATS ? 2 * BT * 4 : 0));
+                const int row = qb * BT;
+                if constexpr (STAGE_STATS) {
+                    bulk_load_1d(sm.lse_s[s], p.lse2 + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
+                    bulk_load_1d(sm.dsc_s[s], p.delta_s + (int64_t)bh * p.Tq128 + row, BT * 4, &sm.y_full[s]);
+                }
+                for (int hh = 0; hh < HALVES; ++hh) {
+                    tma_load_4d(sm.y1[s] + hh * PANEL, &p.mq, &sm.y_full[s], hh * 64, row, h, b);
+                    tma_load_4d(sm.y2[s] + hh * PANEL, &p.mdo, &sm.y_full[s], hh * 64, row, h, b);
+                }
+                if constexpr (BIAS) {
+                    // sub-tile of sub-block parity sb: queries row + 64 sb .. + 63, keys r0 .. r0 + 127
+                    for (int sb = 0; sb < 2 && ok; ++sb) {
+                        ok = mbar_wait(&sm.bb_empty[sb], ((uint32_t)it & 1u) ^ 1u, status, 72);
+                        if (!ok) break;
+                        mbar_expect_tx(&sm.bb_full[sb], BIAS_BYTES);
+                        for (int pn = 0; pn < 2; ++pn)
+                            tma_load_4d(sm.bias[sb] + pn * (64 * 128), &p.mbias64, &sm.bb_full[sb], r0 + pn * 64,
+                                        row + sb * 64, p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                    }
+                    if (!ok) break;
+                }
+            }
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 9 || warp == 10) {
+        // ------------- MMA issuers A1 / A2: the score GEMMs K Q^T and V dO^T -------------
+        // One thread can issue an MMA only every ~54 clocks whatever its size, which is as long
+        // as these N = 64 MMAs take to run, so each kind of GEMM gets its own issuing thread.
+        if (lane == 0 && nit > 0) {
+            const bool second = warp == 10;
+            constexpr uint32_t idesc_g = make_idesc(BF16, BT, 64, false, false);
+            // Descriptors of the operand tiles, encoded once; the loop below only adds offsets.
+            const uint64_t dx = make_sdesc(smem_u32(second ? sm.x2 : sm.x1), 16, 1024);
+            uint64_t dyk[2];                                 // Q (or dO) per stage, K-major view
+#pragma unroll
+            for (int s = 0; s < 2; ++s) dyk[s] = make_sdesc(smem_u32(second ? sm.y2[s] : sm.y1[s]), 16, 1024);
+            const uint32_t gcol = tbase + (second ? G2_COL : G1_COL);
+            uint64_t *full = second ? sm.g2_full : sm.g1_full, *free_ = second ? sm.g2_free : sm.g1_free;
+            bool ok = mbar_wait(&sm.x_full, 0, status, 81);
+            for (int u = 0; u < nsub && ok; ++u) {
+                const int sb = u & 1, it = u >> 1, s = it & 1;
+                if (sb == 0) {
+                    ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 82);
+                    if (!ok) break;
+                }
+                // the columns are free once the accumulation GEMM of sub-block u - 2 has read them
+                if (u >= 2) {
+                    ok = mbar_wait(&free_[sb], (uint32_t)(it - 1) & 1u, status, 85);
+                    if (!ok) break;
+                }
+                tc_fence_after_sync();
+                // [128 keys] x [64 queries of sub-block u], contraction over channels
+                const uint64_t ydu = sdesc_advance(dyk[s], sb * SUB_ROWS);
+                const uint32_t dcol = gcol + sb * 64;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * PANEL + (kk % 4) * 32;
+                    umma_ss(dcol, sdesc_advance(dx, off), sdesc_advance(ydu, off), idesc_g, kk > 0);
+                }
+                umma_commit(&full[sb]);
+            }
+        }
+    } else if (warp == 11) {
+        // ------------------- MMA issuer B: the accumulation GEMMs -------------------
+        // All MMAs that add into dV / dK come from this one thread, in sub-block order, so the
+        // order of the floating-point sums is fixed.
+        if (lane == 0 && nit > 0) {
+            constexpr uint32_t idesc_acc = make_idesc(BF16, BT, D, false, true);
+            constexpr uint32_t idesc_dq = make_idesc(BF16, BT, D, true, true);
+            const uint64_t ddsm = make_sdesc(smem_u32(sm.dsm), 64 * 128 * 2, 1024);   // two 64-query atoms 16 KB apart
+            const uint64_t dkm = make_sdesc(smem_u32(sm.x1), 16, 1024);               // 64 channels: one atom
+            uint64_t dy1m[2], dy2m[2];                       // Q / dO per stage, MN-major view
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                dy1m[s] = make_sdesc(smem_u32(sm.y1[s]), PANEL, 1024);
+                dy2m[s] = make_sdesc(smem_u32(sm.y2[s]), PANEL, 1024);
+            }
+            // accumulation GEMM of sub-block u: contraction over its 64 queries (4 steps of 16),
+            // packed two per column into the first 32 columns of the sub-block's score columns
+            auto issue_acc = [&](int u, uint32_t acc_col, uint32_t a_col, uint64_t yd) {
+                const uint64_t ydu = sdesc_advance(yd, (u & 1) * SUB_ROWS);
+                const uint32_t acol = tbase + a_col + (u & 1) * 64;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma_ts(tbase + acc_col, acol + kk * 8, sdesc_advance(ydu, kk * 2048), idesc_acc, u > 0 || kk > 0);
+            };
+            bool ok = true;
+            for (int u = 0; u < nsub && ok; ++u) {
+                const int sb = u & 1, it = u >> 1, s = it & 1;
+                const uint32_t par = (uint32_t)it & 1u;
+                if (sb == 0) {
+                    ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 87);
+                    if (!ok) break;
+                }
+                ok = mbar_wait(&sm.p_ready[sb], par, status, 83);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_acc(u, ACC1_COL, G1_COL, dy2m[s]);            // dV += P^T dO
+                tc_fence_before_sync();
+                mbar_arrive(&sm.g1_free[sb]);   // issued, not finished: the tensor pipe runs MMAs in issue order
+                ok = mbar_wait(&sm.ds_ready[sb], par, status, 84);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_acc(u, ACC2_COL, G2_COL, dy1m[s]);            // dK += dS^T Q
+                tc_fence_before_sync();
+                mbar_arrive(&sm.g2_free[sb]);
+                if (sb == 1) {
+                    umma_commit(&sm.y_empty[s]);                     // both sub-blocks of this block consumed
+                    // dQ partial tile of this block: [128 queries x 64 channels] = dS [queries x keys] K, with
+                    // A = dS^T as the compute threads left it in shared memory ([key][query], MN-major, one
+                    // 64-query atom per sub-block) and B = the resident K tile ([key][channel], MN-major).
+                    // Its columns are free once the read-back warps hold the previous block's tile.
+                    if (it >= 1) {
+                        ok = mbar_wait(&sm.dq_read, (uint32_t)(it - 1) & 1u, status, 121);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < BT / 16; ++kk)
+                        umma_ss(tbase + DQ_COL, sdesc_advance(ddsm, kk * 2048), sdesc_advance(dkm, kk * 2048), idesc_dq, kk > 0);
+                    umma_commit(&sm.dq_full);
+                }
+            }
+            umma_commit(&sm.acc_full);
+        }
+    } else if (warp >= 12) {
+        // ------------- read-back warps: dQ partial tiles -> fp32 accumulator in global memory -------------
+        // Thread = query row of the block.  The accumulator of a (batch, head) is laid out
+        // [channel / 4][query][channel % 4], so a warp's 16-byte vector reduction covers 512
+        // contiguous bytes.  These warps take the stalls of the reduction traffic.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        const int row_l = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+        float *acc_bh = p.dq_acc + (int64_t)bh * (D / 4) * p.Tq128 * 4;
+        bool ok = true;
+        for (int it = 0; it < nit && ok; ++it) {
+            ok = mbar_wait(&sm.dq_full, (uint32_t)it & 1u, status, 122);
+            if (!ok) break;
+            tc_fence_after_sync();
+            float *dst = acc_bh + ((int64_t)(i_begin + it) * BT + row_l) * 4;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t r[32];
+                tmem_ld32(lane_base + DQ_COL + c * 32, r);
+                tmem_wait_ld();
+                if (c == 1) {
+                    tc_fence_before_sync();
+                    mbar_arrive(&sm.dq_read);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + (int64_t)(c * 8 + i) * p.Tq128 * 4),
+                                 "f"(__uint_as_float(r[4 * i])), "f"(__uint_as_float(r[4 * i + 1])),
+                                 "f"(__uint_as_float(r[4 * i + 2])), "f"(__uint_as_float(r[4 * i + 3]))
+                                 : "memory");
+            }
+        }
+    } else {
+        // ------------------------------ compute warps ------------------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+        // Warps 0-3 own the even sub-blocks, warps 4-7 the odd ones: each thread handles one
+        // key row and all 64 queries of its sub-block, and the two groups run half a period
+        // apart, so one group's exponentials overlap the other's tensor-memory round trips.
+        const int row_l = (warp & 3) * 32 + lane;          // key row of the tile == TMEM lane
+        const int sb = warp >> 2;                          // sub-block parity this warp group owns
+        const int half = sb;                               // epilogue: which half of the channels
+        const int row = r0 + row_l;
+        const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+        const bool cta_key_tail = r0 + BT > p.Tk;
+        const uint32_t col = sb * 64;                      // this group's columns inside G1 / G2
+        // vector bias: this thread's key has one value for every query, times log2(e)
+        float bk2 = 0.f;
+        if constexpr (BIASM == 2) {
+            if (row < p.Tk) {
+                const char *bias_bh = reinterpret_cast<const char *>(p.bias) +
+                                      ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh) * (p.bias_f32 ? 4 : 2);
+                bk2 = (p.bias_f32 ? reinterpret_cast<const float *>(bias_bh)[row]
+                                  : to_f32<T>(reinterpret_cast<const T *>(bias_bh)[row])) * LOG2E;
+            }
+        }
+
+        bool ok = true;
+        for (int it = 0; it < nit; ++it) {
+            const uint32_t par = (uint32_t)it & 1u;
+            const int s = it & 1;
+            int blk0 = (i_begin + it) * BT;
+            if constexpr (LISTS) {
+                // the block's index is posted with its tiles
+                ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
+                if (!ok) break;
+                blk0 = sm.qblk[s] * BT;
+            }
+            const int c0 = blk0 + sb * 64;                 // first query of the sub-block
+            const bool slow = cta_key_tail || (p.causal && blk0 == r0);
+            // row statistics of this sub-block's 64 queries: staged in shared memory, else from global
+            const float *lse_f = STAGE_STATS ? &sm.lse_s[s][sb * 64] : p.lse2 + (int64_t)bh * p.Tq128 + c0;
+            const float *dsc_f = STAGE_STATS ? &sm.dsc_s[s][sb * 64] : p.delta_s + (int64_t)bh * p.Tq128 + c0;
+            const float4 *lse4 = reinterpret_cast<const float4 *>(lse_f);
+            const float4 *dsc4 = reinterpret_cast<const float4 *>(dsc_f);
+            float pv[64];
+
+            if constexpr (!LISTS) {
+                // row statistics of this block have landed
+                ok = mbar_wait(&sm.y_full[s], (uint32_t)(it >> 1) & 1u, status, 90);
+                if (!ok) break;
+            }
+
+            // x0[i] = bias * log2(e) - lse * log2(e) of query i (only -lse without a bias), formed
+            // before the scores are waited for
+            float x0[BIAS ? 64 : 1];
+            if constexpr (BIAS) {
+                ok = mbar_wait(&sm.bb_full[sb], (uint32_t)it & 1u, status, 94);
+                if (!ok) break;
+                // this thread's key column of the sub-tile: panel = key / 64, 16-byte chunk index
+                // XOR (query mod 8) inside the 128-byte row of query i
+                const unsigned char *colp = sm.bias[sb] + (row_l >> 6) * (64 * 128) + (row_l & 7) * 2;
+                const int kc = (row_l & 63) >> 3;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float4 l = lse4[i];
+                    const float lv[4] = {l.x, l.y, l.z, l.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int qi = 4 * i + e;
+                        const float bvl = to_f32<T>(*reinterpret_cast<const T *>(colp + qi * 128 + ((kc ^ (qi & 7)) << 4)));
+                        x0[qi] = fmaf(bvl, LOG2E, -lv[e]);
+                    }
+                }
+            }
+            ok = mbar_wait(&sm.g1_full[sb], par, status, 91);
+            if (!ok) break;
+            tc_fence_after_sync();
+            {
+                uint32_t ra[32], rb[32];
+                tmem_ld32(lane_base + G1_COL + col, ra);
+                tmem_ld32(lane_base + G1_COL + col + 32, rb);
+                tmem_wait_ld();
+                if (!slow) {
+                    if constexpr (BIAS) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            pv[i] = ex2b(fmaf(__uint_as_float(ra[i]), p.scale_log2, x0[i]));
+                            pv[32 + i] = ex2b(fmaf(__uint_as_float(rb[i]), p.scale_log2, x0[32 + i]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 l = lse4[i];
+                            pv[4 * i + 0] = ex2b(fmaf(__uint_as_float(ra[4 * i + 0]), p.scale_log2, bk2 - l.x));
+                            pv[4 * i + 1] = ex2b(fmaf(__uint_as_float(ra[4 * i + 1]), p.scale_log2, bk2 - l.y));
+                            pv[4 * i + 2] = ex2b(fmaf(__uint_as_float(ra[4 * i + 2]), p.scale_log2, bk2 - l.z));
+                            pv[4 * i + 3] = ex2b(fmaf(__uint_as_float(ra[4 * i + 3]), p.scale_log2, bk2 - l.w));
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 l = lse4[8 + i];
+                            pv[32 + 4 * i + 0] = ex2b(fmaf(__uint_as_float(rb[4 * i + 0]), p.scale_log2, bk2 - l.x));
+                            pv[32 + 4 * i + 1] = ex2b(fmaf(__uint_as_float(rb[4 * i + 1]), p.scale_log2, bk2 - l.y));
+                            pv[32 + 4 * i + 2] = ex2b(fmaf(__uint_as_float(rb[4 * i + 2]), p.scale_log2, bk2 - l.z));
+                            pv[32 + 4 * i + 3] = ex2b(fmaf(__uint_as_float(rb[4 * i + 3]), p.scale_log2, bk2 - l.w));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int qi = c0 + i;
+                        const bool masked = row >= p.Tk || qi >= p.Tq || (p.causal && row > qi);
+                        const float sv = __uint_as_float(i < 32 ? ra[i & 31] : rb[i & 31]);
+                        const float off = BIAS ? x0[BIAS ? i : 0] : bk2 - lse_f[i];
+                        pv[i] = masked ? 0.f : ex2b(fmaf(sv, p.scale_log2, off));
+                    }
+                }
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) pk[i] = pack16b<BF16>(pv[2 * i], pv[2 * i + 1]);
+                tmem_st32(lane_base + G1_COL + col, pk);
+                tmem_wait_st();
+            }
+            // P, which depends on every bias value read above, is stored: the bias stage is free
+            if constexpr (BIAS) mbar_arrive(&sm.bb_empty[sb]);
+            tc_fence_before_sync();
+            mbar_arrive(&sm.p_ready[sb]);
+
+            ok = mbar_wait(&sm.g2_full[sb], par, status, 92);
+            if (!ok) break;
+            tc_fence_after_sync();
+            {
+                uint32_t ga[32], gb[32];
+                tmem_ld32(lane_base + G2_COL + col, ga);
+                tmem_ld32(lane_base + G2_COL + col + 32, gb);
+                tmem_wait_ld();
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float4 dd = dsc4[i];
+                    const uint32_t *g = i < 8 ? ga : gb;
+                    const int j = (i & 7) * 4;
+                    const float a0 = pv[4 * i + 0] * fmaf(__uint_as_float(g[j + 0]), p.scale, -dd.x);
+                    const float a1 = pv[4 * i + 1] * fmaf(__uint_as_float(g[j + 1]), p.scale, -dd.y);
+                    const float a2 = pv[4 * i + 2] * fmaf(__uint_as_float(g[j + 2]), p.scale, -dd.z);
+                    const float a3 = pv[4 * i + 3] * fmaf(__uint_as_float(g[j + 3]), p.scale, -dd.w);
+                    pk[2 * i] = pack16b<BF16>(a0, a1);
+                    pk[2 * i + 1] = pack16b<BF16>(a2, a3);
+                }
+                tmem_st32(lane_base + G2_COL + col, pk);
+                // dS^T also goes to shared memory for the dQ partial GEMM, once the GEMM of the previous
+                // block has read it: this key's 64 queries are one 128-byte row, 16-byte chunk c = queries
+                // 8c .. 8c + 7, 128-byte swizzle
+                if (it >= 1) {
+                    ok = mbar_wait(&sm.dq_full, (uint32_t)(it - 1) & 1u, status, 123);
+                    if (!ok) break;
+                }
+                unsigned char *ds_row = sm.dsm + sb * (64 * 128 * 2) + row_l * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4 *>(ds_row + ((c ^ (row_l & 7)) << 4)) =
+                        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                fence_proxy_async_smem();
+                tmem_wait_st();
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&sm.ds_ready[sb]);
+        }
+
+        // epilogue: dV, dK -> global
+        if (ok && nit > 0) ok = mbar_wait(&sm.acc_full, 0, status, 93);
+        tc_fence_after_sync();
+        if (ok) {
+#pragma unroll
+            for (int o = 0; o < 2; ++o) {
+                T *base = reinterpret_cast<T *>(o == 0 ? p.out1 : p.out2);
+                const int64_t sb_ = o == 0 ? p.o1_sb : p.o2_sb, sh = o == 0 ? p.o1_sh : p.o2_sh,
+                              sn = o == 0 ? p.o1_sn : p.o2_sn;
+                T *orow = base + (int64_t)b * sb_ + (int64_t)h * sh + (int64_t)row * sn;
+                const uint32_t acc_col = o == 0 ? ACC1_COL : ACC2_COL;
+#pragma unroll 1
+                for (int c = 0; c < D / 64; ++c) {
+                    const int cc = half * (D / 2) + c * 32;
+                    uint32_t r[32];
+                    if (nit > 0) {
+                        tmem_ld32(lane_base + acc_col + cc, r);
+                        tmem_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = 0u;
+                    }
+                    if (row < p.Tk) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 v;
+                            v.x = pack16b<BF16>(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                            v.y = pack16b<BF16>(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                            v.z = pack16b<BF16>(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                            v.w = pack16b<BF16>(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                            *reinterpret_cast<uint4 *>(orow + cc + i) = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tbase, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
 // dQ without bias, pipelined.  One CTA per 128-query tile, looping over key blocks:
 //   S = Q K^T, dP = dO V^T (SS MMAs), P = exp2(S * scale * log2e - lse2) in registers,
 //   dS = P * (dP * scale - delta_s) packed into the dP columns, dQ += dS K (TS MMA).
@@ -1703,6 +2203,28 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
 // scale, and lse * log2(e).  Rows in [Tq, Tq128) get +inf / 0 so that query
 // positions past the end need no masking in the main kernels.  One warp per row.
 // ---------------------------------------------------------------------------
+// Rounds the fp32 dQ accumulator of the single-pass backward ([B H][16][Tq128][4], head_dim 64) into
+// dQ.  One CTA per 64 queries of one (batch, head): thread = (query, 16 channels).
+template <bool BF16>
+__global__ void __launch_bounds__(256) attn_bwd_dq_round64_kernel(const float *__restrict__ acc, void *dq, int64_t sb, int64_t sh,
+                                                                  int64_t sn, int H, int Tq, int Tq128) {
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+    const int q = blockIdx.x * 64 + ((int)threadIdx.x & 63), part = (int)threadIdx.x >> 6;   // channels 16 part .. + 15
+    if (q >= Tq) return;
+    const float4 *src = reinterpret_cast<const float4 *>(acc) + ((int64_t)bh * 16 + part * 4) * Tq128 + q;
+    uint32_t w[8];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const float4 v = __ldcs(src + (int64_t)g * Tq128);        // a warp reads 512 contiguous bytes
+        w[2 * g] = pack16b<BF16>(v.x, v.y);
+        w[2 * g + 1] = pack16b<BF16>(v.z, v.w);
+    }
+    T *orow = reinterpret_cast<T *>(dq) + (int64_t)b * sb + (int64_t)h * sh + (int64_t)q * sn + part * 16;
+    *reinterpret_cast<uint4 *>(orow) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4 *>(orow + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __grid_constant__ AttnParams p, float *lse2, float *delta_s,
                                                             int Tq128) {
@@ -1736,6 +2258,17 @@ __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __grid_constan
 int64_t tmem_bwd_workspace_bytes(int64_t B, int64_t H, int64_t Tq) {
     const int64_t Tq128 = (Tq + 127) / 128 * 128;
     return 2 * B * H * Tq128 * (int64_t)sizeof(float);
+}
+
+// The fp32 dQ accumulator of the single-pass backward (0 bytes: no such form for this head_dim); it
+// follows the statistics rows in the workspace, 256-byte aligned.
+int64_t single_pass_acc_offset(int64_t B, int64_t H, int64_t Tq) {
+    return (tmem_bwd_workspace_bytes(B, H, Tq) + 255) / 256 * 256;
+}
+int64_t single_pass_acc_bytes(int64_t B, int64_t H, int64_t Tq, int64_t d) {
+    if (d != 64) return 0;
+    const int64_t Tq128 = (Tq + 127) / 128 * 128;
+    return B * H * Tq128 * d * (int64_t)sizeof(float);
 }
 
 bool tmem_bwd_eligible(const AttnParams &p) {
@@ -1774,11 +2307,43 @@ static int launch_dkdv_sub(const BwdTmaParams &bp, int nblocks, int BH, cudaStre
     return check_launch();
 }
 
+// Single-pass form (head_dim 64): zero the accumulator, one kernel for dK, dV and the dQ partial sums,
+// round dQ.  bias_mode: 0 none, 1 matrix bias staged by TMA, 2 vector bias.
+template <bool BF16>
+static int bwd_single64(BwdTmaParams &bp, const AttnParams &p, int bias_mode, cudaStream_t st) {
+    const int BH = p.B * p.H;
+    if (cudaMemsetAsync(bp.dq_acc, 0, (size_t)BH * bp.Tq128 * 64 * sizeof(float), st) != cudaSuccess) return RGD_E_DEVICE;
+    const size_t smem = (bias_mode == 1 ? sizeof(Single64Smem<true>) : sizeof(Single64Smem<false>)) + 1024;
+    const void *kernel = bias_mode == 1   ? reinterpret_cast<const void *>(attn_bwd_single64<BF16, 1>)
+                         : bias_mode == 2 ? reinterpret_cast<const void *>(attn_bwd_single64<BF16, 2>)
+                                          : reinterpret_cast<const void *>(attn_bwd_single64<BF16, 0>);
+    if (int e = ensure_dyn_smem(kernel, smem)) return e;
+    dim3 grid((p.Tk + BT - 1) / BT, BH);
+    if (bias_mode == 1) attn_bwd_single64<BF16, 1><<<grid, SINGLE64_THREADS, smem, st>>>(bp);
+    else if (bias_mode == 2) attn_bwd_single64<BF16, 2><<<grid, SINGLE64_THREADS, smem, st>>>(bp);
+    else attn_bwd_single64<BF16, 0><<<grid, SINGLE64_THREADS, smem, st>>>(bp);
+    count_launch();
+    if (int e = check_launch()) return e;
+    dim3 rgrid((p.Tq + 63) / 64, BH);
+    attn_bwd_dq_round64_kernel<BF16><<<rgrid, 256, 0, st>>>(bp.dq_acc, p.dq, p.dq_sb, p.dq_sh, p.dq_sn, p.H, p.Tq, bp.Tq128);
+    count_launch();
+    return check_launch();
+}
+
 template <int D, bool BF16>
 static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     const int BH = p.B * p.H;
     bp.out1 = p.dv; bp.o1_sb = p.dv_sb; bp.o1_sh = p.dv_sh; bp.o1_sn = p.dv_sn;
     bp.out2 = p.dk; bp.o2_sb = p.dk_sb; bp.o2_sh = p.dk_sh; bp.o2_sn = p.dk_sn;
+    if constexpr (D == 64) {
+        // the caller gave room for the fp32 dQ accumulator: single-pass form (not with tile lists or
+        // a bias gradient, which the two-kernel form serves)
+        if (bp.dq_acc != nullptr && bp.dbias == nullptr && bp.tlk_cnt == nullptr && p.Tk > 0) {
+            if (bp.bias_kind == RGD_BIAS_NONE) return bwd_single64<BF16>(bp, p, 0, st);
+            if (bp.bias_vec == 2) return bwd_single64<BF16>(bp, p, 1, st);
+            if (bp.bias_kind == RGD_BIAS_VECTOR) return bwd_single64<BF16>(bp, p, 2, st);
+        }
+    }
     if (bp.bias_kind == RGD_BIAS_NONE) {
         if (int e = launch_dkdv_sub<D, BF16, 0>(bp, (p.Tk + BT - 1) / BT, BH, st)) return e;
     } else if (bp.bias_vec == 2) {       // matrix bias staged by TMA, with or without tile lists
@@ -1830,10 +2395,13 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     return launch_bwd_tmem<D, BF16, false>(bp, (p.Tq + BT - 1) / BT, BH, st);
 }
 
-// p.delta points at the caller's workspace (tmem_bwd_workspace_bytes).  Returns TMEM_NOT_TAKEN
+// p.delta points at the caller's workspace (tmem_bwd_workspace_bytes); dq_acc, when not null, at an
+// fp32 accumulator of single_pass_acc_bytes, which selects the single-pass form where one exists.
+// Returns TMEM_NOT_TAKEN
 // (nothing launched) when a descriptor cannot be encoded after all.
-int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, cudaStream_t st) {
+int tmem_bwd(const AttnParams &p, int dtype, rgd_cache *cache, float *dq_acc, cudaStream_t st) {
     BwdTmaParams bp{};
+    bp.dq_acc = dq_acc;
     const bool bf16 = dtype == RGD_BF16;
     const int Tq128 = (p.Tq + 127) / 128 * 128;
     float *lse2 = p.delta, *delta_s = p.delta + (int64_t)p.B * p.H * Tq128;

@@ -183,6 +183,12 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_
     return d;
 }
 
+// Makes shared-memory writes of this thread (generic proxy) visible to the async proxy, through
+// which MMAs and bulk copies read shared memory.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // The same descriptor `bytes` further into shared memory.  The start-address field is the
 // low 14 bits in 16-byte units and shared memory ends below 2^18 bytes, so the sum never
 // carries into the next field: one add instead of re-encoding the descriptor per MMA (the

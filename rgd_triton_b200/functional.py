@@ -37,6 +37,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 import weakref
 
 import torch
@@ -823,6 +824,31 @@ class FlashAttnFunc(torch.autograd.Function):
         return dq, dk, dv, dbias, None, None, None
 
 
+# How the attention backward forms dQ where the library offers a choice (head_dim 64 on the
+# tensor-memory kernels):
+#   "single_pass"  S, dP and the exponentials are evaluated once per tile pair and the dQ partial tiles
+#                  are added into an fp32 accumulator (B * H * Tq * d * 4 bytes of scratch per call) with
+#                  vector reductions, like the reference's atomic adds into dq
+#                  (flash_attn_triton_cached.py:556-561): dK, dV bit-reproducible, dQ to its last bits only;
+#   "two_kernel"   a dK/dV kernel and a dQ kernel, every output bit-reproducible, no accumulator.
+_ATTN_BWD_MODE = os.environ.get("RGD_B200_ATTN_BWD", "single_pass")
+
+
+def set_attention_backward(mode: str) -> str:
+    """Select "single_pass" (default) or "two_kernel"; returns the previous setting."""
+    global _ATTN_BWD_MODE
+    _require(mode in ("single_pass", "two_kernel"), "mode must be 'single_pass' or 'two_kernel'")
+    prev, _ATTN_BWD_MODE = _ATTN_BWD_MODE, mode
+    return prev
+
+
+def _attn_bwd_bytes(lib, single, *dims) -> int:
+    nbytes = int(lib.rgd_attn_bwd_workspace_bytes(*dims))
+    if single and nbytes >= 0:
+        nbytes = max(nbytes, int(lib.rgd_attn_bwd_single_pass_workspace_bytes(*dims)))
+    return nbytes
+
+
 def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache, want_dbias=False, tiles=None):
     """dq, dk, dv and, when asked for, the gradient of the bias (the reference refuses it,
     flash_attn_triton_cached.py:1107): d bias = P * (dP - delta), summed over the dimensions along
@@ -838,8 +864,9 @@ def _attn_backward(q, k, v, bias, o, lse, do, causal, softmax_scale, cache, want
     if tiles is not None and not want_dbias:
         bias_s.tiles = tiles.data_ptr()
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    dt, nbytes = _const(plan, "c", lambda: (_lib.dtype_code(q.dtype), int(lib.rgd_attn_bwd_workspace_bytes(
-        batch, nheads, seqlen_q, seqlen_k, d, _lib.dtype_code(q.dtype)))))
+    single = _ATTN_BWD_MODE == "single_pass" and d == 64 and not want_dbias and tiles is None
+    dt, nbytes = _const(plan, ("c", single), lambda: (_lib.dtype_code(q.dtype), _attn_bwd_bytes(
+        lib, single, batch, nheads, seqlen_q, seqlen_k, d, _lib.dtype_code(q.dtype))))
     _require(nbytes >= 0, "attn_bwd: bad sizes")
     work = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
     qh, kh, vh, oh, doh, dqh, dkh, dvh = _heads_refs(plan, "h", (q, k, v, o, do, dq, dk, dv), _attn_heads)

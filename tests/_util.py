@@ -70,3 +70,18 @@ def assert_attn(got, exact_f32, lowp, what, factor=2.0, floor=1e-4):
 
 def T(a):
     return torch.from_numpy(np.asarray(a))
+
+
+import contextlib
+
+
+@contextlib.contextmanager
+def attention_backward(mode):
+    """Run the body with the attention backward in "two_kernel" (every output bit-reproducible)
+    or "single_pass" (head_dim 64: dQ is summed with reductions whose order is not fixed) mode."""
+    from rgd_triton_b200 import functional as F_
+    prev = F_.set_attention_backward(mode)
+    try:
+        yield
+    finally:
+        F_.set_attention_backward(prev)

@@ -13,7 +13,7 @@ import torch
 
 from oracle import oracle as O
 from rgd_triton_b200 import functional as F_, ops
-from tests._util import DTYPES, T, assert_attn, attn_error, gen, randn
+from tests._util import DTYPES, T, assert_attn, attention_backward, attn_error, gen, randn
 
 pytestmark = pytest.mark.gpu
 
@@ -278,23 +278,59 @@ def test_backward_overflow_small_seqlens():
         assert_attn(dv, edv, ldv, "dv", factor=5.0, floor=2e-2)
 
 
-def test_repeat_runs_are_bit_identical():
-    """tests/test_flash_attn.py:341-388: outputs and dK/dV bit-equal across
-    repeated launches; here dQ as well (no atomics anywhere)."""
+@pytest.mark.parametrize("mode", ["two_kernel", "single_pass"])
+def test_repeat_runs_are_bit_identical(mode):
+    """tests/test_flash_attn.py:341-388: outputs and dK/dV bit-equal across repeated launches, dQ
+    within 2 * max |(dq + 0.3 - 0.3) - dq| (the reference adds into dq with atomics).  The
+    two-kernel backward has no atomics anywhere, so there dQ is bit-equal as well; the single-pass
+    backward (head_dim 64) holds exactly the reference's contract."""
     g = gen(10)
     q, k, v = (randn(g, 6, n, 5, 64, dtype=torch.bfloat16).cuda() for n in (239, 127, 127))
     do = randn(g, 6, 239, 5, 64, dtype=torch.bfloat16).cuda()
     m = ops.FlashAttention()
     first = None
-    for _ in range(10):
-        qi, ki, vi = (t.clone().requires_grad_(True) for t in (q, k, v))
-        o = m(qi, ki, vi)
-        cur = [o, *torch.autograd.grad(o, (qi, ki, vi), do)]
-        if first is None:
-            first = [t.clone() for t in cur]
-        else:
-            assert all(torch.equal(a, b) for a, b in zip(first, cur))
+    with attention_backward(mode):
+        for _ in range(10):
+            qi, ki, vi = (t.clone().requires_grad_(True) for t in (q, k, v))
+            o = m(qi, ki, vi)
+            cur = [o, *torch.autograd.grad(o, (qi, ki, vi), do)]
+            if first is None:
+                first = [t.clone() for t in cur]
+                dq_atol = 2 * ((first[1] + 0.3 - 0.3) - first[1]).abs().max().item()
+            else:
+                for i in (0, 2, 3):
+                    assert torch.equal(first[i], cur[i])
+                if mode == "two_kernel":
+                    assert torch.equal(first[1], cur[1])
+                else:
+                    assert (first[1].float() - cur[1].float()).abs().max().item() <= dq_atol
     assert m.cache.fwd is not None and m.cache.bwd is not None
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("bias_kind", [None, "vector", "matrix"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_single_pass_backward_against_two_kernel(dt, bias_kind, causal):
+    """head_dim 64: the single-pass backward returns bit-identical dK and dV and a dQ within one
+    rounding step of the two-kernel form (same arithmetic per tile; only the order of the fp32 sums
+    into dQ differs), on sizes with ragged ends and several key and query blocks."""
+    dtype = DTYPES[dt]
+    g = gen(64 + int(causal) + len(bias_kind or ""))
+    B, H, tq, tk = 2, 3, 1100, 904
+    q, do = randn(g, B, tq, H, 64, dtype=dtype), randn(g, B, tq, H, 64, dtype=dtype)
+    k, v = randn(g, B, tk, H, 64, dtype=dtype), randn(g, B, tk, H, 64, dtype=dtype)
+    bias = None
+    if bias_kind == "vector":
+        bias = randn(g, B, H, 1, tk, dtype=dtype)
+    elif bias_kind == "matrix":
+        bias = randn(g, 1, H, tq, tk, dtype=dtype)
+    with attention_backward("two_kernel"):
+        a = run_attn(q, k, v, do, bias, causal)
+    with attention_backward("single_pass"):
+        b = run_attn(q, k, v, do, bias, causal)
+    assert torch.equal(a[3], b[3]) and torch.equal(a[4], b[4])
+    ulp = 2.0 ** (-7 if dtype == torch.bfloat16 else -10)
+    assert (a[2].float() - b[2].float()).abs().max().item() <= 2 * ulp * a[2].float().abs().max().item()
 
 
 @pytest.mark.parametrize("d", [64, 128])
@@ -308,12 +344,17 @@ def test_long_sequences_steady_state_pipeline(d, causal):
     q, k, v, do = (randn(g, 1, 1664, 2, d, dtype=torch.bfloat16) for _ in range(4))
     check(q, k, v, do, None, causal, f"long d={d} causal={causal}")
     first = None
-    for _ in range(4):
+    with attention_backward("two_kernel"):
+        for _ in range(4):
+            cur = run_attn(q, k, v, do, None, causal)
+            if first is None:
+                first = cur
+            else:
+                assert all(torch.equal(a, b) for a, b in zip(first, cur))
+    # the default backward (single-pass at head_dim 64): everything but dQ stays bit-equal
+    for _ in range(3):
         cur = run_attn(q, k, v, do, None, causal)
-        if first is None:
-            first = cur
-        else:
-            assert all(torch.equal(a, b) for a, b in zip(first, cur))
+        assert all(torch.equal(first[i], cur[i]) for i in (0, 1, 3, 4))
 
 
 def _check_sampled_heads(cfg, q, k, v, do, bias_dev, o, grads, pairs):
@@ -534,10 +575,12 @@ def test_masked_bias_tiles_are_skipped_with_identical_results(d, form, mask):
         return [o.detach(), *torch.autograd.grad(o, (qd, kd, vd), dod)]
 
     prev = F_.set_skip_masked_tiles(False)
+    prev_mode = F_.set_attention_backward("two_kernel")     # the list-following backward is the two-kernel form
     try:
         dense = run(ops.FlashAttention())
     finally:
         F_.set_skip_masked_tiles(prev)
+        F_.set_attention_backward(prev_mode)
     # the dense evaluation itself against the oracle (so that "identical" cannot mean "equally wrong")
     fb = bias.float()
     eo, _ = O.attn_fwd(q.float(), k.float(), v.float(), fb)
@@ -547,10 +590,11 @@ def test_masked_bias_tiles_are_skipped_with_identical_results(d, form, mask):
         assert_attn(got_.cpu(), e_, l_, f"dense {name} ({mask}, {form}, d={d})", factor=2.0,
                     floor=1e-4 if name == "o" else GRAD_FLOOR)
     m = ops.FlashAttention()
-    for call in range(3):
-        got = run(m)
-        for a, b_, name in zip(got, dense, ("o", "dq", "dk", "dv")):
-            assert torch.equal(a, b_), f"call {call}: {name} differs from the dense evaluation"
+    with attention_backward("two_kernel"):
+        for call in range(3):
+            got = run(m)
+            for a, b_, name in zip(got, dense, ("o", "dq", "dk", "dv")):
+                assert torch.equal(a, b_), f"call {call}: {name} differs from the dense evaluation"
     torch.cuda.synchronize()
     ent = m.cache._tiles
     assert ent[0]() is bd and torch.is_tensor(ent[2]), "the bias was not scanned on its second use"

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from rgd_triton_b200 import ops
-from tests._util import gen, randn, rotary_table
+from tests._util import attention_backward, gen, randn, rotary_table
 
 pytestmark = pytest.mark.gpu
 
@@ -52,5 +52,6 @@ def test_attention_compiles():
     q, k, v = (randn(g, 2, 200, 3, 64, dtype=torch.float16).cuda() for _ in range(3))
     bias = randn(g, 2, 3, 200, 200, dtype=torch.float16).cuda()
     fa = ops.FlashAttention()
-    _both(lambda a, b, c: fa(a, b, c), [q, k, v])
-    _both(lambda a, b, c: fa(a, b, c, bias, True), [q, k, v])
+    with attention_backward("two_kernel"):      # bit-equality of dq needs the form without reductions at head_dim 64
+        _both(lambda a, b, c: fa(a, b, c), [q, k, v])
+        _both(lambda a, b, c: fa(a, b, c, bias, True), [q, k, v])

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from rgd_triton_b200 import _lib, ops
-from tests._util import gen, randn, rotary_table
+from tests._util import attention_backward, gen, randn, rotary_table
 
 pytestmark = pytest.mark.gpu
 
@@ -87,4 +87,35 @@ def test_attention_captures(d, bias_kind):
     elif bias_kind == "vector":
         bias = randn(g, B, 1, 1, T_, dtype=dt).cuda()
     fa = ops.FlashAttention()
-    _capture_and_replay(_fwd_bwd(lambda q, k, v: fa(q, k, v, bias, d == 64)), a, b)
+    with attention_backward("two_kernel"):
+        _capture_and_replay(_fwd_bwd(lambda q, k, v: fa(q, k, v, bias, d == 64)), a, b)
+
+
+def test_single_pass_attention_backward_captures():
+    """The single-pass backward (head_dim 64: accumulator zero-fill, one kernel, rounding kernel)
+    inside a graph: o, dk, dv of the replay bit-equal to eager, dq to within one rounding step."""
+    g = gen(99)
+    dt = torch.float16
+    mk = lambda: [randn(g, 2, 640, 3, 64, dtype=dt).cuda() for _ in range(3)]
+    a, b = mk(), mk()
+    bias = randn(g, 2, 3, 640, 640, dtype=dt).cuda()
+    fa = ops.FlashAttention()
+    step = _fwd_bwd(lambda q, k, v: fa(q, k, v, bias))
+    static = [t.clone() for t in a]
+    with attention_backward("single_pass"):
+        for _ in range(3):
+            step(*static)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured = step(*static)
+        for s_, f in zip(static, b):
+            s_.copy_(f)
+        graph.replay()
+        torch.cuda.synchronize()
+        want = step(*[f.clone() for f in b])
+    torch.cuda.synchronize()
+    for i in (0, 2, 3):
+        assert torch.equal(captured[i], want[i])
+    assert (captured[1].float() - want[1].float()).abs().max().item() <= 2 ** -9 * want[1].float().abs().max().item()
+    assert _lib.load().rgd_device_status() == 0
