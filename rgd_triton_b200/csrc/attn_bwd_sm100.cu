@@ -1853,7 +1853,10 @@ struct alignas(1024) DqBiasSmem {
     uint32_t tmem_base;
 };
 
-template <int D, bool BF16, bool DBIAS, bool LISTS>
+// VEC: the bias is a vector (one value per key, 16-bit, 16-byte addressable, key count a multiple of 8):
+// the producer stages the block's 128 values (256 bytes) with one bulk copy instead of a 32 KB tile, and
+// every compute thread reads its 64 from shared memory (the same addresses in all threads: broadcasts).
+template <int D, bool BF16, bool DBIAS, bool LISTS, bool VEC>
 __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __grid_constant__ BwdTmaParams p,
                                                                        const void *q_base, const void *do_base,
                                                                        int64_t q_sb, int64_t q_sh, int64_t q_sn,
@@ -1921,7 +1924,7 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
         if (lane == 0 && nit > 0) {
             tma_prefetch_desc(&p.mk);
             tma_prefetch_desc(&p.mv);
-            tma_prefetch_desc(&p.mbias);
+            if constexpr (!VEC) tma_prefetch_desc(&p.mbias);
             bool ok = true;
             int ks = 0;
             uint32_t kph = 0;                              // phase of the K ring slot's previous use
@@ -1937,10 +1940,17 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
                 // bias tile of block it: rows = this CTA's queries, columns = the block's keys
                 ok = mbar_wait(&sm.bb_empty[vs], ((uint32_t)(it >> 1) & 1u) ^ 1u, status, 43);
                 if (!ok) break;
-                mbar_expect_tx(&sm.bb_full[vs], BIAS_BYTES);
-                for (int pn = 0; pn < 2; ++pn)
-                    tma_load_4d(sm.bias[vs] + pn * (BT * 128), &p.mbias, &sm.bb_full[vs], row + pn * 64, r0,
-                                p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                if constexpr (VEC) {
+                    const uint32_t nbytes = (uint32_t)min(BT, p.Tk - row) * 2u;       // a multiple of 16
+                    mbar_expect_tx(&sm.bb_full[vs], nbytes);
+                    bulk_load_1d(sm.bias[vs], reinterpret_cast<const char *>(p.bias) +
+                                                  ((int64_t)b * p.b_sb + (int64_t)h * p.b_sh + row) * 2, nbytes, &sm.bb_full[vs]);
+                } else {
+                    mbar_expect_tx(&sm.bb_full[vs], BIAS_BYTES);
+                    for (int pn = 0; pn < 2; ++pn)
+                        tma_load_4d(sm.bias[vs] + pn * (BT * 128), &p.mbias, &sm.bb_full[vs], row + pn * 64, r0,
+                                    p.bias_h0 ? 0 : h, p.bias_b0 ? 0 : b);
+                }
                 ok = mbar_wait(&sm.v_empty[vs], ((uint32_t)(it >> 1) & 1u) ^ 1u, status, 42);
                 if (!ok) break;
                 mbar_expect_tx(&sm.v_full[vs], TILE_BYTES);
@@ -2064,11 +2074,13 @@ __global__ void __launch_bounds__(DQ_PIPE_THREADS, 1) attn_bwd_dq_bias(const __g
             if (!mbar_wait(&sm.bb_full[j & 1], (uint32_t)(j >> 1) & 1u, status, 65)) return false;
             // 64 key columns = the whole 128-byte row of panel `half`; pv first holds
             // bias * log2(e) - lse * log2(e)
-            const unsigned char *rowp = sm.bias[j & 1] + half * (BT * 128) + row_l * 128;
+            // (vector bias: the 64 values of this half of the block, the same for every row; values past
+            // the end of the keys were not loaded and are masked below)
+            const unsigned char *rowp = VEC ? sm.bias[j & 1] + half * 128 : sm.bias[j & 1] + half * (BT * 128) + row_l * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 union { uint4 u; T v[8]; } cv;
-                cv.u = *reinterpret_cast<const uint4 *>(rowp + ((c ^ (row_l & 7)) << 4));
+                cv.u = *reinterpret_cast<const uint4 *>(rowp + (VEC ? (c << 4) : ((c ^ (row_l & 7)) << 4)));
 #pragma unroll
                 for (int e = 0; e < 8; ++e) pv[8 * c + e] = fmaf(to_f32<T>(cv.v[e]), LOG2E, -lse_row);
             }
@@ -2359,6 +2371,17 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
     }
     bp.out1 = p.dq; bp.o1_sb = p.dq_sb; bp.o1_sh = p.dq_sh; bp.o1_sn = p.dq_sn;
     bp.out2 = nullptr;
+    if (bp.bias_kind == RGD_BIAS_VECTOR && bp.bias_vec == 1 && !bp.bias_f32 && p.Tk % 8 == 0) {
+        // 16-bit vector bias, 16-byte addressable: staged per key block by one bulk copy
+        const size_t smem = sizeof(DqBiasSmem<D>) + 1024;
+        const void *kernel = reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, false, false, true>);
+        if (int e = ensure_dyn_smem(kernel, smem)) return e;
+        dim3 grid((p.Tq + BT - 1) / BT, BH);
+        attn_bwd_dq_bias<D, BF16, false, false, true><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
+                                                                                             p.do_sb, p.do_sh, p.do_sn);
+        count_launch();
+        return check_launch();
+    }
     if (bp.bias_kind == RGD_BIAS_NONE || (bp.bias_kind == RGD_BIAS_VECTOR && bp.bias_vec != 2)) {
         const bool vec = bp.bias_kind == RGD_BIAS_VECTOR;
         const size_t smem = sizeof(DqPipeSmem<D>) + 1024;
@@ -2375,19 +2398,19 @@ static int bwd_both(BwdTmaParams &bp, const AttnParams &p, cudaStream_t st) {
         const size_t smem = sizeof(DqBiasSmem<D>) + 1024;
         // three instantiations: plain, writing the bias gradient, following tile lists (never both)
         const int mode = bp.dbias != nullptr ? 1 : (bp.tlq_cnt != nullptr ? 2 : 0);
-        const void *kernel = mode == 1   ? reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, true, false>)
-                             : mode == 2 ? reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, false, true>)
-                                         : reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, false, false>);
+        const void *kernel = mode == 1   ? reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, true, false, false>)
+                             : mode == 2 ? reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, false, true, false>)
+                                         : reinterpret_cast<const void *>(attn_bwd_dq_bias<D, BF16, false, false, false>);
         if (int e = ensure_dyn_smem(kernel, smem)) return e;
         dim3 grid((p.Tq + BT - 1) / BT, BH);
         if (mode == 1)
-            attn_bwd_dq_bias<D, BF16, true, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
+            attn_bwd_dq_bias<D, BF16, true, false, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
                                                                                           p.do_sb, p.do_sh, p.do_sn);
         else if (mode == 2)
-            attn_bwd_dq_bias<D, BF16, false, true><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
+            attn_bwd_dq_bias<D, BF16, false, true, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh, p.q_sn,
                                                                                           p.do_sb, p.do_sh, p.do_sn);
         else
-            attn_bwd_dq_bias<D, BF16, false, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh,
+            attn_bwd_dq_bias<D, BF16, false, false, false><<<grid, DQ_PIPE_THREADS, smem, st>>>(bp, p.q, p.d_o, p.q_sb, p.q_sh,
                                                                                            p.q_sn, p.do_sb, p.do_sh, p.do_sn);
         count_launch();
         return check_launch();
