@@ -225,6 +225,71 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
 }
 
 // ---------------------------------------------------------------------------
+// CTA pairs (clusters of two, tcgen05 cta_group::2): one MMA spans the tensor cores of both SMs
+// (M = 256: each CTA supplies its 128 rows of A and receives its 128 rows of D; B's N rows are
+// split between the two CTAs' shared memories, so each SM fetches only half of B).  The thread
+// of the even CTA (the leader) issues; barriers that both CTAs feed live in the leader and are
+// addressed through the shared::cluster window (mapa).  No multicast anywhere: every CTA loads
+// its own operand halves from this GPU's memory.  The library's kernels do not use pairs (an
+// attention forward built on them ran the MMAs at full rate but measured no faster than the
+// one-CTA kernel); microbench/mma_rate.cu measures them.
+// ---------------------------------------------------------------------------
+// shared::cluster address of the object at this shared-memory address in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_addr(const void *p, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(p)), "r"(rank));
+    return a;
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// All threads of all CTAs of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Tensor memory of a CTA pair: executed by the same warp of BOTH CTAs.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A[smem of each CTA] * B[smem, halves]; issued by ONE thread of the leader.
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+// One arrival on the barrier at this offset in BOTH CTAs once every pair MMA issued so far by
+// this thread has finished: two commits, one per CTA (no multicast form).
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr(bar, 0)) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr(bar, 1)) : "memory");
+}
+
+// ---------------------------------------------------------------------------
 // Host: tensor maps
 // ---------------------------------------------------------------------------
 // Encode a 4-D tiled tensor map over a (B, H, T, d) view of 16-bit elements

@@ -1,6 +1,6 @@
 """Build and run one of the micro-benchmarks of this folder on the current GPU.
 
-    python -m rgd_triton_b200.microbench.run mma_rate | l2_reduction
+    python -m rgd_triton_b200.microbench.run mma_rate | l2_reduction | alu_rate
 
 They are stand-alone programs (not part of librgd_b200.so): measurements that shaped the
 kernels and that the notes under profiles/ quote.  Each runs for a few seconds on one GPU.
@@ -15,7 +15,7 @@ from pathlib import Path
 from ..build import NVCC_FLAGS, _nvcc
 
 HERE = Path(__file__).resolve().parent
-NAMES = ("mma_rate", "l2_reduction")
+NAMES = ("mma_rate", "l2_reduction", "alu_rate")
 
 
 def main(argv=None) -> int:
