@@ -498,6 +498,87 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 continue;
             }
 
+            if (BIAS == 0 && need_mask) {
+                // ---- no bias, block crossing the causal diagonal or the end of the keys: the
+                // same pipelined passes as above (a copy of their own, so that the interior blocks'
+                // code stays as it is), with the hidden scores set to -inf in registers as each
+                // chunk arrives.  Every row of a visited block keeps at least its first key, so
+                // the block maximum stays finite. ----
+                const int last_key = min(p.Tk - 1, p.causal ? row : p.Tk - 1) - n0;   // last visible key of this row, block-relative
+                auto mask32 = [&](uint32_t (&r)[32], int c0) {
+                    const int lim = last_key - c0;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (i > lim) r[i] = 0xff800000u;          // -inf
+                };
+                uint32_t ra[32], rb[32];
+                tmem_ld32(s_addr, ra);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 32, rb);
+                mask32(ra, 0);
+                float m0 = max32(ra);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 64, ra);
+                mask32(rb, 32);
+                float m1 = max32(rb);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 96, rb);
+                mask32(ra, 64);
+                m0 = fmaxf(m0, max32(ra));
+                tmem_wait_ld();
+                tmem_ld32(s_addr, ra);                       // chunk 0 again, for the second pass
+                mask32(rb, 96);
+                m1 = fmaxf(m1, max32(rb));
+                const float mx = fmaxf(m0, m1) * p.scale_log2;          // scale > 0: max commutes with it
+                const bool want = (mx > m_ref + RESCALE_THRESHOLD) || (m_ref == -INFINITY && mx > -INFINITY);
+                if (__any_sync(0xffffffffu, want)) {
+                    const float alpha = !want ? 1.f : (m_ref == -INFINITY ? 0.f : ex2(m_ref - mx));
+                    l_sum *= alpha;
+                    if (want) m_ref = mx;
+                    if (j > 0) {
+#pragma unroll 1
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t r[32];
+                            tmem_ld32(lane_base + o_col + c * 32, r);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                            tmem_st32(lane_base + o_col + c * 32, r);
+                        }
+                    }
+                }
+                const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+                float ls0 = 0.f, ls1 = 0.f;
+                uint32_t pk[16];
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 32, rb);
+                mask32(ra, 0);
+                exp32<BF16>(ra, p.scale_log2, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr, pk);                       // packed P over columns already read
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 64, ra);
+                mask32(rb, 32);
+                exp32<BF16>(rb, p.scale_log2, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr + 16, pk);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 96, rb);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.p_half[t][0]);               // keys 0..63 of P are in place
+                mask32(ra, 64);
+                exp32<BF16>(ra, p.scale_log2, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr + 32, pk);
+                tmem_wait_ld();
+                mask32(rb, 96);
+                exp32<BF16>(rb, p.scale_log2, m_use, pk, ls0, ls1);
+                tmem_st16(s_addr + 48, pk);
+                l_sum += ls0 + ls1;
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sm.p_half[t][1]);
+                continue;
+            }
+
             if (BIAS != 0 && !need_mask) {
                 // ---- interior block with a bias: x = s * scale * log2e + bias * log2e is formed
                 // ONCE per element (the bias tile is read and converted once), written back over
