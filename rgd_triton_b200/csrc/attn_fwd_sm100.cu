@@ -189,6 +189,109 @@ __device__ __forceinline__ void exp32(const uint32_t (&r)[32], float scale_log2,
     }
 }
 
+// A block with a bias that crosses the causal diagonal or the end of the keys: the two passes
+// of the interior bias block of the kernel below, with x of the hidden keys set to -inf as it
+// is formed.  Out of line on purpose: inlined next to the interior passes it costs those
+// 8-19 % (registers), and it runs for one or two of a tile's key blocks only.  head_dim 128
+// only: at head_dim 64 even the call costs the interior blocks of a dense bias 6 %, so those
+// kernels keep the per-element passes at the end of the key loop.
+// `last_key`: last visible key of this thread's row, relative to the block; `bias_row`: for
+// BIAS == 1 the 32-value loader's row pointer arguments, for BIAS == 2 the staged tile.
+struct MaskedBiasArgs {
+    uint32_t s_addr, o_addr;     // tensor-memory addresses of this thread's score and accumulator rows
+    int last_key, n0, row_l, brow, j;
+    const char *bias_bh;         // BIAS == 1, not staged
+    const float *vbias;          // BIAS == 1, staged vector: 128 values of this block
+    const unsigned char *btile;  // BIAS == 2
+    float m_ref, l_sum;          // in / out
+};
+
+template <int D, bool BF16, int BIAS>
+__device__ __noinline__ void masked_bias_block(const FwdTmaParams &p, MaskedBiasArgs &a, uint64_t *b_empty, uint64_t *p_half0,
+                                               uint64_t *p_half1) {
+    uint32_t ra[32], rb[32];
+    float m0 = -INFINITY, m1 = -INFINITY;
+    const uint32_t s_addr = a.s_addr;
+    tmem_ld32(s_addr, ra);
+    tmem_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t (&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t (&nxt)[32] = (c & 1) ? ra : rb;
+        if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, nxt);
+        float bb[32];
+        if constexpr (BIAS == 1) {
+            if (a.vbias != nullptr) {
+                const float4 *src = reinterpret_cast<const float4 *>(a.vbias + c * 32);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float4 f = src[i];
+                    bb[4 * i] = f.x; bb[4 * i + 1] = f.y; bb[4 * i + 2] = f.z; bb[4 * i + 3] = f.w;
+                }
+            } else {
+                load_bias32<BF16>(p, a.bias_bh, a.brow, a.n0 + c * 32, bb);
+            }
+        }
+        if constexpr (BIAS == 2) bias_from_smem<BF16>(a.btile, a.row_l, c * 32, bb);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            cur[i] = (i > a.last_key - c * 32) ? 0xff800000u : __float_as_uint(fmaf(__uint_as_float(cur[i]), p.scale_log2, bb[i]));
+        if (c & 1) m1 = fmaxf(m1, max32(cur));
+        else m0 = fmaxf(m0, max32(cur));
+        tmem_st32(s_addr + c * 32, cur);
+        if (c < 3) tmem_wait_ld();
+    }
+    tmem_wait_st();                              // x is in tensor memory; the bias tile is consumed
+    if constexpr (BIAS == 2) mbar_arrive(b_empty);
+    tmem_ld32(s_addr, ra);                       // chunk 0 of x, for the second pass
+    float m_ref = a.m_ref, l_sum = a.l_sum;
+    const float mx = fmaxf(m0, m1);
+    const bool want = (mx > m_ref + RESCALE_THRESHOLD) || (m_ref == -INFINITY && mx > -INFINITY);
+    if (__any_sync(0xffffffffu, want)) {
+        const float alpha = !want ? 1.f : (m_ref == -INFINITY ? 0.f : ex2(m_ref - mx));
+        l_sum *= alpha;
+        if (want) m_ref = mx;
+        if (a.j > 0) {
+            tmem_wait_ld();                      // (chunk 0 of x: loaded again below)
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                tmem_ld32(a.o_addr + c * 32, rb);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) rb[i] = __float_as_uint(__uint_as_float(rb[i]) * alpha);
+                tmem_st32(a.o_addr + c * 32, rb);
+            }
+        }
+    }
+    const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+    float ls0 = 0.f, ls1 = 0.f;
+    uint32_t pk[16];
+    tmem_wait_ld();
+    tmem_ld32(s_addr + 32, rb);
+    exp32<BF16>(ra, 1.0f, m_use, pk, ls0, ls1);
+    tmem_st16(s_addr, pk);
+    tmem_wait_ld();
+    tmem_ld32(s_addr + 64, ra);
+    exp32<BF16>(rb, 1.0f, m_use, pk, ls0, ls1);
+    tmem_st16(s_addr + 16, pk);
+    tmem_wait_ld();
+    tmem_ld32(s_addr + 96, rb);
+    tmem_wait_st();
+    tc_fence_before_sync();
+    mbar_arrive(p_half0);
+    exp32<BF16>(ra, 1.0f, m_use, pk, ls0, ls1);
+    tmem_st16(s_addr + 32, pk);
+    tmem_wait_ld();
+    exp32<BF16>(rb, 1.0f, m_use, pk, ls0, ls1);
+    tmem_st16(s_addr + 48, pk);
+    l_sum += ls0 + ls1;
+    tmem_wait_st();
+    tc_fence_before_sync();
+    mbar_arrive(p_half1);
+    a.m_ref = m_ref;
+    a.l_sum = l_sum;
+}
+
 // BIAS: 0 none, 1 read straight from global memory by the softmax threads (vector
 // bias, fp32 bias, unaligned views), 2 matrix bias staged tile by tile through TMA.
 // LISTS: a matrix bias came with tile lists (an instantiation of its own: the dense form pays for
@@ -660,6 +763,28 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&sm.p_half[t][1]);
+                continue;
+            }
+
+            if constexpr (BIAS != 0 && D == 128) {
+                // a block with a bias that crosses the causal diagonal or the end of the keys
+                MaskedBiasArgs a;
+                a.s_addr = s_addr;
+                a.o_addr = lane_base + o_col;
+                a.last_key = min(p.Tk - 1, p.causal ? row : p.Tk - 1) - n0;
+                a.n0 = n0;
+                a.row_l = row_l;
+                a.brow = brow;
+                a.j = j;
+                a.bias_bh = bias_bh;
+                a.vbias = (BIAS == 1 && vec_staged) ? &sm.vbias[BIAS == 1 ? t : 0][j & 1][0] : nullptr;
+                a.btile = btile;
+                a.m_ref = m_ref;
+                a.l_sum = l_sum;
+                masked_bias_block<D, BF16, BIAS>(p, a, BIAS == 2 ? &sm.b_empty[t][j % BSD] : nullptr, &sm.p_half[t][0],
+                                                 &sm.p_half[t][1]);
+                m_ref = a.m_ref;
+                l_sum = a.l_sum;
                 continue;
             }
 
