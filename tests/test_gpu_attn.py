@@ -111,6 +111,25 @@ def test_causal_with_bias(dt, d, kind):
         check(q, k, v, do, bias, True, f"causal {kind} d={d} ({tq},{tk})")
 
 
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("kind", [None, "vector", "matrix"])
+@pytest.mark.parametrize("shape", [(384, 384, True), (256, 300, False), (200, 330, True)])
+def test_scores_growing_along_the_keys(d, kind, shape):
+    """Scores that grow by about 7 nats per 128 keys: the softmax's reference maximum is raised in
+    every key block, the last one included - the block that crosses the causal diagonal or the
+    end of the keys, which has code of its own in the forward."""
+    tq, tk, causal = shape
+    g = gen(5 * d + tq + (0 if kind is None else len(kind)))
+    B, H = 1, 2
+    u = torch.ones(d)
+    ramp = 7.0 / (128 * d ** 0.5) * torch.arange(tk, dtype=torch.float32)
+    q = (0.3 * randn(g, B, tq, H, d) + u).to(torch.bfloat16)
+    k = (0.3 * randn(g, B, tk, H, d) + ramp[None, :, None, None] * u).to(torch.bfloat16)
+    v, do = randn(g, B, tk, H, d, dtype=torch.bfloat16), randn(g, B, tq, H, d, dtype=torch.bfloat16)
+    bias = None if kind is None else make_bias(g, kind, B, H, tq, tk, torch.bfloat16)
+    check(q, k, v, do, bias, causal, f"growing scores d={d} {kind} ({tq},{tk}) causal={causal}")
+
+
 def _uses_tmem_fwd(q, k, v):
     import ctypes as C
     from rgd_triton_b200 import _lib
