@@ -192,9 +192,11 @@ __device__ __forceinline__ void exp32(const uint32_t (&r)[32], float scale_log2,
 // A block with a bias that crosses the causal diagonal or the end of the keys: the two passes
 // of the interior bias block of the kernel below, with x of the hidden keys set to -inf as it
 // is formed.  Out of line on purpose: inlined next to the interior passes it costs those
-// 8-19 % (registers), and it runs for one or two of a tile's key blocks only.  head_dim 128
-// only: at head_dim 64 even the call costs the interior blocks of a dense bias 6 %, so those
-// kernels keep the per-element passes at the end of the key loop.
+// 8-19 % (registers), and it runs for one or two of a tile's key blocks only.  Used at
+// head_dim 128 by the kernels that read the bias from global memory or a staged vector
+// (BIAS == 1): in the kernels with a TMA-staged matrix bias even the call costs the interior
+// blocks 4-6 % (measured at both head dims), so those keep the per-element passes at the end
+// of the key loop for their masked blocks.
 // `last_key`: last visible key of this thread's row, relative to the block; `bias_row`: for
 // BIAS == 1 the 32-value loader's row pointer arguments, for BIAS == 2 the staged tile.
 struct MaskedBiasArgs {
@@ -766,7 +768,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tmem(const __grid_con
                 continue;
             }
 
-            if constexpr (BIAS != 0 && D == 128) {
+            if constexpr (BIAS == 1 && D == 128) {
                 // a block with a bias that crosses the causal diagonal or the end of the keys
                 MaskedBiasArgs a;
                 a.s_addr = s_addr;
