@@ -254,7 +254,7 @@ __device__ __noinline__ void masked_bias_block(const FwdTmaParams &p, MaskedBias
         l_sum *= alpha;
         if (want) m_ref = mx;
         if (a.j > 0) {
-            tmem_wait_ld();                      // (chunk 0 of x: loaded again below)
+            tmem_wait_ld();                      // chunk 0 of x has landed in ra; rb is free for the accumulator
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
                 tmem_ld32(a.o_addr + c * 32, rb);
